@@ -1,0 +1,89 @@
+// C interface of the kernel library.  Every function returns 0 on success; otherwise it
+// has launched nothing (or reports a failed launch) and rdl_last_error() gives the reason.
+// Pointers are device pointers unless said otherwise; `stream` is a cudaStream_t.
+#pragma once
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RDL_ACT_GELU_TANH 0
+#define RDL_ACT_SILU 1
+
+#define RDL_ABI_VERSION 1
+
+const char* rdl_last_error(void);
+int rdl_abi_version(void);
+
+// One attention call over a batch of sequences: the new tokens of this step are the queries,
+// keys and values come from a paged cache and from the step's own packed rows.
+typedef struct {
+    int dtype;                 // of q, k, v, cache and out
+    int n_tokens, n_seqs;      // query rows, sequences
+    int n_heads, n_kv_heads, head_dim;
+    float score_scale;         // scores are multiplied by it
+    float softcap;             // 0: none
+    int window;                // 0: all earlier keys; else keys with p - j < window
+    const void* q; long long q_stride;                       // row stride in elements; heads are contiguous
+    const void* k_new; const void* v_new; long long kv_stride;
+    void* out; long long out_stride;
+    const int* tok_seq; const int* tok_pos;                  // [n_tokens] sequence index and absolute position
+    const int* seq_start;                                    // [n_seqs + 1] first packed row of each sequence
+    const int* seq_past;                                     // [n_seqs] position of each sequence's first new token
+    const int* seq_cached;                                   // [n_seqs] keys below this position come from the cache
+    const void* k_cache; const void* v_cache;                // [pages][kv heads][page_size][head_dim]
+    const int* tables; int table_width, page_size, ring_pages;  // [n_seqs][table_width] page lists
+    // prefill kernels: query tiles, 64 rows each
+    const int* tile_seq; const int* tile_q0; int n_tiles;
+    // decode kernel: keys per split, splits launched per (token, kv head), float scratch
+    int keys_per_split, max_splits;
+    void* scratch; long long scratch_bytes;
+} AttentionArgs;
+
+int rdl_attention_plain(const AttentionArgs* a, void* stream);
+int rdl_attention_prefill(const AttentionArgs* a, void* stream);
+int rdl_attention_decode(const AttentionArgs* a, void* stream);
+long long rdl_attention_decode_scratch_bytes(int n_tokens, int n_heads, int head_dim, int max_splits);
+
+int rdl_embed_rows(void* out_f32, const void* table, int table_dtype, const int* ids, float scale,
+                   int n_rows, int hidden, int vocab, int* status, void* stream);
+int rdl_norm_residual_norm(const void* x, int x_dtype, const int* row_index,
+                           const void* w1, int w1_dtype, float eps1, float off1, void* res_f32,
+                           const void* w2, int w2_dtype, float eps2, float off2,
+                           void* y, int y_dtype, int n_rows, int hidden, void* stream);
+int rdl_gated_activation(void* out, const void* gate_up, int dtype, int activation, int n_rows, int inter, void* stream);
+int rdl_softcap_inplace(void* z_f32, long long total, float cap, void* stream);
+int rdl_residual_add(void* res_f32, const void* x, int x_dtype, long long total, void* stream);
+int rdl_convert_rows(void* out, int out_dtype, const void* in, int in_dtype, const int* row_index,
+                     int n_rows, int width, void* stream);
+
+int rdl_rope_cache(void* qkv, int dtype, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                   int rotary_dim, const float* cos_table, const float* sin_table,
+                   const int* tok_seq, const int* tok_pos, int do_rope, int do_write,
+                   void* k_cache, void* v_cache, const int* tables, int table_width, int page_size,
+                   int ring_pages, const int* seq_end, void* stream);
+
+// out[m, n] = sum_k x[m, k] * w[n, k], all float, plain FMA in a fixed order of k
+int rdl_gemm_f32(void* out, const void* x, const void* w, int m, int n, int k, void* stream);
+
+// sampling over float logits [rows, vocab]
+typedef struct {
+    float temperature;          // < 1e-7: greedy
+    int top_k;                  // 0: off
+    float top_p;                // >= 1: off
+    float repetition_penalty;   // 1: off
+    unsigned long long seed;
+} SamplingArgs;
+int rdl_sample(int* out_tokens, const float* logits, int n_rows, int vocab, const SamplingArgs* params,
+               const unsigned long long* row_stream, const int* row_step,
+               const int* history, const int* history_start, float* work, void* stream);
+// the uniform number in [0, 1) that rdl_sample draws with for (seed, stream id, step); host function
+float rdl_sampling_uniform(unsigned long long seed, unsigned long long stream, unsigned long long step);
+
+#ifdef __cplusplus
+}
+#endif
+
+#ifdef __cplusplus
+int rdl_check_attention_args(const AttentionArgs* a, const char* who);
+#endif

@@ -1,0 +1,19 @@
+// Error reporting of the kernel library: the last failure's message, per host thread.
+#include <stdarg.h>
+
+#include "api.h"
+#include "common.cuh"
+
+static thread_local char g_error[512] = "";
+
+void rdl_set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+extern "C" const char* rdl_last_error(void) { return g_error; }
+
+// Bumped whenever a signature in api.h changes, so that a stale build is noticed on load.
+extern "C" int rdl_abi_version(void) { return RDL_ABI_VERSION; }

@@ -1,0 +1,215 @@
+// Row-wise kernels: embedding gather, fused RMS norms with the residual sum, gated
+// activation, soft-cap.  All statistics and sums are computed in float.
+//
+// Formulas (reference, paths within rustml/):
+//   embedding gather * scale        nn/main/src/core/embedding.rs:50-76, nlp/main/src/core/model.rs:896-900
+//   x / sqrt(mean(x^2)+eps) * (w+o) core/main/src/core/tensor/ops.rs:735-743, nn/main/src/core/rms_norm.rs:43-50
+//   gelu_tanh(g) * u                nn/main/src/core/feed_forward.rs:151-161, core/main/src/core/tensor/ops.rs:433-438
+//   cap * tanh(z / cap)             nn/main/src/core/attention.rs:419-423
+#include "api.h"
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------------
+// embedding
+// ---------------------------------------------------------------------------------------------
+__global__ void embed_rows_kernel(float* __restrict__ out, const void* __restrict__ table, int table_dtype,
+                                  const int* __restrict__ ids, float scale, int hidden, int vocab,
+                                  int* __restrict__ status) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* o = out + (long long)t * hidden;
+    if (id < 0 || id >= vocab) {
+        // never a wrong result: the row is poisoned and the step reports the fault
+        for (int j = threadIdx.x; j < hidden; j += blockDim.x) o[j] = __int_as_float(0x7fc00000);
+        if (threadIdx.x == 0 && status) atomicExch(status, 1);
+        return;
+    }
+    const long long base = (long long)id * hidden;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) o[j] = rdl_load(table, base + j, table_dtype) * scale;
+}
+
+extern "C" int rdl_embed_rows(void* out_f32, const void* table, int table_dtype, const int* ids, float scale,
+                              int n_rows, int hidden, int vocab, int* status, void* stream) {
+    RDL_REQUIRE(rdl_valid_dtype(table_dtype), "embed_rows: bad table dtype %d", table_dtype);
+    RDL_REQUIRE(n_rows >= 0 && hidden > 0 && vocab > 0, "embed_rows: bad sizes rows=%d hidden=%d vocab=%d", n_rows, hidden, vocab);
+    if (n_rows == 0) return 0;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    embed_rows_kernel<<<n_rows, threads, 0, (cudaStream_t)stream>>>((float*)out_f32, table, table_dtype, ids, scale,
+                                                                     hidden, vocab, status);
+    RDL_CHECK_LAUNCH("embed_rows");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// fused norm / residual / norm
+//   t = w1 ? rms_norm(x; w1, eps1, off1) : x
+//   h = res ? res + t : t ;  res <- h (float) when res is given
+//   y = w2 ? rms_norm(h; w2, eps2, off2) : h          (written when y is given)
+// x rows may be gathered through row_index.
+// ---------------------------------------------------------------------------------------------
+struct NormArgs {
+    const void* x; int x_dtype;
+    const int* row_index;
+    const void* w1; int w1_dtype; float eps1, off1;
+    float* res;
+    const void* w2; int w2_dtype; float eps2, off2;
+    void* y; int y_dtype;
+    int hidden;
+};
+
+__global__ void norm_residual_norm_kernel(NormArgs a) {
+    extern __shared__ float row[];          // hidden floats
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const int H = a.hidden;
+    const long long xin = (long long)(a.row_index ? a.row_index[r] : r) * H;
+    const long long out = (long long)r * H;
+
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        const float v = rdl_load(a.x, xin + j, a.x_dtype);
+        row[j] = v;
+        ss += v * v;
+    }
+    if (a.w1) {
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)H + a.eps1);
+        for (int j = threadIdx.x; j < H; j += blockDim.x)
+            row[j] = row[j] * inv * (rdl_load(a.w1, j, a.w1_dtype) + a.off1);
+    }
+    if (a.res) {
+        for (int j = threadIdx.x; j < H; j += blockDim.x) {
+            const float h = a.res[out + j] + row[j];
+            a.res[out + j] = h;
+            row[j] = h;
+        }
+    }
+    if (!a.y) return;
+    if (a.w2) {
+        float s2 = 0.f;
+        for (int j = threadIdx.x; j < H; j += blockDim.x) s2 += row[j] * row[j];
+        s2 = block_sum(s2, scratch);
+        const float inv = 1.0f / sqrtf(s2 / (float)H + a.eps2);
+        for (int j = threadIdx.x; j < H; j += blockDim.x)
+            rdl_store(a.y, out + j, a.y_dtype, row[j] * inv * (rdl_load(a.w2, j, a.w2_dtype) + a.off2));
+    } else {
+        for (int j = threadIdx.x; j < H; j += blockDim.x) rdl_store(a.y, out + j, a.y_dtype, row[j]);
+    }
+}
+
+extern "C" int rdl_norm_residual_norm(const void* x, int x_dtype, const int* row_index,
+                                      const void* w1, int w1_dtype, float eps1, float off1,
+                                      void* res_f32,
+                                      const void* w2, int w2_dtype, float eps2, float off2,
+                                      void* y, int y_dtype, int n_rows, int hidden, void* stream) {
+    RDL_REQUIRE(rdl_valid_dtype(x_dtype) && rdl_valid_dtype(y_dtype), "norm: bad dtype");
+    RDL_REQUIRE(!w1 || rdl_valid_dtype(w1_dtype), "norm: bad dtype of the first weight");
+    RDL_REQUIRE(!w2 || rdl_valid_dtype(w2_dtype), "norm: bad dtype of the second weight");
+    RDL_REQUIRE(n_rows >= 0 && hidden > 0, "norm: bad sizes rows=%d hidden=%d", n_rows, hidden);
+    RDL_REQUIRE(!(row_index && res_f32), "norm: gathered rows cannot be combined with a residual");
+    RDL_REQUIRE(y || res_f32, "norm: nothing to write");
+    const size_t smem = (size_t)hidden * sizeof(float);
+    RDL_REQUIRE(smem <= 200 * 1024, "norm: hidden size %d needs %zu bytes of shared memory, limit is 204800", hidden, smem);
+    if (n_rows == 0) return 0;
+    if (smem > 48 * 1024) {
+        static size_t granted = 0;  // largest size already opted in
+        if (smem > granted) {
+            RDL_CUDA(cudaFuncSetAttribute(norm_residual_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "norm");
+            granted = smem;
+        }
+    }
+    NormArgs a{x, x_dtype, row_index, w1, w1_dtype, eps1, off1, (float*)res_f32, w2, w2_dtype, eps2, off2, y, y_dtype, hidden};
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    norm_residual_norm_kernel<<<n_rows, threads, smem, (cudaStream_t)stream>>>(a);
+    RDL_CHECK_LAUNCH("norm_residual_norm");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// gated activation: out[t, i] = act(gu[t, i]) * gu[t, I + i]
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float gelu_tanh(float x) {
+    const float k = 0.7978845608028654f;  // sqrt(2/pi)
+    return 0.5f * x * (1.0f + tanhf(k * (x + 0.044715f * x * x * x)));
+}
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
+
+__global__ void gated_activation_kernel(void* __restrict__ out, const void* __restrict__ gu, int dtype, int act,
+                                        long long n_rows, int inter) {
+    const long long total = n_rows * inter;
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long t = idx / inter;
+        const int i = (int)(idx - t * inter);
+        const float g = rdl_load(gu, t * 2 * inter + i, dtype);
+        const float u = rdl_load(gu, t * 2 * inter + inter + i, dtype);
+        const float a = act == RDL_ACT_GELU_TANH ? gelu_tanh(g) : silu(g);
+        rdl_store(out, idx, dtype, a * u);
+    }
+}
+
+extern "C" int rdl_gated_activation(void* out, const void* gate_up, int dtype, int activation, int n_rows, int inter,
+                                    void* stream) {
+    RDL_REQUIRE(rdl_valid_dtype(dtype), "gated_activation: bad dtype %d", dtype);
+    RDL_REQUIRE(activation == RDL_ACT_GELU_TANH || activation == RDL_ACT_SILU, "gated_activation: unknown activation %d", activation);
+    RDL_REQUIRE(n_rows >= 0 && inter > 0, "gated_activation: bad sizes");
+    if (n_rows == 0) return 0;
+    const long long total = (long long)n_rows * inter;
+    const int threads = 256;
+    const long long blocks = (total + threads - 1) / threads;
+    gated_activation_kernel<<<(unsigned)(blocks > 148 * 16 ? 148 * 16 : blocks), threads, 0, (cudaStream_t)stream>>>(
+        out, gate_up, dtype, activation, n_rows, inter);
+    RDL_CHECK_LAUNCH("gated_activation");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// soft-cap in place on float rows, and residual add
+// ---------------------------------------------------------------------------------------------
+__global__ void softcap_kernel(float* __restrict__ z, long long total, float cap) {
+    const float inv = 1.0f / cap;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+        z[i] = cap * tanhf(z[i] * inv);
+}
+
+extern "C" int rdl_softcap_inplace(void* z_f32, long long total, float cap, void* stream) {
+    RDL_REQUIRE(cap > 0.f, "softcap: cap must be positive, got %g", (double)cap);
+    RDL_REQUIRE(total >= 0, "softcap: bad size");
+    if (total == 0) return 0;
+    const long long blocks = (total + 255) / 256;
+    softcap_kernel<<<(unsigned)(blocks > 148 * 16 ? 148 * 16 : blocks), 256, 0, (cudaStream_t)stream>>>((float*)z_f32, total, cap);
+    RDL_CHECK_LAUNCH("softcap");
+    return 0;
+}
+
+__global__ void residual_add_kernel(float* __restrict__ res, const void* __restrict__ x, int dtype, long long total) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+        res[i] += rdl_load(x, i, dtype);
+}
+
+extern "C" int rdl_residual_add(void* res_f32, const void* x, int x_dtype, long long total, void* stream) {
+    RDL_REQUIRE(rdl_valid_dtype(x_dtype), "residual_add: bad dtype");
+    if (total <= 0) return 0;
+    const long long blocks = (total + 255) / 256;
+    residual_add_kernel<<<(unsigned)(blocks > 148 * 16 ? 148 * 16 : blocks), 256, 0, (cudaStream_t)stream>>>(
+        (float*)res_f32, x, x_dtype, total);
+    RDL_CHECK_LAUNCH("residual_add");
+    return 0;
+}
+
+// Copies `rows` rows of `width` floats/bf16 chosen by row_index into a dense output, converting dtype.
+__global__ void convert_rows_kernel(void* __restrict__ out, int out_dtype, const void* __restrict__ in, int in_dtype,
+                                    const int* __restrict__ row_index, int width) {
+    const long long src = (long long)(row_index ? row_index[blockIdx.x] : blockIdx.x) * width;
+    const long long dst = (long long)blockIdx.x * width;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) rdl_store(out, dst + j, out_dtype, rdl_load(in, src + j, in_dtype));
+}
+
+extern "C" int rdl_convert_rows(void* out, int out_dtype, const void* in, int in_dtype, const int* row_index,
+                                int n_rows, int width, void* stream) {
+    RDL_REQUIRE(rdl_valid_dtype(out_dtype) && rdl_valid_dtype(in_dtype), "convert_rows: bad dtype");
+    if (n_rows <= 0) return 0;
+    convert_rows_kernel<<<n_rows, 256, 0, (cudaStream_t)stream>>>(out, out_dtype, in, in_dtype, row_index, width);
+    RDL_CHECK_LAUNCH("convert_rows");
+    return 0;
+}

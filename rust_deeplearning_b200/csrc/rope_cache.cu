@@ -1,0 +1,81 @@
+// Rotary position encoding of the query and key heads of a packed [tokens, heads, head_dim]
+// buffer, in place, and the write of the new key and value rows into a paged cache.
+//
+// Rotation (reference: rustml/nn/main/src/core/rope.rs:188-191, half-split pairing):
+//   out[i]        = x[i] * cos - x[i + r/2] * sin
+//   out[i + r/2]  = x[i] * sin + x[i + r/2] * cos      for i < r/2, r = rotary_dim
+// with cos/sin read from float tables [position][r/2]; the product is formed in float.
+// The cache write corresponds to rustml/nn/main/src/core/kv_cache.rs:97-109, with pages and a
+// length per sequence instead of one shared length.
+#include "api.h"
+#include "common.cuh"
+
+template <typename T>
+__global__ void rope_cache_kernel(T* __restrict__ qkv, int n_heads, int n_kv_heads, int head_dim, int rotary_dim,
+                                  const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                  const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                                  int do_rope, int do_write, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                  const int* __restrict__ tables, int table_width, int page_size, int ring_pages,
+                                  const int* __restrict__ seq_end) {
+    const int t = blockIdx.x;
+    const int head = blockIdx.y;
+    const int total_heads = n_heads + 2 * n_kv_heads;
+    T* row = qkv + ((long long)t * total_heads + head) * head_dim;
+    const int pos = tok_pos[t];
+    if (pos < 0) return;  // a padding row of a fixed-size batch
+    const bool is_v = head >= n_heads + n_kv_heads;
+
+    if (do_rope && !is_v) {
+        const int half = rotary_dim >> 1;
+        const float* c = cos_t + (long long)pos * half;
+        const float* s = sin_t + (long long)pos * half;
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const float x1 = to_float(row[i]), x2 = to_float(row[i + half]);
+            const float cs = c[i], sn = s[i];
+            row[i] = from_float<T>(x1 * cs - x2 * sn);
+            row[i + half] = from_float<T>(x1 * sn + x2 * cs);
+        }
+    }
+    if (!do_write || head < n_heads) return;
+    const int seq = tok_seq[t];
+    // In a ring a later token of this step may land on the same row: only the last writer writes.
+    const long long ring_rows = (long long)ring_pages * page_size;
+    if ((long long)pos + ring_rows < (long long)seq_end[seq]) return;
+    __syncthreads();  // the rotated key of this block is complete
+    const int kv_head = is_v ? head - n_heads - n_kv_heads : head - n_heads;
+    T* dst = (is_v ? v_cache : k_cache) +
+             rdl_cache_offset(tables + (long long)seq * table_width, pos, page_size, ring_pages, n_kv_heads, kv_head, head_dim);
+    for (int i = threadIdx.x; i < head_dim; i += blockDim.x) dst[i] = row[i];
+}
+
+extern "C" int rdl_rope_cache(void* qkv, int dtype, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                              int rotary_dim, const float* cos_table, const float* sin_table,
+                              const int* tok_seq, const int* tok_pos, int do_rope, int do_write,
+                              void* k_cache, void* v_cache, const int* tables, int table_width, int page_size,
+                              int ring_pages, const int* seq_end, void* stream) {
+    RDL_REQUIRE(rdl_valid_dtype(dtype), "rope_cache: bad dtype %d", dtype);
+    RDL_REQUIRE(n_tokens >= 0 && n_heads >= 0 && n_kv_heads >= 0 && n_heads + n_kv_heads > 0 && head_dim > 0,
+                "rope_cache: bad sizes tokens=%d heads=%d kv_heads=%d head_dim=%d", n_tokens, n_heads, n_kv_heads, head_dim);
+    RDL_REQUIRE(!do_rope || (rotary_dim > 0 && rotary_dim % 2 == 0 && rotary_dim <= head_dim && cos_table && sin_table),
+                "rope_cache: rotary_dim %d must be even and at most head_dim %d", rotary_dim, head_dim);
+    RDL_REQUIRE(!do_write || n_kv_heads == 0 ||
+                    (k_cache && v_cache && tables && seq_end && tok_seq && page_size > 0 && ring_pages > 0 && ring_pages <= table_width),
+                "rope_cache: cache write needs storage, page tables and lengths (page_size=%d ring_pages=%d table_width=%d)",
+                page_size, ring_pages, table_width);
+    const int total_heads = n_heads + 2 * n_kv_heads;
+    RDL_REQUIRE(total_heads <= 65535, "rope_cache: %d heads exceed the grid limit", total_heads);
+    if (n_tokens == 0) return 0;
+    dim3 grid(n_tokens, total_heads);
+    const int threads = head_dim >= 256 ? 128 : (head_dim >= 64 ? 64 : 32);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == RDL_BF16)
+        rope_cache_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>((__nv_bfloat16*)qkv, n_heads, n_kv_heads, head_dim, rotary_dim,
+            cos_table, sin_table, tok_seq, tok_pos, do_rope, do_write, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
+            tables, table_width, page_size, ring_pages, seq_end);
+    else
+        rope_cache_kernel<float><<<grid, threads, 0, st>>>((float*)qkv, n_heads, n_kv_heads, head_dim, rotary_dim,
+            cos_table, sin_table, tok_seq, tok_pos, do_rope, do_write, (float*)k_cache, (float*)v_cache,
+            tables, table_width, page_size, ring_pages, seq_end);
+    RDL_CHECK_LAUNCH("rope_cache");
+    return 0;
+}

@@ -1,0 +1,349 @@
+"""Typed entry points of the CUDA kernels, over torch tensors.
+
+Each function checks devices, dtypes, shapes and contiguity, launches on torch's
+current stream and returns torch tensors.  There is no other implementation
+behind these names: on a machine without the library or without a GPU they
+raise.  Parts call them as `ops.<name>` (attribute lookup at call time).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import NamedTuple, Optional, Tuple
+
+import torch
+
+from . import library
+from .library import AttentionArgs, KernelError, SamplingArgs
+
+ACTIVATIONS = {"gelu_pytorch_tanh": 0, "gelu_tanh": 0, "silu": 1}
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype is torch.float32:
+        return 0
+    if t.dtype is torch.bfloat16:
+        return 1
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {t.dtype}")
+
+
+def _stream(t: torch.Tensor):
+    if not t.is_cuda:
+        raise KernelError("kernels run on CUDA tensors only; there is no CPU path")
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _need(cond, msg):
+    if not cond:
+        raise KernelError(msg)
+
+
+def _dense(t, name):
+    _need(t.is_contiguous(), f"{name} must be contiguous")
+    return t
+
+
+def _int32(t, name, n=None):
+    _need(t.dtype is torch.int32 and t.is_contiguous(), f"{name} must be a contiguous int32 tensor")
+    if n is not None:
+        _need(t.numel() >= n, f"{name} holds {t.numel()} entries, {n} are needed")
+    return t
+
+
+# ------------------------------------------------------------------------------------------
+# row-wise kernels
+# ------------------------------------------------------------------------------------------
+
+def embed_rows(table: torch.Tensor, ids: torch.Tensor, scale: float, status: Optional[torch.Tensor] = None):
+    """float32 rows `table[ids] * scale`.  An id outside the table poisons its row with NaN and
+    sets `status[0]` (int32) if given."""
+    _dense(table, "embedding table")
+    _int32(ids, "ids")
+    V, H = table.shape
+    T = ids.numel()
+    out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    library.check(library.load().rdl_embed_rows(_ptr(out), _ptr(table), _dtype_code(table), _ptr(ids), float(scale),
+                                                T, H, V, _ptr(status), _stream(table)))
+    return out
+
+
+class NormParams(NamedTuple):
+    weight: torch.Tensor
+    eps: float
+    offset: float
+
+
+def norm_residual_norm(x: torch.Tensor, *, first: Optional[NormParams] = None, residual: Optional[torch.Tensor] = None,
+                       second: Optional[NormParams] = None, out_dtype: Optional[torch.dtype] = None,
+                       row_index: Optional[torch.Tensor] = None, want_output: bool = True):
+    """t = first ? rms_norm(x; first) : x;  h = residual + t (written back to `residual`, float32)
+    or t;  returns second ? rms_norm(h; second) : h in `out_dtype`, or None if not wanted.
+    rms_norm(v; w, eps, off) = v / sqrt(mean(v^2) + eps) * (w + off), statistics in float32."""
+    _dense(x, "x")
+    _need(x.dim() == 2, "x must be [rows, hidden]")
+    H = x.shape[1]
+    rows = row_index.numel() if row_index is not None else x.shape[0]
+    if row_index is not None:
+        _int32(row_index, "row_index")
+    for p, name in ((first, "first"), (second, "second")):
+        if p is not None:
+            _need(p.weight.is_contiguous() and p.weight.numel() == H, f"{name} norm weight must hold {H} values")
+    if residual is not None:
+        _need(residual.dtype is torch.float32 and residual.is_contiguous() and tuple(residual.shape) == (rows, H),
+              "residual must be a contiguous float32 [rows, hidden] tensor")
+    y = torch.empty((rows, H), dtype=out_dtype or x.dtype, device=x.device) if want_output else None
+    _need(y is not None or residual is not None, "norm_residual_norm: nothing to write")
+    library.check(library.load().rdl_norm_residual_norm(
+        _ptr(x), _dtype_code(x), _ptr(row_index),
+        _ptr(first.weight) if first else None, _dtype_code(first.weight) if first else 0,
+        float(first.eps) if first else 0.0, float(first.offset) if first else 0.0,
+        _ptr(residual),
+        _ptr(second.weight) if second else None, _dtype_code(second.weight) if second else 0,
+        float(second.eps) if second else 0.0, float(second.offset) if second else 0.0,
+        _ptr(y), _dtype_code(y) if y is not None else 0, rows, H, _stream(x)))
+    return y
+
+
+def gated_activation(gate_up: torch.Tensor, activation: str):
+    """[rows, 2I] -> [rows, I]: act(gate_up[:, :I]) * gate_up[:, I:], computed in float32."""
+    _dense(gate_up, "gate_up")
+    _need(activation in ACTIVATIONS, f"unknown activation '{activation}', known: {sorted(ACTIVATIONS)}")
+    rows, two_i = gate_up.shape
+    _need(two_i % 2 == 0, "gate_up must have an even width")
+    out = torch.empty((rows, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    library.check(library.load().rdl_gated_activation(_ptr(out), _ptr(gate_up), _dtype_code(gate_up),
+                                                      ACTIVATIONS[activation], rows, two_i // 2, _stream(gate_up)))
+    return out
+
+
+def softcap_(z: torch.Tensor, cap: float):
+    """In place on float32: cap * tanh(z / cap)."""
+    _need(z.dtype is torch.float32 and z.is_contiguous(), "softcap_ takes a contiguous float32 tensor")
+    library.check(library.load().rdl_softcap_inplace(_ptr(z), z.numel(), float(cap), _stream(z)))
+    return z
+
+
+def residual_add_(residual: torch.Tensor, x: torch.Tensor):
+    _need(residual.dtype is torch.float32 and residual.is_contiguous() and x.is_contiguous()
+          and residual.shape == x.shape, "residual_add_ takes a float32 residual and an addend of the same shape")
+    library.check(library.load().rdl_residual_add(_ptr(residual), _ptr(x), _dtype_code(x), residual.numel(), _stream(x)))
+    return residual
+
+
+def convert_rows(x: torch.Tensor, out_dtype: torch.dtype, row_index: Optional[torch.Tensor] = None):
+    """Rows of x (all, or those `row_index` names) converted to `out_dtype`."""
+    _dense(x, "x")
+    rows = row_index.numel() if row_index is not None else x.shape[0]
+    if row_index is not None:
+        _int32(row_index, "row_index")
+    out = torch.empty((rows, x.shape[1]), dtype=out_dtype, device=x.device)
+    library.check(library.load().rdl_convert_rows(_ptr(out), _dtype_code(out), _ptr(x), _dtype_code(x), _ptr(row_index),
+                                                  rows, x.shape[1], _stream(x)))
+    return out
+
+
+# ------------------------------------------------------------------------------------------
+# matrix products
+# ------------------------------------------------------------------------------------------
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None):
+    """x [rows, in] times weight [out, in] transposed.
+
+    float32: the library's own FMA kernel (no tensor cores, no reduced-precision mode).
+    bfloat16: a library matrix product with float32 accumulation (cuBLAS through torch), where
+    the reference's engine calls a GEMM library as well."""
+    _need(x.dim() == 2 and weight.dim() == 2 and x.shape[1] == weight.shape[1],
+          f"linear: shapes {tuple(x.shape)} and {tuple(weight.shape)} do not fit")
+    _need(x.dtype is weight.dtype, f"linear: input is {x.dtype}, weight is {weight.dtype}")
+    out_dtype = out_dtype or x.dtype
+    if x.dtype is torch.float32:
+        _need(out_dtype is torch.float32, "linear: the 32-bit path writes float32")
+        _dense(x, "x"); _dense(weight, "weight")
+        out = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.float32, device=x.device)
+        library.check(library.load().rdl_gemm_f32(_ptr(out), _ptr(x), _ptr(weight), x.shape[0], weight.shape[0],
+                                                  x.shape[1], _stream(x)))
+        return out
+    _need(x.is_cuda, "kernels run on CUDA tensors only; there is no CPU path")
+    if out_dtype is torch.float32:
+        return torch.mm(x, weight.t(), out_dtype=torch.float32)
+    return torch.mm(x, weight.t())
+
+
+# ------------------------------------------------------------------------------------------
+# position encoding, cache write, attention
+# ------------------------------------------------------------------------------------------
+
+class KVPages(NamedTuple):
+    """One schedule entry's key/value storage and the page lists of the step's sequences."""
+    k: torch.Tensor            # [pages, kv_heads, page_size, head_dim]
+    v: torch.Tensor
+    tables: torch.Tensor       # int32 [n_seqs, table_width]
+    page_size: int
+    ring_pages: int            # entries of a page list used as a ring (= table width when all keys are kept)
+
+
+def rope_cache(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, *, tok_seq, tok_pos,
+               cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None, rotary_dim: int = 0,
+               pages: Optional[KVPages] = None, seq_end: Optional[torch.Tensor] = None):
+    """In place on packed rows [tokens, (n_heads + 2 n_kv_heads) * head_dim]: rotate query and key heads by
+    the tables (if given), then write key and value rows to the cache (if `pages` is given)."""
+    _dense(qkv, "qkv")
+    T = qkv.shape[0]
+    _need(qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim, "qkv width does not match the head counts")
+    _int32(tok_pos, "tok_pos", T)
+    _int32(tok_seq, "tok_seq", T)
+    do_rope = cos is not None
+    if do_rope:
+        _need(cos.dtype is torch.float32 and sin.dtype is torch.float32 and cos.is_contiguous() and sin.is_contiguous()
+              and cos.shape == sin.shape and cos.shape[1] * 2 == rotary_dim, "rotary tables must be float32 [positions, rotary_dim/2]")
+    do_write = pages is not None and n_kv_heads > 0
+    if do_write:
+        _need(pages.k.dtype is qkv.dtype and pages.v.dtype is qkv.dtype, "cache dtype differs from the activations'")
+        _need(tuple(pages.k.shape[1:]) == (n_kv_heads, pages.page_size, head_dim) and pages.k.is_contiguous()
+              and pages.v.is_contiguous() and pages.v.shape == pages.k.shape, "cache storage has the wrong shape")
+        _int32(pages.tables, "page tables")
+        _int32(seq_end, "seq_end")
+    library.check(library.load().rdl_rope_cache(
+        _ptr(qkv), _dtype_code(qkv), T, n_heads, n_kv_heads, head_dim, rotary_dim,
+        _ptr(cos), _ptr(sin), _ptr(tok_seq), _ptr(tok_pos), int(do_rope), int(do_write),
+        _ptr(pages.k) if do_write else None, _ptr(pages.v) if do_write else None,
+        _ptr(pages.tables) if do_write else None, pages.tables.shape[1] if do_write else 0,
+        pages.page_size if do_write else 0, pages.ring_pages if do_write else 0,
+        _ptr(seq_end) if do_write else None, _stream(qkv)))
+    return qkv
+
+
+class AttentionBatch(NamedTuple):
+    """The step's sequences as the attention kernels see them (device int32 tensors)."""
+    n_tokens: int
+    n_seqs: int
+    tok_seq: torch.Tensor      # [tokens]
+    tok_pos: torch.Tensor      # [tokens], -1 marks a padding row
+    seq_start: torch.Tensor    # [seqs + 1]
+    seq_past: torch.Tensor     # [seqs]
+    seq_cached: torch.Tensor   # [seqs] keys below this position are read from the cache
+    tile_seq: Optional[torch.Tensor] = None   # prefill: 64-row query tiles
+    tile_q0: Optional[torch.Tensor] = None
+    n_tiles: int = 0
+    max_keys: int = 0          # decode: longest key run any token of the batch reads (window applied)
+
+
+def _attention_args(q, q_stride, k_new, v_new, kv_stride, out, b: AttentionBatch, pages: Optional[KVPages],
+                    n_heads, n_kv_heads, head_dim, score_scale, softcap, window):
+    a = AttentionArgs()
+    a.dtype = _dtype_code(out)
+    a.n_tokens, a.n_seqs = b.n_tokens, b.n_seqs
+    a.n_heads, a.n_kv_heads, a.head_dim = n_heads, n_kv_heads, head_dim
+    a.score_scale = float(score_scale)
+    a.softcap = float(softcap or 0.0)
+    a.window = int(window or 0)
+    a.q, a.q_stride = q, q_stride
+    a.k_new, a.v_new, a.kv_stride = k_new, v_new, kv_stride
+    a.out, a.out_stride = out.data_ptr(), out.stride(0)
+    a.tok_seq, a.tok_pos = b.tok_seq.data_ptr(), b.tok_pos.data_ptr()
+    a.seq_start, a.seq_past, a.seq_cached = b.seq_start.data_ptr(), b.seq_past.data_ptr(), b.seq_cached.data_ptr()
+    if pages is not None:
+        a.k_cache, a.v_cache = pages.k.data_ptr(), pages.v.data_ptr()
+        a.tables, a.table_width = pages.tables.data_ptr(), pages.tables.shape[1]
+        a.page_size, a.ring_pages = pages.page_size, pages.ring_pages
+    return a
+
+
+def choose_keys_per_split(n_tokens: int, n_kv_heads: int, max_keys: int, page_size: int) -> int:
+    """Keys per block of the decode kernel: the largest run (in pages) that still gives the GPU
+    about four blocks per multiprocessor; at least one page."""
+    for pages in (8, 4, 2):
+        keys = pages * page_size
+        if n_tokens * n_kv_heads * ((max_keys + keys - 1) // keys) >= 4 * 148:
+            return keys
+    return page_size
+
+
+def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n_heads: int, n_kv_heads: int,
+              head_dim: int, score_scale: float, softcap: Optional[float], window: Optional[int],
+              new_kv: Optional[Tuple[torch.Tensor, int, int]] = None, kind: str = "auto",
+              scratch=None, keys_per_split: Optional[int] = None):
+    """Attention of the step's tokens over cache and new rows.
+
+    q: [tokens, >= n_heads * head_dim] rows whose first n_heads * head_dim values are the (rotated)
+    query heads; the row stride may be larger (packed q/k/v rows).
+    new_kv: (rows, k_col, v_col) - this step's packed rows and the columns at which the rotated
+    keys and the values start; needed when `b.seq_cached` says that new keys are not in the cache.
+    kind: "plain" (float arithmetic, any dtype), "prefill" (bfloat16, tensor cores), "decode"
+    (bfloat16, split keys; reads the cache only), or "auto".
+    scratch: callable(nbytes) -> float32 tensor, for the decode kernel's partial results.
+    Returns [tokens, n_heads * head_dim] in the dtype of q."""
+    _need(q.dim() == 2 and q.stride(1) == 1 and q.shape[1] >= n_heads * head_dim, "attention: bad query rows")
+    T = q.shape[0]
+    _need(T >= b.n_tokens, "attention: fewer rows than tokens")
+    out = torch.empty((T, n_heads * head_dim), dtype=q.dtype, device=q.device)
+    es = q.element_size()
+    k_new = v_new = None
+    kv_stride = 0
+    if new_kv is not None:
+        rows, k_col, v_col = new_kv
+        _need(rows.dtype is q.dtype and rows.dim() == 2 and rows.stride(1) == 1 and
+              rows.shape[1] >= max(k_col, v_col) + n_kv_heads * head_dim, "attention: bad new key/value rows")
+        k_new, v_new, kv_stride = rows.data_ptr() + k_col * es, rows.data_ptr() + v_col * es, rows.stride(0)
+    a = _attention_args(q.data_ptr(), q.stride(0), k_new, v_new, kv_stride, out, b, pages, n_heads, n_kv_heads,
+                        head_dim, score_scale, softcap, window)
+    if pages is not None:
+        _need(pages.k.dtype is q.dtype, "attention: cache dtype differs from the activations'")
+    fast_ok = q.dtype is torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256
+    if kind == "auto":
+        kind = "prefill" if fast_ok and b.n_tiles > 0 else "plain"
+    lib = library.load()
+    if kind == "plain":
+        library.check(lib.rdl_attention_plain(ctypes.byref(a), _stream(q)))
+    elif kind == "prefill":
+        _need(b.tile_seq is not None and b.tile_q0 is not None, "attention: prefill needs query tiles")
+        a.tile_seq, a.tile_q0, a.n_tiles = b.tile_seq.data_ptr(), b.tile_q0.data_ptr(), b.n_tiles
+        library.check(lib.rdl_attention_prefill(ctypes.byref(a), _stream(q)))
+    elif kind == "decode":
+        _need(pages is not None, "attention: decode reads the cache")
+        ks = keys_per_split or choose_keys_per_split(b.n_tokens, n_kv_heads, b.max_keys, pages.page_size)
+        a.keys_per_split = ks
+        # a run of max_keys positions can straddle one more split than its length suggests
+        a.max_splits = (max(b.max_keys, 1) + ks - 1) // ks + 1
+        need = lib.rdl_attention_decode_scratch_bytes(b.n_tokens, n_heads, head_dim, a.max_splits)
+        buf = scratch(need) if scratch is not None else torch.empty(-(-need // 4), dtype=torch.float32, device=q.device)
+        _need(buf.dtype is torch.float32 and buf.numel() * 4 >= need, "attention: decode scratch too small")
+        a.scratch, a.scratch_bytes = buf.data_ptr(), buf.numel() * 4
+        library.check(lib.rdl_attention_decode(ctypes.byref(a), _stream(q)))
+    else:
+        raise KernelError(f"attention: unknown kind '{kind}'")
+    return out
+
+
+# ------------------------------------------------------------------------------------------
+# sampling
+# ------------------------------------------------------------------------------------------
+
+def sample(logits: torch.Tensor, *, temperature: float, top_k: Optional[int] = None, top_p: Optional[float] = None,
+           repetition_penalty: Optional[float] = None, seed: int = 0, row_stream: Optional[torch.Tensor] = None,
+           row_step: Optional[torch.Tensor] = None, history: Optional[torch.Tensor] = None,
+           history_start: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None):
+    """One token per row of float32 logits [rows, vocab] -> int32 [rows]."""
+    _need(logits.dtype is torch.float32 and logits.dim() == 2 and logits.is_contiguous(),
+          "sample takes contiguous float32 logits [rows, vocab]")
+    rows, vocab = logits.shape
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    prm = SamplingArgs(float(temperature), int(top_k or 0), float(top_p if top_p is not None else 1.0),
+                       float(repetition_penalty if repetition_penalty is not None else 1.0), int(seed) & (2**64 - 1))
+    work = None
+    if temperature >= 1e-7:
+        work = torch.empty_like(logits)
+        if row_stream is not None:
+            _need(row_stream.dtype is torch.int64 and row_stream.numel() >= rows, "row_stream must be int64 [rows]")
+        if row_step is not None:
+            _int32(row_step, "row_step", rows)
+        if history is not None:
+            _int32(history, "history")
+            _int32(history_start, "history_start", rows + 1)
+    library.check(library.load().rdl_sample(_ptr(out), _ptr(logits), rows, vocab, ctypes.byref(prm), _ptr(row_stream),
+                                            _ptr(row_step), _ptr(history), _ptr(history_start), _ptr(work), _stream(logits)))
+    return out

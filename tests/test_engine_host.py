@@ -1,0 +1,115 @@
+"""The engine's host logic (packing, paging, rings, slots, schedules) on a machine without a GPU:
+the CUDA entry points are replaced by the plain functions of tests/kernel_refs.py, everything
+above them is the product's code.  Logits are compared with the plain implementation."""
+import numpy as np
+import pytest
+import torch
+
+import kernel_refs
+import plain_gemma2 as plain
+import tiny_configs
+from rust_deeplearning_b200.config.base import architecture_for
+from rust_deeplearning_b200.engine.step import Engine
+from rust_deeplearning_b200.parts.model import Model
+from rust_deeplearning_b200.weights.loader import load_weights
+from rust_deeplearning_b200.weights.random_init import write_random_model
+
+TOL = 2e-5   # float32 activations between float64 kernels
+
+
+def build(tmp_path, name, monkeypatch, page_size=4, max_tokens=4096, max_seqs=None):
+    kernel_refs.install(monkeypatch)
+    cfg, seed = tiny_configs.config(name)
+    folder = str(tmp_path / f"tiny_{name}")
+    write_random_model(folder, cfg, seed, "float32")
+    arch = architecture_for(cfg)
+    spec = arch.build_spec(arch.parse_config(cfg))
+    model = Model(spec, load_weights(spec, folder, torch.float32, "cpu"), torch.float32, "cpu")
+    engine = Engine(model, max_tokens=max_tokens, max_seqs=max_seqs, page_size=page_size, use_graphs=False)
+    pcfg, pw = plain.load_folder(folder)
+    return engine, pcfg, pw
+
+
+def prompt(rng, n, vocab):
+    return [int(v) for v in rng.integers(0, vocab, size=n)]
+
+
+def close(got, want):
+    got = got.detach().cpu().double().numpy()
+    assert got.shape == want.shape
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= TOL, np.abs(got - want).max()
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_whole_prompt_equals_plain(tmp_path, monkeypatch, name):
+    engine, cfg, w = build(tmp_path, name, monkeypatch)
+    rng = np.random.default_rng(1)
+    ids = prompt(rng, 37, cfg["vocab_size"])          # longer than both windows
+    slot = engine.new_sequence()
+    logits = engine.step([slot], [ids], "all")
+    close(logits, plain.forward(cfg, w, ids))
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_token_by_token_and_chunks_equal_plain(tmp_path, monkeypatch, name):
+    engine, cfg, w = build(tmp_path, name, monkeypatch)
+    rng = np.random.default_rng(2)
+    ids = prompt(rng, 45, cfg["vocab_size"])
+    want = plain.forward(cfg, w, ids)
+    # a prefix whole, then one by one
+    slot = engine.new_sequence()
+    close(engine.step([slot], [ids[:13]], "all"), want[:13])
+    for t in range(13, 45):
+        close(engine.step([slot], [[ids[t]]], "all"), want[t:t + 1])
+    engine.release(slot)
+    # the same in three chunks: a chunk after an existing prefix reads cache and new rows
+    slot = engine.new_sequence()
+    close(engine.step([slot], [ids[:7]], "all"), want[:7])
+    close(engine.step([slot], [ids[7:30]], "all"), want[7:30])
+    close(engine.step([slot], [ids[30:]], "all"), want[30:])
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_unequal_batches_and_slot_reuse(tmp_path, monkeypatch, name):
+    engine, cfg, w = build(tmp_path, name, monkeypatch, max_tokens=256, max_seqs=4)
+    rng = np.random.default_rng(3)
+    V = cfg["vocab_size"]
+    for round_ in range(3):                      # one batch after another on the same small cache
+        lens = [1, 9, 23, 40] if round_ % 2 == 0 else [17, 5, 11]
+        extra = [3, 12, 6, 1]
+        seqs = [prompt(rng, n + e, V) for n, e in zip(lens, extra)]
+        want = [plain.forward(cfg, w, s) for s in seqs]
+        slots = [engine.new_sequence() for _ in seqs]
+        got = engine.step(slots, [s[:n] for s, n in zip(seqs, lens)], "all")
+        close(got, np.concatenate([wv[:n] for wv, n in zip(want, lens)]))
+        pos = list(lens)
+        live = list(range(len(seqs)))
+        while live:
+            got = engine.step([slots[i] for i in live], [[seqs[i][pos[i]]] for i in live], "last")
+            close(got, np.stack([want[i][pos[i]] for i in live]))
+            for i in live:
+                pos[i] += 1
+            for i in [i for i in live if pos[i] == len(seqs[i])]:
+                engine.release(slots[i])         # shorter requests end earlier
+            live = [i for i in live if pos[i] < len(seqs[i])]
+        assert engine.cache.n_free_slots == 4
+        assert all(g.pool.n_free == g.pool.n_pages for g in engine.cache.kv_groups)
+
+
+def test_wanted_places_and_errors(tmp_path, monkeypatch):
+    engine, cfg, w = build(tmp_path, "A", monkeypatch)
+    from rust_deeplearning_b200.engine.step import StepError
+    rng = np.random.default_rng(4)
+    a, b = prompt(rng, 6, 256), prompt(rng, 11, 256)
+    s0, s1 = engine.new_sequence(), engine.new_sequence()
+    got = engine.step([s0, s1], [a, b], [[0, 5], []])
+    close(got, plain.forward(cfg, w, a)[[0, 5]])
+    assert engine.length(s0) == 6 and engine.length(s1) == 11
+    got = engine.step([s1, s0], [[3], [4]], [[0], []])
+    close(got, plain.forward(cfg, w, b + [3])[-1:])
+    with pytest.raises(StepError):
+        engine.step([s0], [[256]])
+    with pytest.raises(StepError):
+        engine.step([s0], [[]])
+    assert engine.length(s0) == 7                 # failed steps changed nothing
