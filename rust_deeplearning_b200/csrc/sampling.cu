@@ -120,9 +120,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(int* __restrict_
     }
 
     float* w = work + (long long)row * vocab;
-    const float inv_t = 1.0f / prm.temperature;
     // ---- penalty (once per distinct token, from the untouched logits) and temperature ----
-    for (int i = tid; i < vocab; i += SAMPLE_THREADS) w[i] = x[i] * inv_t;
+    for (int i = tid; i < vocab; i += SAMPLE_THREADS) w[i] = x[i] / prm.temperature;
     __syncthreads();
     if (prm.repetition_penalty != 1.0f && history) {
         const int hb = history_start[row], he = history_start[row + 1];
@@ -130,7 +129,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(int* __restrict_
             const int tok = history[i];
             if (tok >= 0 && tok < vocab) {
                 const float v = x[tok];
-                w[tok] = (v > 0.f ? v / prm.repetition_penalty : v * prm.repetition_penalty) * inv_t;  // equal writers
+                w[tok] = (v > 0.f ? v / prm.repetition_penalty : v * prm.repetition_penalty) / prm.temperature;  // equal writers
             }
         }
         __syncthreads();

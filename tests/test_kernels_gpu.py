@@ -1,0 +1,278 @@
+"""Each CUDA kernel alone against its plain reference (tests/kernel_refs.py, float64), at sizes
+other than the engine's: odd row counts, head sizes in steps of 16, widths and vocabularies that
+are no power of two, windows shorter and longer than the context, ring caches that wrap.
+Outputs are allocated by the kernels' wrappers with torch.empty, so stale values would show."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import kernel_refs as ref
+from rust_deeplearning_b200.kernels import ops
+from rust_deeplearning_b200.sampling.sampler import uniform_for
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+BF16_EPS = 2.0 ** -8      # half a unit in the last place of bfloat16, relative
+
+
+def rnd(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def assert_close(got, want, dtype, rel=4.0, what=""):
+    """float32 results agree to ~1e-5 relative to the tensor's scale; bfloat16 results to a few
+    units of bfloat16 rounding of that scale."""
+    got, want = got.double().cpu(), want.double().cpu()
+    assert got.shape == want.shape, (got.shape, want.shape)
+    assert torch.isfinite(got).all(), f"{what}: non-finite output"
+    scale = max(want.abs().max().item(), 1e-6)
+    tol = (2e-5 if dtype is torch.float32 else rel * BF16_EPS) * scale
+    err = (got - want).abs().max().item()
+    assert err <= tol, f"{what}: max error {err:.3e} > {tol:.3e} (scale {scale:.3e})"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_rows(dtype):
+    table = rnd((131, 80), dtype, 0)
+    ids = torch.tensor([0, 130, 5, 5, 77], dtype=torch.int32, device=DEV)
+    got = ops.embed_rows(table, ids, math.sqrt(80))
+    assert_close(got, ref.embed_rows(table, ids, math.sqrt(80)), torch.float32)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    bad = ops.embed_rows(table, torch.tensor([3, 131], dtype=torch.int32, device=DEV), 1.0, status)
+    assert status.item() == 1 and torch.isnan(bad[1]).all() and torch.isfinite(bad[0]).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hidden", [80, 2304, 5000])
+def test_norm_residual_norm(dtype, hidden):
+    rows = 7
+    x = rnd((rows, hidden), dtype, 1, 3.0)
+    w1 = ops.NormParams(rnd((hidden,), dtype, 2, 0.5), 1e-5, 1.0)
+    w2 = ops.NormParams(rnd((hidden,), torch.float32, 3, 0.5), 1e-6, 0.0)   # a norm weight kept in 32 bits
+    res = rnd((rows, hidden), torch.float32, 4, 2.0)
+    # norm only
+    assert_close(ops.norm_residual_norm(x, second=w1), ref.norm_residual_norm(x, second=w1), dtype, what="norm")
+    # post-norm, residual add, pre-norm in one kernel
+    r_got, r_ref = res.clone(), res.clone()
+    y = ops.norm_residual_norm(x, first=w1, residual=r_got, second=w2, out_dtype=dtype)
+    y_ref = ref.norm_residual_norm(x, first=w1, residual=r_ref, second=w2, out_dtype=dtype)
+    assert_close(r_got, r_ref, torch.float32, what="residual")
+    assert_close(y, y_ref, dtype, what="fused output")
+    # residual update without output, and a plain add
+    r_got, r_ref = res.clone(), res.clone()
+    assert ops.norm_residual_norm(x, first=None, residual=r_got, want_output=False) is None
+    ref.norm_residual_norm(x, first=None, residual=r_ref, want_output=False)
+    assert_close(r_got, r_ref, torch.float32, what="plain add")
+    # gathered rows
+    idx = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    assert_close(ops.norm_residual_norm(res, second=w2, out_dtype=dtype, row_index=idx),
+                 ref.norm_residual_norm(res, second=w2, out_dtype=dtype, row_index=idx), dtype, what="gathered")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gated_activation_softcap_add_convert(dtype):
+    gu = rnd((5, 2 * 112), dtype, 5, 2.0)
+    for act in ("gelu_pytorch_tanh", "silu"):
+        assert_close(ops.gated_activation(gu, act), ref.gated_activation(gu, act), dtype, what=act)
+    z = rnd((3, 131), torch.float32, 6, 40.0)
+    assert_close(ops.softcap_(z.clone(), 30.0), ref.softcap_(z.clone(), 30.0), torch.float32, what="softcap")
+    res = rnd((5, 112), torch.float32, 7)
+    x = rnd((5, 112), dtype, 8)
+    assert_close(ops.residual_add_(res.clone(), x), ref.residual_add_(res.clone(), x), torch.float32, what="add")
+    idx = torch.tensor([4, 4, 1], dtype=torch.int32, device=DEV)
+    assert_close(ops.convert_rows(res, dtype, idx), ref.convert_rows(res, dtype, idx), dtype, what="convert")
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 131, 80), (7, 300, 257), (129, 65, 64), (64, 64, 16)])
+def test_gemm_f32_is_exact_float32(m, n, k):
+    x, w = rnd((m, k), torch.float32, 9), rnd((n, k), torch.float32, 10)
+    got = ops.linear(x, w)
+    assert_close(got, ref.linear(x, w), torch.float32, what="gemm_f32")
+    # a row's result does not depend on the other rows of the batch: bit-equal
+    alone = ops.linear(x[m // 2:m // 2 + 1].contiguous(), w)
+    assert torch.equal(alone[0], got[m // 2])
+
+
+def test_linear_bf16_float32_output():
+    x, w = rnd((5, 96), torch.bfloat16, 11), rnd((384, 96), torch.bfloat16, 12)
+    assert ops.linear(x, w, out_dtype=torch.float32).dtype is torch.float32
+    assert_close(ops.linear(x, w, out_dtype=torch.float32), ref.linear(x, w, torch.float32), torch.float32, what="head")
+    assert_close(ops.linear(x, w), ref.linear(x, w), torch.bfloat16, what="linear")
+
+
+# ------------------------------------------------------------------------------------------
+# position encoding, cache write and attention
+# ------------------------------------------------------------------------------------------
+
+class Case:
+    """A packed batch over a paged cache, built on the host like the engine builds it."""
+
+    def __init__(self, *, past, new, n_heads, n_kv_heads, head_dim, page_size, window, dtype, seed,
+                 shuffle_pages=True, max_context=None):
+        from rust_deeplearning_b200.cache.cache import ring_pages_for
+        self.n_heads, self.n_kv_heads, self.head_dim, self.window, self.dtype = n_heads, n_kv_heads, head_dim, window, dtype
+        self.page_size = page_size
+        n = len(past)
+        totals = [p + s for p, s in zip(past, new)]
+        max_context = max_context or max(totals)
+        ctx_pages = -(-max_context // page_size)
+        ring = ring_pages_for(window, page_size) if window else ctx_pages
+        self.ring_pages = min(ring, ctx_pages)
+        rng = np.random.default_rng(seed)
+        n_pages = n * self.ring_pages + 3
+        order = rng.permutation(n_pages) if shuffle_pages else np.arange(n_pages)
+        tables = np.zeros((n, self.ring_pages), dtype=np.int32)
+        for i in range(n):
+            tables[i] = order[i * self.ring_pages:(i + 1) * self.ring_pages]
+        T = sum(new)
+        tok_seq = np.concatenate([np.full(s, i) for i, s in enumerate(new)]).astype(np.int32)
+        tok_pos = np.concatenate([np.arange(p, p + s) for p, s in zip(past, new)]).astype(np.int32)
+        starts = np.concatenate([[0], np.cumsum(new)]).astype(np.int32)
+        tiles = [(i, q0) for i, s in enumerate(new) for q0 in range(0, s, 64)]
+        dev = lambda a: torch.from_numpy(np.asarray(a, dtype=np.int32)).to(DEV)
+        self.T, self.n = T, n
+        self.tok_seq, self.tok_pos, self.seq_start = dev(tok_seq), dev(tok_pos), dev(starts)
+        self.seq_past, self.seq_end = dev(past), dev(totals)
+        self.tile_seq, self.tile_q0 = dev([t[0] for t in tiles]), dev([t[1] for t in tiles])
+        self.n_tiles = len(tiles)
+        self.max_total = max(totals)
+        self.k = rnd((n_pages, n_kv_heads, page_size, head_dim), dtype, seed + 1)
+        self.v = rnd((n_pages, n_kv_heads, page_size, head_dim), dtype, seed + 2)
+        self.pages = ops.KVPages(self.k, self.v, dev(tables), page_size, self.ring_pages)
+        width = (n_heads + 2 * n_kv_heads) * head_dim
+        self.qkv = rnd((T, width), dtype, seed + 3)
+
+    def batch(self, keys_in_cache):
+        cached = self.seq_past if keys_in_cache == "past" else self.seq_end
+        max_keys = min(self.max_total, self.window) if self.window else self.max_total
+        return ops.AttentionBatch(self.T, self.n, self.tok_seq, self.tok_pos, self.seq_start, self.seq_past, cached,
+                                  self.tile_seq, self.tile_q0, self.n_tiles, max_keys)
+
+    def kw(self, scale=None, softcap=None):
+        return dict(n_heads=self.n_heads, n_kv_heads=self.n_kv_heads, head_dim=self.head_dim,
+                    score_scale=scale or 1.0 / math.sqrt(self.head_dim), softcap=softcap, window=self.window)
+
+    def new_kv(self):
+        q = self.n_heads * self.head_dim
+        return (self.qkv, q, q + self.n_kv_heads * self.head_dim)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("head_dim,rotary", [(16, 16), (48, 32), (256, 256)])
+def test_rope_and_cache_write(dtype, head_dim, rotary):
+    c = Case(past=[0, 5, 30], new=[7, 1, 40], n_heads=3, n_kv_heads=1, head_dim=head_dim, page_size=4,
+             window=8, dtype=dtype, seed=20)           # ring of 4 pages = 16 rows, wrapped by the third sequence
+    half = rotary // 2
+    ang = torch.arange(100, dtype=torch.float64)[:, None] / (50.0 ** (torch.arange(half, dtype=torch.float64) / half))
+    cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
+    q_got, q_ref = c.qkv.clone(), c.qkv.clone()
+    k_ref, v_ref = c.k.clone(), c.v.clone()
+    pages_ref = ops.KVPages(k_ref, v_ref, c.pages.tables, c.page_size, c.ring_pages)
+    ops.rope_cache(q_got, 3, 1, head_dim, tok_seq=c.tok_seq, tok_pos=c.tok_pos, cos=cos, sin=sin, rotary_dim=rotary,
+                   pages=c.pages, seq_end=c.seq_end)
+    ref.rope_cache(q_ref, 3, 1, head_dim, tok_seq=c.tok_seq, tok_pos=c.tok_pos, cos=cos, sin=sin, rotary_dim=rotary,
+                   pages=pages_ref, seq_end=c.seq_end)
+    assert_close(q_got, q_ref, dtype, rel=1.0, what="rotated rows")
+    assert_close(c.k, k_ref, dtype, rel=1.0, what="key cache")
+    assert_close(c.v, v_ref, dtype, rel=1.0, what="value cache")
+
+
+ATTN_SHAPES = [
+    # past, new, heads, kv heads, head_dim, page, window
+    dict(past=[0], new=[1], n_heads=1, n_kv_heads=1, head_dim=16, page_size=64, window=None),
+    dict(past=[0, 0, 0], new=[5, 129, 70], n_heads=4, n_kv_heads=2, head_dim=32, page_size=16, window=None),
+    dict(past=[0, 0], new=[200, 33], n_heads=6, n_kv_heads=1, head_dim=48, page_size=8, window=24),
+    dict(past=[90, 3, 0], new=[70, 130, 1], n_heads=2, n_kv_heads=2, head_dim=80, page_size=16, window=50),
+    dict(past=[10, 0], new=[65, 64], n_heads=8, n_kv_heads=4, head_dim=256, page_size=64, window=None),
+    dict(past=[0], new=[150], n_heads=3, n_kv_heads=3, head_dim=128, page_size=32, window=100),
+]
+
+
+@pytest.mark.parametrize("shape", ATTN_SHAPES)
+@pytest.mark.parametrize("dtype,kind", [(torch.float32, "plain"), (torch.bfloat16, "plain"), (torch.bfloat16, "prefill")])
+def test_attention_over_cache_and_new_rows(shape, dtype, kind):
+    c = Case(dtype=dtype, seed=30, **shape)
+    b = c.batch("past")
+    for softcap in (None, 5.0):
+        got = ops.attention(c.qkv, b, c.pages, new_kv=c.new_kv(), kind=kind, **c.kw(softcap=softcap))
+        want = ref.attention(c.qkv, b, c.pages, new_kv=c.new_kv(), **c.kw(softcap=softcap))
+        assert_close(got, want, dtype, rel=6.0, what=f"{kind} softcap={softcap}")
+
+
+DECODE_SHAPES = [
+    dict(past=[0, 63, 64, 700], n_heads=8, n_kv_heads=4, head_dim=256, page_size=64, window=None),
+    dict(past=[5, 1000, 300], n_heads=6, n_kv_heads=1, head_dim=32, page_size=16, window=None),
+    dict(past=[2000, 17, 130], n_heads=4, n_kv_heads=2, head_dim=128, page_size=64, window=100),
+    dict(past=[511, 512], n_heads=3, n_kv_heads=3, head_dim=48, page_size=32, window=512),
+    dict(past=[77], n_heads=16, n_kv_heads=2, head_dim=80, page_size=64, window=33),
+]
+
+
+@pytest.mark.parametrize("shape", DECODE_SHAPES)
+@pytest.mark.parametrize("keys_per_split", [None, "one_page", "eight_pages"])
+def test_decode_attention_over_cache(shape, keys_per_split):
+    shape = dict(shape)
+    past = shape.pop("past")
+    c = Case(past=past, new=[1] * len(past), dtype=torch.bfloat16, seed=40, **shape)
+    b = c.batch("all")
+    ks = {None: None, "one_page": c.page_size, "eight_pages": 8 * c.page_size}[keys_per_split]
+    for softcap in (None, 7.0):
+        got = ops.attention(c.qkv, b, c.pages, kind="decode", keys_per_split=ks, **c.kw(softcap=softcap))
+        want = ref.attention(c.qkv, b, c.pages, **c.kw(softcap=softcap))
+        assert_close(got, want, torch.bfloat16, rel=6.0, what=f"decode softcap={softcap}")
+        plain = ops.attention(c.qkv, b, c.pages, kind="plain", **c.kw(softcap=softcap))
+        assert_close(plain, want, torch.bfloat16, rel=6.0, what="plain on the same case")
+
+
+def test_attention_finds_one_far_key():
+    """One key among a thousand is made to dominate: the output must be that key's value row.
+    Shows a wrong page, a missed split or a window edge that random data would average away."""
+    for window, far in ((None, 3), (400, 1001 - 400), (400, 1001 - 401)):
+        c = Case(past=[1000], new=[1], n_heads=2, n_kv_heads=1, head_dim=64, page_size=64, window=window,
+                 dtype=torch.bfloat16, seed=50)
+        b = c.batch("all")
+        page, r = ref._cache_index(c.pages.tables[0], far, c.page_size, c.ring_pages)
+        c.qkv[0, :128] = 0.25
+        c.k[page, 0, r] = 8.0                       # score 128 against about 0 +- 4 elsewhere
+        want = ref.attention(c.qkv, b, c.pages, **c.kw(scale=1.0))
+        visible = window is None or 1000 - far < window
+        target = c.v[page, 0, r].double().cpu()
+        hit = (want[0, :64].double().cpu() - target).abs().max().item() < 1e-2
+        assert hit == visible
+        for kind in ("decode", "plain"):
+            got = ops.attention(c.qkv, b, c.pages, kind=kind, **c.kw(scale=1.0))
+            assert_close(got, want, torch.bfloat16, rel=6.0, what=f"{kind} window={window}")
+
+
+# ------------------------------------------------------------------------------------------
+# sampling
+# ------------------------------------------------------------------------------------------
+
+def test_uniform_matches_host():
+    from rust_deeplearning_b200.kernels import library
+    lib = library.load()
+    for seed, stream, step in [(0, 0, 0), (1, 2, 3), (2**63 + 5, 77, 1000), (123456789, 2**40, 2**31)]:
+        assert lib.rdl_sampling_uniform(seed, stream, step) == np.float32(uniform_for(seed, stream, step))
+
+
+@pytest.mark.parametrize("vocab", [131, 256000])
+def test_sampling(vocab):
+    rows = 5
+    logits = rnd((rows, vocab), torch.float32, 60, 3.0)
+    logits[1, 7] = logits[1, 100] = logits[1].max() + 1.0          # a tie: the first maximum wins
+    got = ops.sample(logits, temperature=0.0)
+    assert got.tolist() == ref.sample(logits, temperature=0.0).tolist()
+    assert got[1].item() == 7
+    stream = torch.arange(rows, dtype=torch.int64, device=DEV) + 10
+    for step in range(3):
+        steps = torch.full((rows,), step, dtype=torch.int32, device=DEV)
+        hist = torch.randint(0, vocab, (rows * 6,), dtype=torch.int32, device=DEV)
+        starts = torch.arange(0, rows * 6 + 1, 6, dtype=torch.int32, device=DEV)
+        for kw in (dict(), dict(top_k=7), dict(top_p=0.6), dict(top_k=50, top_p=0.9, repetition_penalty=1.3)):
+            args = dict(temperature=0.8, seed=99, row_stream=stream, row_step=steps, history=hist, history_start=starts, **kw)
+            got = ops.sample(logits, **args).tolist()
+            want = ref.sample(logits, **args).tolist()
+            assert got == want, (kw, step, got, want)

@@ -1,0 +1,123 @@
+"""bin/trace_run driven as a user drives it: steps on standard input, logits in files.  The same
+requests are replayed whole, with the last 32 tokens one by one, and in batches of unequal lengths
+whose shorter requests end earlier (one batch after another on a cache that only holds one batch,
+so slots and pages are used again); every written position is compared with the plain implementation."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import model_helpers as mh
+import tiny_configs
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TRACE_RUN = os.path.join(ROOT, "bin", "trace_run")
+
+
+def replay(name, dtype, steps, max_tokens, out_dir):
+    """Feed `steps` one at a time, waiting for `done <step>` after each, as the protocol asks."""
+    proc = subprocess.Popen([sys.executable, TRACE_RUN, "--model", mh.model_folder(name), "--dtype", dtype,
+                             "--out", out_dir, "--max-tokens", str(max_tokens)],
+                            stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
+    try:
+        for s in steps:
+            proc.stdin.write(json.dumps(s) + "\n")
+            proc.stdin.flush()
+            line = proc.stdout.readline().strip()
+            assert line == f"done {s['step']}", f"expected 'done {s['step']}', got {line!r}"
+        proc.stdin.close()
+        assert proc.wait(timeout=120) == 0
+    finally:
+        if proc.poll() is None:
+            proc.kill()
+    V = tiny_configs.config(name)[0]["vocab_size"]
+    out = {}
+    for s in steps:
+        n = sum(len(e.get("want", [])) for e in s["entries"])
+        path = os.path.join(out_dir, f"{s['step']}.f32")
+        if n:
+            out[s["step"]] = np.fromfile(path, dtype="<f4").reshape(n, V)
+        else:
+            assert not os.path.exists(path)
+    return out
+
+
+def check(name, dtype, steps, outputs, seqs):
+    """Every wanted place of every step against the plain logits of its request at its position."""
+    pos = {rid: 0 for rid in seqs}
+    for s in steps:
+        rows = []
+        for e in s["entries"]:
+            want = mh.plain_logits(name, seqs[e["id"]])
+            rows += [want[pos[e["id"]] + w] for w in e.get("want", [])]
+            pos[e["id"]] += len(e["tokens"])
+        if rows:
+            got = outputs[s["step"]]
+            tol = mh.tolerance(dtype, np.stack(rows))
+            err = np.abs(got.astype(np.float64) - np.stack(rows)).max(axis=1)
+            assert np.isfinite(got).all()
+            assert err.max() <= tol, f"step {s['step']}: error {err.max():.3e} > {tol:.3e}, first bad row {int(np.argmax(err > tol))}"
+
+
+def requests(name):
+    V = tiny_configs.config(name)[0]["vocab_size"]
+    lens = {"a": 70, "b": 33, "c": 101, "d": 40, "e": 65}
+    return {rid: mh.prompt(500 + i, n, V) for i, (rid, n) in enumerate(lens.items())}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_replay_whole_then_last_32_one_by_one(tmp_path, name, dtype):
+    seqs = requests(name)
+    steps, k = [], 0
+    for rid, ids in seqs.items():                    # each request alone and whole
+        steps.append({"step": k, "entries": [{"id": rid + "w", "tokens": ids, "want": list(range(len(ids)))}],
+                      "end": [rid + "w"]})
+        k += 1
+    for rid, ids in seqs.items():                    # each request alone, the last 32 tokens one by one
+        cut = len(ids) - 32
+        steps.append({"step": k, "entries": [{"id": rid, "tokens": ids[:cut], "want": [0, cut - 1]}], "end": []})
+        k += 1
+        for t in range(cut, len(ids)):
+            steps.append({"step": k, "entries": [{"id": rid, "tokens": [ids[t]], "want": [0]}],
+                          "end": [rid] if t == len(ids) - 1 else []})
+            k += 1
+    all_seqs = dict(seqs)
+    all_seqs.update({rid + "w": ids for rid, ids in seqs.items()})
+    out = replay(name, dtype, steps, max_tokens=128, out_dir=str(tmp_path))   # one request of 101 tokens at a time
+    check(name, dtype, steps, out, all_seqs)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_replay_unequal_batches_one_after_another(tmp_path, name, dtype):
+    seqs = requests(name)
+    prompt_len = {"a": 50, "b": 1, "c": 90, "d": 17, "e": 64}
+    steps, k = [], 0
+    for members in (["a", "b", "c"], ["d", "e"], ["c", "a", "e", "b"][:3], ["b", "d"]):
+        ids = {m: seqs[m] for m in members}
+        pos = {m: prompt_len[m] for m in members}
+        ending = [m for m in members if pos[m] == len(ids[m])]
+        steps.append({"step": k, "entries": [{"id": f"{m}{k}", "tokens": ids[m][:pos[m]], "want": [pos[m] - 1]}
+                                             for m in members], "end": [f"{m}{k}" for m in ending]})
+        names = {m: f"{m}{k}" for m in members}
+        k += 1
+        live = [m for m in members if m not in ending]
+        while live:
+            ending = [m for m in live if pos[m] + 1 == len(ids[m])]
+            steps.append({"step": k, "entries": [{"id": names[m], "tokens": [ids[m][pos[m]]],
+                                                  "want": [0] if (pos[m] % 3 or m in ending) else []} for m in live],
+                          "end": [names[m] for m in ending]})
+            k += 1
+            for m in live:
+                pos[m] += 1
+            live = [m for m in live if m not in ending]
+        for m in members:
+            seqs[names[m]] = ids[m]
+    # the largest batch holds 128 + 64 + 128 positions (rounded up to 64): the cache fits one batch only
+    out = replay(name, dtype, steps, max_tokens=320, out_dir=str(tmp_path))
+    check(name, dtype, steps, out, seqs)
