@@ -19,6 +19,7 @@ import numpy as np
 import torch
 
 from ..cache.cache import Cache, CacheError
+from ..kernels import library
 from .batch import BatchLayout, StepBatch, batch_from_buffer, count_tiles, fill_batch
 
 
@@ -39,6 +40,7 @@ class _Graph:
         self.batch: Optional[StepBatch] = None
         self.logits: Optional[torch.Tensor] = None
         self.scratch: Dict[str, torch.Tensor] = {}
+        self.kernels = 0          # kernels of the library inside the captured graph
 
 
 class Engine:
@@ -91,6 +93,9 @@ class Engine:
             want = [list(range(l)) for l in lens]
         elif len(want) != n:
             raise StepError("`want` must name places for every sequence")
+        for i, (w, l) in enumerate(zip(want, lens)):
+            if any(not 0 <= int(x) < l for x in w):
+                raise StepError(f"sequence {i}: a wanted place is outside its {l} new tokens")
         flat = np.concatenate([np.asarray(t, dtype=np.int64).reshape(-1) for t in tokens])
         if flat.min() < 0 or flat.max() >= self.model.vocab_size:
             raise StepError(f"token id outside the vocabulary of {self.model.vocab_size}")
@@ -161,22 +166,24 @@ class Engine:
         if g.graph is None and g.seen >= 2:
             # the first step of a shape ran eagerly (and warmed the libraries up); capture now
             graph = torch.cuda.CUDAGraph()
+            before = library.launch_count
             with torch.cuda.graph(graph):
                 g.logits = self.model.forward(g.batch, self.cache)
+            g.kernels = library.launch_count - before     # captured, not run
+            library.launch_count = before
             g.graph = graph
         if g.graph is not None:
             g.graph.replay()
+            library.launch_count += g.kernels
             self.graph_replays += 1
             logits = g.logits
         else:
             logits = self.model.forward(g.batch, self.cache)
             self.eager_steps += 1
-        picked = [i for i, w in enumerate(want) if len(w)]
         for i, w in enumerate(want):
             if any(x != 0 for x in w):
                 raise StepError(f"sequence {i} brings one token; only place 0 can be wanted")
-        if len(picked) == n == n_pad:
-            return logits
+        picked = [i for i, w in enumerate(want) for _ in w]
         if picked == list(range(len(picked))):
             return logits[:len(picked)]
         return logits[torch.tensor(picked, dtype=torch.long, device=self.device)]

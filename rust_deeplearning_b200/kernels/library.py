@@ -216,6 +216,12 @@ class KernelError(RuntimeError):
     """A kernel launcher refused its arguments or the launch failed."""
 
 
-def check(status: int):
+launch_count = 0   # kernels of this library launched (or captured into a graph) so far
+
+
+def check(status: int, kernels: int = 1):
+    """Raise if a launcher refused or failed; otherwise count its kernels."""
+    global launch_count
     if status != 0:
         raise KernelError(load().rdl_last_error().decode(errors="replace"))
+    launch_count += kernels

@@ -312,7 +312,7 @@ def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n
         buf = scratch(need) if scratch is not None else torch.empty(-(-need // 4), dtype=torch.float32, device=q.device)
         _need(buf.dtype is torch.float32 and buf.numel() * 4 >= need, "attention: decode scratch too small")
         a.scratch, a.scratch_bytes = buf.data_ptr(), buf.numel() * 4
-        library.check(lib.rdl_attention_decode(ctypes.byref(a), _stream(q)))
+        library.check(lib.rdl_attention_decode(ctypes.byref(a), _stream(q)), kernels=2)
     else:
         raise KernelError(f"attention: unknown kind '{kind}'")
     return out
