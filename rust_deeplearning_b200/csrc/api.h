@@ -10,7 +10,7 @@ extern "C" {
 #define RDL_ACT_GELU_TANH 0
 #define RDL_ACT_SILU 1
 
-#define RDL_ABI_VERSION 1
+#define RDL_ABI_VERSION 3
 
 const char* rdl_last_error(void);
 int rdl_abi_version(void);
@@ -38,12 +38,15 @@ typedef struct {
     // decode kernel: keys per split, splits launched per (token, kv head), float scratch
     int keys_per_split, max_splits;
     void* scratch; long long scratch_bytes;
+    long long counter_bytes;   // size of the counter area at the start of scratch (rdl_attention_decode_counter_bytes)
+    int* status;               // optional: set non-zero when a kernel gives up on a bounded wait
 } AttentionArgs;
 
 int rdl_attention_plain(const AttentionArgs* a, void* stream);
 int rdl_attention_prefill(const AttentionArgs* a, void* stream);
 int rdl_attention_decode(const AttentionArgs* a, void* stream);
-long long rdl_attention_decode_scratch_bytes(int n_tokens, int n_heads, int head_dim, int max_splits);
+long long rdl_attention_decode_counter_bytes(int n_tokens, int n_kv_heads);
+long long rdl_attention_decode_scratch_bytes(int n_tokens, int n_heads, int n_kv_heads, int head_dim, int max_splits);
 
 int rdl_embed_rows(void* out_f32, const void* table, int table_dtype, const int* ids, float scale,
                    int n_rows, int hidden, int vocab, int* status, void* stream);
@@ -65,6 +68,12 @@ int rdl_rope_cache(void* qkv, int dtype, int n_tokens, int n_heads, int n_kv_hea
 
 // out[m, n] = sum_k x[m, k] * w[n, k], all float, plain FMA in a fixed order of k
 int rdl_gemm_f32(void* out, const void* x, const void* w, int m, int n, int k, void* stream);
+
+// out[m, n] = epilogue(sum_k x[m, k] * w[n, k]) for m <= 16, bfloat16 operands, float accumulation.
+// gated: w is [2 n, k] (gate rows, then up rows) and the result is act(gate) * up.
+// softcap > 0: cap * tanh(v / cap).  out_dtype: RDL_F32 or RDL_BF16.
+int rdl_gemm_skinny(void* out, int out_dtype, const void* x, const void* w, int m, int n, int k,
+                    int gated, int activation, float softcap, void* stream);
 
 // sampling over float logits [rows, vocab]
 typedef struct {

@@ -97,11 +97,113 @@ __global__ void norm_residual_norm_kernel(NormArgs a) {
     }
 }
 
+// The same operation with the row held in registers: every load of a row is issued before the
+// first reduction, so the kernel's critical path is one trip to memory and two block sums.  Used
+// when hidden is a multiple of 4 and at most 256 * 4 * ITER.
+__device__ __forceinline__ float4 load4(const void* p, long long i, int dtype) {
+    if (dtype == RDL_BF16) {
+        const uint2 raw = *reinterpret_cast<const uint2*>((const __nv_bfloat16*)p + i);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    return *reinterpret_cast<const float4*>((const float*)p + i);
+}
+__device__ __forceinline__ void store4(void* p, long long i, int dtype, float4 v) {
+    if (dtype == RDL_BF16) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<uint32_t*>(&a);
+        raw.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>((__nv_bfloat16*)p + i) = raw;
+    } else {
+        *reinterpret_cast<float4*>((float*)p + i) = v;
+    }
+}
+
+template <int ITER>
+__global__ void __launch_bounds__(256) norm_residual_norm_vec_kernel(NormArgs a) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const int H = a.hidden;
+    const long long xin = (long long)(a.row_index ? a.row_index[r] : r) * H;
+    const long long out = (long long)r * H;
+    float4 xv[ITER], rv[ITER], w1v[ITER], w2v[ITER];
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < ITER; ++i) {
+        const int j = (i * 256 + threadIdx.x) * 4;
+        const bool on = j < H;
+        xv[i] = on ? load4(a.x, xin + j, a.x_dtype) : zero;
+        rv[i] = (on && a.res) ? *reinterpret_cast<const float4*>(a.res + out + j) : zero;
+        w1v[i] = (on && a.w1) ? load4(a.w1, j, a.w1_dtype) : zero;
+        w2v[i] = (on && a.w2 && a.y) ? load4(a.w2, j, a.w2_dtype) : zero;
+    }
+    if (a.w1) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < ITER; ++i) ss += xv[i].x * xv[i].x + xv[i].y * xv[i].y + xv[i].z * xv[i].z + xv[i].w * xv[i].w;
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)H + a.eps1);
+#pragma unroll
+        for (int i = 0; i < ITER; ++i) {
+            xv[i].x = xv[i].x * inv * (w1v[i].x + a.off1);
+            xv[i].y = xv[i].y * inv * (w1v[i].y + a.off1);
+            xv[i].z = xv[i].z * inv * (w1v[i].z + a.off1);
+            xv[i].w = xv[i].w * inv * (w1v[i].w + a.off1);
+        }
+    }
+    if (a.res) {
+#pragma unroll
+        for (int i = 0; i < ITER; ++i) {
+            const int j = (i * 256 + threadIdx.x) * 4;
+            xv[i].x += rv[i].x; xv[i].y += rv[i].y; xv[i].z += rv[i].z; xv[i].w += rv[i].w;
+            if (j < H) *reinterpret_cast<float4*>(a.res + out + j) = xv[i];
+        }
+    }
+    if (!a.y) return;
+    float inv2 = 1.f;
+    if (a.w2) {
+        float s2 = 0.f;
+#pragma unroll
+        for (int i = 0; i < ITER; ++i) s2 += xv[i].x * xv[i].x + xv[i].y * xv[i].y + xv[i].z * xv[i].z + xv[i].w * xv[i].w;
+        s2 = block_sum(s2, scratch);
+        inv2 = 1.0f / sqrtf(s2 / (float)H + a.eps2);
+    }
+#pragma unroll
+    for (int i = 0; i < ITER; ++i) {
+        const int j = (i * 256 + threadIdx.x) * 4;
+        if (j >= H) continue;
+        float4 v = xv[i];
+        if (a.w2) {
+            v.x = v.x * inv2 * (w2v[i].x + a.off2);
+            v.y = v.y * inv2 * (w2v[i].y + a.off2);
+            v.z = v.z * inv2 * (w2v[i].z + a.off2);
+            v.w = v.w * inv2 * (w2v[i].w + a.off2);
+        }
+        store4(a.y, out + j, a.y_dtype, v);
+    }
+}
+
+static bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
 extern "C" int rdl_norm_residual_norm(const void* x, int x_dtype, const int* row_index,
                                       const void* w1, int w1_dtype, float eps1, float off1,
                                       void* res_f32,
                                       const void* w2, int w2_dtype, float eps2, float off2,
                                       void* y, int y_dtype, int n_rows, int hidden, void* stream) {
+    if (hidden > 0 && hidden % 4 == 0 && hidden <= 8192 && n_rows > 0 && rdl_valid_dtype(x_dtype) && rdl_valid_dtype(y_dtype) &&
+        (!w1 || rdl_valid_dtype(w1_dtype)) && (!w2 || rdl_valid_dtype(w2_dtype)) && !(row_index && res_f32) && (y || res_f32) &&
+        aligned16(x) && aligned16(res_f32) && aligned16(w1) && aligned16(w2) && aligned16(y)) {
+        NormArgs a{x, x_dtype, row_index, w1, w1_dtype, eps1, off1, (float*)res_f32, w2, w2_dtype, eps2, off2, y, y_dtype, hidden};
+        cudaStream_t st = (cudaStream_t)stream;
+        if (hidden <= 1024) norm_residual_norm_vec_kernel<1><<<n_rows, 256, 0, st>>>(a);
+        else if (hidden <= 2048) norm_residual_norm_vec_kernel<2><<<n_rows, 256, 0, st>>>(a);
+        else if (hidden <= 4096) norm_residual_norm_vec_kernel<4><<<n_rows, 256, 0, st>>>(a);
+        else norm_residual_norm_vec_kernel<8><<<n_rows, 256, 0, st>>>(a);
+        RDL_CHECK_LAUNCH("norm_residual_norm");
+        return 0;
+    }
     RDL_REQUIRE(rdl_valid_dtype(x_dtype) && rdl_valid_dtype(y_dtype), "norm: bad dtype");
     RDL_REQUIRE(!w1 || rdl_valid_dtype(w1_dtype), "norm: bad dtype of the first weight");
     RDL_REQUIRE(!w2 || rdl_valid_dtype(w2_dtype), "norm: bad dtype of the second weight");

@@ -1,0 +1,175 @@
+// Matrix product for few rows (decode): out[m, n] = sum_k x[m, k] * w[n, k] with m <= 16.
+// The weight matrix is streamed from HBM exactly once with 16-byte loads straight into
+// tensor-core fragments; the few activation rows come through L1/L2.  bfloat16 operands, float
+// accumulation (mma.sync m16n8k16: 16 weight rows x 8 activation rows per instruction).
+//
+// One block owns 16 weight rows (and, for the gated form, the 16 rows of the second matrix with
+// the same indices); its warps split K between them in interleaved chunks of 128 and their
+// partial sums are added in warp order through shared memory.
+//
+// Epilogues: plain store (bfloat16 or float), cap * tanh(v / cap) (the output head), and
+// act(gate) * up for a row-concatenated [gate; up] matrix (the feed-forward), all in float.
+// (y = x W^T, W [out, in]: rustml/nn/main/src/core/linear.rs:12-15; the gated form and the
+// activation: rustml/nn/main/src/core/feed_forward.rs:151-161.)
+//
+// The k index inside a 32-wide step is permuted identically for both operands (a lane's 16
+// bytes feed two instructions), which leaves every dot product unchanged.
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+
+constexpr int ROWS = 16;        // weight rows per block
+constexpr int KCHUNK = 128;     // k per warp iteration: 4 steps of 32
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// streaming load: weights are read once, keep them out of L1
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+    return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+}
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
+
+struct SkinnyArgs {
+    const __nv_bfloat16* x;     // [M, K]
+    const __nv_bfloat16* w;     // [N, K] (gated: [2 * N, K], gate rows first)
+    void* out;                  // [M, N]
+    int M, N, K;
+    int out_dtype;              // RDL_F32 / RDL_BF16
+    int gated;                  // 0: plain, 1: act(gate) * up
+    int activation;
+    float softcap;              // > 0: cap * tanh(v / cap)
+};
+
+// NT: activation row tiles of 8 (M <= 8 * NT).  WARPS: warps that split K.  GATED: two weight streams.
+template <int NT, int WARPS, bool GATED>
+__global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(SkinnyArgs a) {
+    constexpr int NS = GATED ? 2 : 1;
+    __shared__ float partial[WARPS][NS][NT][ROWS * 8];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * ROWS;
+    const int K = a.K;
+    const bool row0_ok = n0 + g < a.N, row1_ok = n0 + g + 8 < a.N;
+    const __nv_bfloat16* wrow[NS][2];
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+        const long long base = (long long)(s * a.N + n0 + g) * K;
+        wrow[s][0] = a.w + base;
+        wrow[s][1] = a.w + base + 8LL * K;
+    }
+    const __nv_bfloat16* xrow[NT];
+    bool x_ok[NT];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+        x_ok[i] = i * 8 + g < a.M;
+        xrow[i] = a.x + (long long)(i * 8 + g) * K;
+    }
+    float acc[NS][NT][4];
+#pragma unroll
+    for (int s = 0; s < NS; ++s)
+#pragma unroll
+        for (int i = 0; i < NT; ++i) acc[s][i][0] = acc[s][i][1] = acc[s][i][2] = acc[s][i][3] = 0.f;
+
+    const uint4 zero4 = make_uint4(0, 0, 0, 0);
+    for (int kc = warp * KCHUNK; kc < K; kc += WARPS * KCHUNK) {
+        uint4 wa[NS][4][2], xb[NT][4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int k = kc + u * 32 + t * 8;
+            const bool k_ok = k < K;      // K is a multiple of 8: a 16-byte load is whole or absent
+#pragma unroll
+            for (int s = 0; s < NS; ++s) {
+                wa[s][u][0] = (k_ok && row0_ok) ? ld_stream(wrow[s][0] + k) : zero4;
+                wa[s][u][1] = (k_ok && row1_ok) ? ld_stream(wrow[s][1] + k) : zero4;
+            }
+#pragma unroll
+            for (int i = 0; i < NT; ++i)
+                xb[i][u] = (k_ok && x_ok[i]) ? __ldg(reinterpret_cast<const uint4*>(xrow[i] + k)) : zero4;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int s = 0; s < NS; ++s)
+#pragma unroll
+                for (int i = 0; i < NT; ++i) {
+                    mma_bf16(acc[s][i], wa[s][u][0].x, wa[s][u][1].x, wa[s][u][0].y, wa[s][u][1].y, xb[i][u].x, xb[i][u].y);
+                    mma_bf16(acc[s][i], wa[s][u][0].z, wa[s][u][1].z, wa[s][u][0].w, wa[s][u][1].w, xb[i][u].z, xb[i][u].w);
+                }
+    }
+    // accumulator element e of a lane: weight row g + 8 * (e >> 1), activation row 2 t + (e & 1)
+#pragma unroll
+    for (int s = 0; s < NS; ++s)
+#pragma unroll
+        for (int i = 0; i < NT; ++i)
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                partial[warp][s][i][(2 * t + (e & 1)) * ROWS + g + 8 * (e >> 1)] = acc[s][i][e];
+    __syncthreads();
+    // thread -> (activation row, weight row): 16 consecutive threads write 16 consecutive outputs
+    for (int idx = threadIdx.x; idx < NT * 8 * ROWS; idx += WARPS * 32) {
+        const int m = idx / ROWS, r = idx - m * ROWS;
+        const int n = n0 + r;
+        if (m >= a.M || n >= a.N) continue;
+        const int i = m >> 3, slot = (m & 7) * ROWS + r;
+        float v[NS];
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+            float sum = 0.f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) sum += partial[w][s][i][slot];
+            v[s] = sum;
+        }
+        float y = v[0];
+        if (GATED) y = (a.activation == RDL_ACT_GELU_TANH ? gelu_tanh(v[0]) : silu(v[0])) * v[NS - 1];
+        if (a.softcap > 0.f) y = a.softcap * tanhf(y / a.softcap);
+        rdl_store(a.out, (long long)m * a.N + n, a.out_dtype, y);
+    }
+}
+
+template <int NT, int WARPS>
+void launch(const SkinnyArgs& a, cudaStream_t st) {
+    const int blocks = (a.N + ROWS - 1) / ROWS;
+    if (a.gated)
+        gemm_skinny_kernel<NT, WARPS, true><<<blocks, WARPS * 32, 0, st>>>(a);
+    else
+        gemm_skinny_kernel<NT, WARPS, false><<<blocks, WARPS * 32, 0, st>>>(a);
+}
+
+}  // namespace
+
+extern "C" int rdl_gemm_skinny(void* out, int out_dtype, const void* x, const void* w, int m, int n, int k,
+                               int gated, int activation, float softcap, void* stream) {
+    RDL_REQUIRE(out && x && w, "gemm_skinny: missing operand");
+    RDL_REQUIRE(rdl_valid_dtype(out_dtype), "gemm_skinny: bad output dtype %d", out_dtype);
+    RDL_REQUIRE(m >= 0 && m <= 16, "gemm_skinny: %d rows, at most 16 are supported", m);
+    RDL_REQUIRE(n > 0 && k > 0 && k % 8 == 0, "gemm_skinny: n=%d, k=%d; k must be a multiple of 8", n, k);
+    RDL_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0, "gemm_skinny: operands must start on 16-byte boundaries");
+    RDL_REQUIRE(!gated || activation == RDL_ACT_GELU_TANH || activation == RDL_ACT_SILU, "gemm_skinny: unknown activation %d", activation);
+    RDL_REQUIRE(softcap >= 0.f, "gemm_skinny: soft-cap must not be negative");
+    if (m == 0) return 0;
+    SkinnyArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, out, m, n, k, out_dtype, gated, activation, softcap};
+    cudaStream_t st = (cudaStream_t)stream;
+    // few blocks (a narrow output): more warps per block keep enough loads in flight
+    const int blocks = (n + ROWS - 1) / ROWS;
+    const bool wide = blocks >= 2 * 148 || k < 8 * KCHUNK;
+    if (m <= 8) {
+        if (wide) launch<1, 4>(a, st); else launch<1, 8>(a, st);
+    } else {
+        if (wide) launch<2, 4>(a, st); else launch<2, 8>(a, st);
+    }
+    RDL_CHECK_LAUNCH("gemm_skinny");
+    return 0;
+}

@@ -81,6 +81,7 @@ class StepBatch:
     new_kv: Dict[int, tuple] = field(default_factory=dict)   # run -> (packed rows, key column, value column) of this step
     cache_owner_of: Dict[int, int] = field(default_factory=dict)     # run -> run whose keys and values it reads
     shared_runs: frozenset = frozenset()                             # runs whose keys and values a later run reads
+    status: Optional[torch.Tensor] = None                            # int32 flag kernels set when they give up a wait
 
     def attention_batch(self, keys_in_cache: str, window: Optional[int] = None) -> AttentionBatch:
         """keys_in_cache: "past" - new keys are read from the step's packed rows;
@@ -91,9 +92,10 @@ class StepBatch:
                               cached, self.tile_seq, self.tile_q0, self.n_tiles, max_keys)
 
     def scratch_buffer(self, name: str, nbytes: int) -> torch.Tensor:
+        """A zero-initialised float32 buffer kept under `name`; its user leaves zero what must start at zero."""
         buf = self.scratch.get(name)
         if buf is None or buf.numel() * 4 < nbytes:
-            buf = torch.empty(-(-nbytes // 4), dtype=torch.float32, device=self.device)
+            buf = torch.zeros(-(-nbytes // 4), dtype=torch.float32, device=self.device)
             self.scratch[name] = buf
         return buf
 

@@ -125,6 +125,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], *, max_new_tokens: int = 
                 tokens = sampler.sample(logits, [seqs[j].request for j in live], [seqs[j].sampled for j in live],
                                         [seqs[j].history() for j in live] if need_history else None)
                 tokens = tokens.tolist()
+                engine.check_status()
                 nxt_live, feed = [], []
                 for j, tok in zip(live, tokens):
                     s = seqs[j]

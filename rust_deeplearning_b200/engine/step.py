@@ -61,6 +61,11 @@ class Engine:
         self._scratch: Dict[str, torch.Tensor] = {}
         self.graph_replays = 0
         self.eager_steps = 0
+        # kernels set this word when they give up a bounded wait; pinned host memory, so the host
+        # reads it without a device call (after any synchronising read of a step's result)
+        self.status = torch.zeros(1, dtype=torch.int32)
+        if self.device.type == "cuda":
+            self.status = self.status.pin_memory()
 
     # ---- sequences ----
     def new_sequence(self) -> int:
@@ -71,6 +76,13 @@ class Engine:
 
     def length(self, slot: int) -> int:
         return self.cache.length(slot)
+
+    def check_status(self):
+        """Raise if a kernel of an earlier, completed step reported a fault (call after a synchronising read)."""
+        code = int(self.status[0])
+        if code:
+            self.status[0] = 0
+            raise RuntimeError(f"a kernel reported fault {code} (1: token outside the vocabulary, 3: a copy did not complete)")
 
     # ---- the step ----
     def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
@@ -120,6 +132,7 @@ class Engine:
             self._upload(dev, host, layout.size)
             batch = batch_from_buffer(dev, layout, real_tokens=real_tokens, real_seqs=n, n_want=n_want, n_tiles=n_tiles,
                                       is_decode=is_decode, max_total_len=max(totals), scratch=self._scratch)
+            batch.status = self.status
             logits = self.model.forward(batch, self.cache)
             self.eager_steps += 1
         self.cache.advance(slots, lens)
@@ -156,6 +169,7 @@ class Engine:
             g.dev = torch.zeros(g.layout.size, dtype=torch.int32, device=self.device)
             g.batch = batch_from_buffer(g.dev, g.layout, real_tokens=n_pad, real_seqs=n_pad, n_want=n_pad, n_tiles=0,
                                         is_decode=True, max_total_len=len_bucket, scratch=g.scratch)
+            g.batch.status = self.status
         # logits are formed for every row of the padded batch; the wanted ones are picked afterwards
         all_rows = [[0]] * n
         host = self._host_buffer(g.layout.size)

@@ -62,6 +62,7 @@ def run(argv=None, stdin=None, stdout=None) -> int:
             logits = engine.step([slots[r] for r in ids], [e["tokens"] for e in entries], want)
             if sum(len(w) for w in want):
                 data = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
+                engine.check_status()
                 tmp = os.path.join(args.out, f"{step}.f32.tmp")
                 data.tofile(tmp)
                 os.replace(tmp, os.path.join(args.out, f"{step}.f32"))

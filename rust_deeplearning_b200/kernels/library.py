@@ -23,7 +23,7 @@ from concurrent.futures import ThreadPoolExecutor
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(_PKG, "csrc")
 LIB_NAME = "librdl_b200_kernels.so"
-ABI_VERSION = 1
+ABI_VERSION = 3
 
 # fast math is never enabled: the 32-bit path relies on exact tanhf/expf/sqrtf and plain FMA
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -154,6 +154,7 @@ class AttentionArgs(ctypes.Structure):
         ("tile_seq", ctypes.c_void_p), ("tile_q0", ctypes.c_void_p), ("n_tiles", ctypes.c_int),
         ("keys_per_split", ctypes.c_int), ("max_splits", ctypes.c_int),
         ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_longlong),
+        ("counter_bytes", ctypes.c_longlong), ("status", ctypes.c_void_p),
     ]
 
 
@@ -175,6 +176,7 @@ _SIGNATURES = {
     "rdl_convert_rows": [_P, _I, _P, _I, _P, _I, _I, _P],
     "rdl_rope_cache": [_P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P],
     "rdl_gemm_f32": [_P, _P, _P, _I, _I, _I, _P],
+    "rdl_gemm_skinny": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P],
     "rdl_sample": [_P, _P, _I, _I, ctypes.POINTER(SamplingArgs), _P, _P, _P, _P, _P, _P],
 }
 
@@ -203,7 +205,9 @@ def load():
             fn = getattr(lib, name)
             fn.argtypes = args
             fn.restype = ctypes.c_int
-        lib.rdl_attention_decode_scratch_bytes.argtypes = [_I, _I, _I, _I]
+        lib.rdl_attention_decode_scratch_bytes.argtypes = [_I, _I, _I, _I, _I]
+        lib.rdl_attention_decode_counter_bytes.argtypes = [_I, _I]
+        lib.rdl_attention_decode_counter_bytes.restype = _LL
         lib.rdl_attention_decode_scratch_bytes.restype = _LL
         lib.rdl_sampling_uniform.argtypes = [ctypes.c_ulonglong] * 3
         lib.rdl_sampling_uniform.restype = ctypes.c_float

@@ -149,27 +149,59 @@ def convert_rows(x: torch.Tensor, out_dtype: torch.dtype, row_index: Optional[to
 # matrix products
 # ------------------------------------------------------------------------------------------
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None):
-    """x [rows, in] times weight [out, in] transposed.
+SKINNY_MAX_ROWS = 16     # up to this many rows the library's own weight-streaming kernel runs
+
+
+def _skinny_ok(x, weight):
+    return (x.dtype is torch.bfloat16 and x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0
+            and x.is_contiguous() and weight.is_contiguous() and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+           softcap: Optional[float] = None):
+    """x [rows, in] times weight [out, in] transposed; optionally cap * tanh(. / cap) on the result.
 
     float32: the library's own FMA kernel (no tensor cores, no reduced-precision mode).
-    bfloat16: a library matrix product with float32 accumulation (cuBLAS through torch), where
-    the reference's engine calls a GEMM library as well."""
+    bfloat16, up to 16 rows (decode): the library's weight-streaming tensor-core kernel with the
+    soft-cap in its epilogue.  bfloat16, more rows: a library matrix product with float32
+    accumulation (cuBLAS through torch), where the reference's engine calls a GEMM library as well."""
     _need(x.dim() == 2 and weight.dim() == 2 and x.shape[1] == weight.shape[1],
           f"linear: shapes {tuple(x.shape)} and {tuple(weight.shape)} do not fit")
     _need(x.dtype is weight.dtype, f"linear: input is {x.dtype}, weight is {weight.dtype}")
     out_dtype = out_dtype or x.dtype
+    _need(softcap is None or out_dtype is torch.float32, "linear: the soft-cap is applied to float32 results")
     if x.dtype is torch.float32:
         _need(out_dtype is torch.float32, "linear: the 32-bit path writes float32")
         _dense(x, "x"); _dense(weight, "weight")
         out = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.float32, device=x.device)
         library.check(library.load().rdl_gemm_f32(_ptr(out), _ptr(x), _ptr(weight), x.shape[0], weight.shape[0],
                                                   x.shape[1], _stream(x)))
+    elif _skinny_ok(x, weight):
+        out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=x.device)
+        library.check(library.load().rdl_gemm_skinny(_ptr(out), _dtype_code(out), _ptr(x), _ptr(weight), x.shape[0],
+                                                     weight.shape[0], x.shape[1], 0, 0, float(softcap or 0.0), _stream(x)))
         return out
-    _need(x.is_cuda, "kernels run on CUDA tensors only; there is no CPU path")
-    if out_dtype is torch.float32:
-        return torch.mm(x, weight.t(), out_dtype=torch.float32)
-    return torch.mm(x, weight.t())
+    else:
+        _need(x.is_cuda, "kernels run on CUDA tensors only; there is no CPU path")
+        out = torch.mm(x, weight.t(), out_dtype=torch.float32) if out_dtype is torch.float32 else torch.mm(x, weight.t())
+    if softcap is not None:
+        softcap_(out, softcap)
+    return out
+
+
+def linear_gated(x: torch.Tensor, weight_gate_up: torch.Tensor, activation: str):
+    """act(x Wg^T) * (x Wu^T) for the row-concatenated matrix [Wg; Wu] ([2I, in]) -> [rows, I].
+    Up to 16 bfloat16 rows this is one kernel; otherwise a product and the gated activation kernel."""
+    _need(activation in ACTIVATIONS, f"unknown activation '{activation}', known: {sorted(ACTIVATIONS)}")
+    _need(weight_gate_up.shape[0] % 2 == 0, "linear_gated: the weight must hold gate rows and as many up rows")
+    if x.dtype is torch.bfloat16 and x.dtype is weight_gate_up.dtype and _skinny_ok(x, weight_gate_up):
+        inter = weight_gate_up.shape[0] // 2
+        out = torch.empty((x.shape[0], inter), dtype=x.dtype, device=x.device)
+        library.check(library.load().rdl_gemm_skinny(_ptr(out), _dtype_code(out), _ptr(x), _ptr(weight_gate_up),
+                                                     x.shape[0], inter, x.shape[1], 1, ACTIVATIONS[activation], 0.0,
+                                                     _stream(x)))
+        return out
+    return gated_activation(linear(x, weight_gate_up), activation)
 
 
 # ------------------------------------------------------------------------------------------
@@ -265,7 +297,7 @@ def choose_keys_per_split(n_tokens: int, n_kv_heads: int, max_keys: int, page_si
 def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n_heads: int, n_kv_heads: int,
               head_dim: int, score_scale: float, softcap: Optional[float], window: Optional[int],
               new_kv: Optional[Tuple[torch.Tensor, int, int]] = None, kind: str = "auto",
-              scratch=None, keys_per_split: Optional[int] = None):
+              scratch=None, keys_per_split: Optional[int] = None, status: Optional[torch.Tensor] = None):
     """Attention of the step's tokens over cache and new rows.
 
     q: [tokens, >= n_heads * head_dim] rows whose first n_heads * head_dim values are the (rotated)
@@ -274,7 +306,9 @@ def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n
     keys and the values start; needed when `b.seq_cached` says that new keys are not in the cache.
     kind: "plain" (float arithmetic, any dtype), "prefill" (bfloat16, tensor cores), "decode"
     (bfloat16, split keys; reads the cache only), or "auto".
-    scratch: callable(nbytes) -> float32 tensor, for the decode kernel's partial results.
+    scratch: callable(nbytes) -> zero-initialised float32 tensor that only this kernel writes, for
+    the decode kernel's counters and partial results.  status: int32 tensor that a kernel sets
+    non-zero when it gives up on a bounded wait.
     Returns [tokens, n_heads * head_dim] in the dtype of q."""
     _need(q.dim() == 2 and q.stride(1) == 1 and q.shape[1] >= n_heads * head_dim, "attention: bad query rows")
     T = q.shape[0]
@@ -308,10 +342,13 @@ def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n
         a.keys_per_split = ks
         # a run of max_keys positions can straddle one more split than its length suggests
         a.max_splits = (max(b.max_keys, 1) + ks - 1) // ks + 1
-        need = lib.rdl_attention_decode_scratch_bytes(b.n_tokens, n_heads, head_dim, a.max_splits)
-        buf = scratch(need) if scratch is not None else torch.empty(-(-need // 4), dtype=torch.float32, device=q.device)
+        need = lib.rdl_attention_decode_scratch_bytes(b.n_tokens, n_heads, n_kv_heads, head_dim, a.max_splits)
+        # the counters at the start of the scratch must be zero before a launch; the kernel leaves them so
+        buf = scratch(need) if scratch is not None else torch.zeros(-(-need // 4), dtype=torch.float32, device=q.device)
         _need(buf.dtype is torch.float32 and buf.numel() * 4 >= need, "attention: decode scratch too small")
         a.scratch, a.scratch_bytes = buf.data_ptr(), buf.numel() * 4
+        a.counter_bytes = lib.rdl_attention_decode_counter_bytes(b.n_tokens, n_kv_heads)
+        a.status = status.data_ptr() if status is not None else None
         library.check(lib.rdl_attention_decode(ctypes.byref(a), _stream(q)), kernels=2)
     else:
         raise KernelError(f"attention: unknown kind '{kind}'")

@@ -73,7 +73,7 @@ class Attention:
             if batch.is_decode or owner is None:
                 ab = batch.attention_batch("all", self.window)
                 kind = "decode" if (fast and batch.is_decode) else ("prefill" if fast and batch.n_tiles else "plain")
-                ctx = ops.attention(q, ab, pages, kind=kind, scratch=lambda n: batch.scratch_buffer("decode", n), **common)
+                ctx = ops.attention(q, ab, pages, kind=kind, scratch=lambda n: batch.scratch_buffer("decode", n), status=batch.status, **common)
             else:
                 rows, k_col, v_col = owner
                 ab = batch.attention_batch("past", self.window)
@@ -94,7 +94,7 @@ class Attention:
                                seq_end=batch.seq_end)
             ab = batch.attention_batch("all", self.window)
             ctx = ops.attention(qkv, ab, pages, kind="decode" if fast else "plain",
-                                scratch=lambda n: batch.scratch_buffer("decode", n), **common)
+                                scratch=lambda n: batch.scratch_buffer("decode", n), status=batch.status, **common)
         else:
             # rotate; attend over the cache (earlier steps) and the packed rows (this step); then write.
             # The write comes last because in a ring it may overwrite rows this step's early queries need.

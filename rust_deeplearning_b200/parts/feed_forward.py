@@ -25,8 +25,7 @@ class GatedMLP:
         self.w_down = w_down
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        gu = ops.linear(x, self.w_gate_up)
-        return ops.linear(ops.gated_activation(gu, self.activation), self.w_down)
+        return ops.linear(ops.linear_gated(x, self.w_gate_up, self.activation), self.w_down)
 
 
 def _build_gated_mlp(spec: PartSpec, ctx: BuildContext) -> GatedMLP:

@@ -47,10 +47,7 @@ class LinearHead:
         self.weight, self.softcap = weight, softcap
 
     def forward(self, n: torch.Tensor) -> torch.Tensor:
-        z = ops.linear(n, self.weight, out_dtype=torch.float32)
-        if self.softcap is not None:
-            ops.softcap_(z, self.softcap)
-        return z
+        return ops.linear(n, self.weight, out_dtype=torch.float32, softcap=self.softcap)
 
 
 register_part("head", "linear_head",

@@ -75,8 +75,15 @@ def convert_rows(x, out_dtype, row_index=None):
     return v.to(out_dtype)
 
 
-def linear(x, weight, out_dtype=None):
-    return (x.to(F64) @ weight.to(F64).t()).to(out_dtype or x.dtype)
+def linear(x, weight, out_dtype=None, softcap=None):
+    z = x.to(F64) @ weight.to(F64).t()
+    if softcap is not None:
+        z = softcap * torch.tanh(z / softcap)
+    return z.to(out_dtype or x.dtype)
+
+
+def linear_gated(x, weight_gate_up, activation):
+    return gated_activation(x.to(F64) @ weight_gate_up.to(F64).t(), activation).to(x.dtype)
 
 
 def _cache_index(table_row, pos, page_size, ring_pages):
@@ -112,7 +119,7 @@ def rope_cache(qkv, n_heads, n_kv_heads, head_dim, *, tok_seq, tok_pos, cos=None
 
 
 def attention(q, b, pages, *, n_heads, n_kv_heads, head_dim, score_scale, softcap, window, new_kv=None,
-              kind="auto", scratch=None, keys_per_split=None):
+              kind="auto", scratch=None, keys_per_split=None, status=None):
     T = q.shape[0]
     out = torch.zeros((T, n_heads * head_dim), dtype=q.dtype, device=q.device)
     group = n_heads // n_kv_heads
@@ -188,7 +195,7 @@ def sample(logits, *, temperature, top_k=None, top_p=None, repetition_penalty=No
 
 
 _NAMES = ["embed_rows", "norm_residual_norm", "gated_activation", "softcap_", "residual_add_", "convert_rows",
-          "linear", "rope_cache", "attention", "sample"]
+          "linear", "linear_gated", "rope_cache", "attention", "sample"]
 
 
 def install(monkeypatch):

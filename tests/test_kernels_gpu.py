@@ -46,7 +46,7 @@ def test_embed_rows(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("hidden", [80, 2304, 5000])
+@pytest.mark.parametrize("hidden", [80, 131, 2304, 5000, 10000])
 def test_norm_residual_norm(dtype, hidden):
     rows = 7
     x = rnd((rows, hidden), dtype, 1, 3.0)
@@ -101,6 +101,26 @@ def test_linear_bf16_float32_output():
     assert ops.linear(x, w, out_dtype=torch.float32).dtype is torch.float32
     assert_close(ops.linear(x, w, out_dtype=torch.float32), ref.linear(x, w, torch.float32), torch.float32, what="head")
     assert_close(ops.linear(x, w), ref.linear(x, w), torch.bfloat16, what="linear")
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("n,k", [(131, 80), (384, 96), (2304, 2048), (40, 1160), (16, 8)])
+def test_skinny_gemm(m, n, k):
+    """The weight-streaming kernel for few rows: plain, float32 output with soft-cap, and gated."""
+    x, w = rnd((m, k), torch.bfloat16, 13), rnd((n, k), torch.bfloat16, 14, 0.2)
+    assert ops._skinny_ok(x, w)
+    assert_close(ops.linear(x, w), ref.linear(x, w), torch.bfloat16, what="plain")
+    assert_close(ops.linear(x, w, out_dtype=torch.float32), ref.linear(x, w, torch.float32), torch.float32, what="float32 out")
+    assert_close(ops.linear(x, w, out_dtype=torch.float32, softcap=3.0), ref.linear(x, w, torch.float32, softcap=3.0),
+                 torch.float32, what="soft-cap")
+    wgu = rnd((2 * n, k), torch.bfloat16, 15, 0.2)
+    for act in ("gelu_pytorch_tanh", "silu"):
+        assert_close(ops.linear_gated(x, wgu, act), ref.linear_gated(x, wgu, act), torch.bfloat16, what=f"gated {act}")
+    # more rows than the kernel takes: the library product and the activation kernel give the same
+    x17 = rnd((17, k), torch.bfloat16, 16)
+    assert not ops._skinny_ok(x17, w)
+    assert_close(ops.linear_gated(x17, wgu, "gelu_pytorch_tanh"), ref.linear_gated(x17, wgu, "gelu_pytorch_tanh"),
+                 torch.bfloat16, what="gated, many rows")
 
 
 # ------------------------------------------------------------------------------------------
