@@ -17,8 +17,10 @@ Here
 * state of fixed size lives beside it, [runs in group][slot][*shape], zeroed when a slot
   is handed out.
 
-Freed slots and pages are reused; reads are bounded by the sequence's length, so stale rows
-of an earlier occupant are never read and nothing is cleared on free.
+Freed slots and pages are reused; what a sequence reads is bounded by its length, so stale rows
+of an earlier occupant never contribute and nothing is cleared on free.  (Kernels that copy whole
+pages may touch such rows, but give them the weight zero; storage starts zero-filled so that
+every row they touch holds finite numbers.)
 """
 from __future__ import annotations
 
@@ -110,8 +112,10 @@ class KVGroup:
         self.pool = PagePool(n_pages)
         self.pages: Dict[int, List[int]] = {}          # slot -> page list (ring entries in order of first use)
         shape = (len(runs), n_pages, requirement.n_kv_heads, page_size, requirement.head_dim)
-        self.k = torch.empty(shape, dtype=dtype, device=device) if allocate else None
-        self.v = torch.empty(shape, dtype=dtype, device=device) if allocate else None
+        # zero-filled: kernels that copy whole pages give rows beyond a sequence's length the weight 0,
+        # which needs those rows to hold finite numbers (never-written memory may not)
+        self.k = torch.zeros(shape, dtype=dtype, device=device) if allocate else None
+        self.v = torch.zeros(shape, dtype=dtype, device=device) if allocate else None
 
     def pages_needed(self, slot: int, length: int) -> int:
         want = min(-(-length // self.page_size), self.ring_pages)

@@ -48,18 +48,20 @@ __global__ void attention_plain_kernel(AttentionArgs a) {
         const T* kp = nullptr;
         const T* vp = nullptr;
         float s = -INFINITY;
+        int sw = -1;   // place of the row in its cache page (rows there are stored swizzled); -1: a packed new row
         if (valid) {
             if (j < cached) {
                 const long long off = rdl_cache_offset(table, j, a.page_size, a.ring_pages, a.n_kv_heads, g, hd);
                 kp = (const T*)a.k_cache + off;
                 vp = (const T*)a.v_cache + off;
+                sw = j % a.page_size;
             } else {
                 const long long off = (long long)(new_row0 + j) * a.kv_stride + (long long)g * hd;
                 kp = (const T*)a.k_new + off;
                 vp = (const T*)a.v_new + off;
             }
             float d = 0.f;
-            for (int i = 0; i < hd; ++i) d = fmaf(to_float(q[i]), to_float(kp[i]), d);
+            for (int i = 0; i < hd; ++i) d = fmaf(to_float(q[i]), to_float(kp[sw < 0 ? i : rdl_cache_col<T>(sw, i, hd)]), d);
             d *= a.score_scale;
             if (a.softcap > 0.f) d = a.softcap * tanhf(d / a.softcap);
             s = d;
@@ -78,11 +80,12 @@ __global__ void attention_plain_kernel(AttentionArgs a) {
             const float pw = __shfl_sync(0xffffffffu, pj, jj);
             const unsigned lo32 = __shfl_sync(0xffffffffu, (unsigned)(vaddr & 0xffffffffull), jj);
             const unsigned hi32 = __shfl_sync(0xffffffffu, (unsigned)(vaddr >> 32), jj);
+            const int vsw = __shfl_sync(0xffffffffu, sw, jj);
             const T* vrow = (const T*)(((unsigned long long)hi32 << 32) | lo32);
 #pragma unroll
             for (int c = 0; c < PLAIN_MAX_CHUNKS; ++c) {
                 const int d = c * 32 + lane;
-                if (d < hd) acc[c] = fmaf(pw, to_float(vrow[d]), acc[c]);
+                if (d < hd) acc[c] = fmaf(pw, to_float(vrow[vsw < 0 ? d : rdl_cache_col<T>(vsw, d, hd)]), acc[c]);
             }
         }
     }

@@ -110,7 +110,9 @@ __global__ void __launch_bounds__(NTHREADS) attention_prefill_kernel(AttentionAr
             uint4 kvv = zero4, vvv = zero4;
             if (j <= p_last && c * 8 < hd) {
                 if (j < cached) {
-                    const long long off = rdl_cache_offset(table, j, a.page_size, a.ring_pages, a.n_kv_heads, g, hd) + c * 8;
+                    // chunks of a cache row are stored swizzled by the row's place in its page
+                    const long long off = rdl_cache_offset(table, j, a.page_size, a.ring_pages, a.n_kv_heads, g, hd) +
+                                          rdl_swizzled_chunk(j % a.page_size, c, hd / 8) * 8;
                     kvv = *(const uint4*)(kcache + off);
                     vvv = *(const uint4*)(vcache + off);
                 } else {

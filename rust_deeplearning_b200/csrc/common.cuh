@@ -100,3 +100,20 @@ __device__ __forceinline__ long long rdl_cache_offset(const int* __restrict__ ta
     const int r = pos - logical * page_size;
     return (((long long)page * n_kv_heads + kv_head) * page_size + r) * head_dim;
 }
+
+// Inside a row of a cache page the 16-byte chunks are stored swizzled by the row: chunk c of the row
+// at place `r` of its page lies at chunk c ^ (r & 7), for the chunks of the row's last incomplete
+// group of eight unchanged.  A whole [page_size][head_dim] block can then be copied to shared
+// memory in one piece and still be read by ldmatrix, eight rows at a time, without bank conflicts.
+// Rows whose size is no multiple of 16 bytes are stored plainly.
+__host__ __device__ __forceinline__ int rdl_swizzled_chunk(int r, int chunk, int chunks_per_row) {
+    return ((chunk | 7) < chunks_per_row) ? (chunk ^ (r & 7)) : chunk;
+}
+// Element i of a cache row of `head_dim` elements of type T -> its place in the stored row.
+template <typename T>
+__device__ __forceinline__ int rdl_cache_col(int r, int i, int head_dim) {
+    constexpr int EPC = 16 / (int)sizeof(T);
+    if (head_dim % EPC) return i;
+    const int c = i / EPC;
+    return rdl_swizzled_chunk(r, c, head_dim / EPC) * EPC + (i - c * EPC);
+}

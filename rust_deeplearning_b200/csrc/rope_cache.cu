@@ -45,7 +45,8 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int n_heads, int n_kv_hea
     const int kv_head = is_v ? head - n_heads - n_kv_heads : head - n_heads;
     T* dst = (is_v ? v_cache : k_cache) +
              rdl_cache_offset(tables + (long long)seq * table_width, pos, page_size, ring_pages, n_kv_heads, kv_head, head_dim);
-    for (int i = threadIdx.x; i < head_dim; i += blockDim.x) dst[i] = row[i];
+    const int r = pos % page_size;   // chunks of a cache row are stored swizzled by its place in the page
+    for (int i = threadIdx.x; i < head_dim; i += blockDim.x) dst[rdl_cache_col<T>(r, i, head_dim)] = row[i];
 }
 
 extern "C" int rdl_rope_cache(void* qkv, int dtype, int n_tokens, int n_heads, int n_kv_heads, int head_dim,

@@ -55,7 +55,7 @@ class Attention:
     def forward(self, x: torch.Tensor, batch, cache: RunCache, run: int) -> torch.Tensor:
         nh, nkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
         pages = self._pages(batch, cache)
-        fast = x.dtype is torch.bfloat16 and hd % 16 == 0 and hd <= 256 and nh // nkv <= 8
+        fast = x.dtype is torch.bfloat16 and hd % 16 == 0 and hd <= 256 and nh // nkv <= 16
         common = dict(n_heads=nh, n_kv_heads=nkv, head_dim=hd, score_scale=self.score_scale,
                       softcap=self.softcap, window=self.window)
         tables, rotary_dim = self._rotary_tables()

@@ -91,6 +91,30 @@ def _cache_index(table_row, pos, page_size, ring_pages):
     return int(table_row[logical % ring_pages]), pos - logical * page_size
 
 
+def _swizzle_index(r, head_dim, element_size):
+    """Where the elements of a row lie inside a cache page: the row's 16-byte chunks are stored at
+    chunk c ^ (r & 7), r being the row's place in its page; chunks of the last incomplete group of
+    eight, and rows whose size is no multiple of 16 bytes, are stored plainly."""
+    epc = 16 // element_size
+    idx = torch.arange(head_dim)
+    if head_dim % epc:
+        return idx
+    chunks = head_dim // epc
+    c = idx // epc
+    c_stored = torch.where((c | 7) < chunks, c ^ (r & 7), c)
+    return c_stored * epc + idx % epc
+
+
+def cache_store(dst_row, values, r):
+    """Write a key or value row into its place `r` of a cache page."""
+    dst_row[_swizzle_index(r, values.numel(), values.element_size()).to(dst_row.device)] = values
+
+
+def cache_load(src_row, r):
+    """Read the key or value row at place `r` of a cache page."""
+    return src_row[_swizzle_index(r, src_row.numel(), src_row.element_size()).to(src_row.device)]
+
+
 def rope_cache(qkv, n_heads, n_kv_heads, head_dim, *, tok_seq, tok_pos, cos=None, sin=None, rotary_dim=0,
                pages=None, seq_end=None):
     T = qkv.shape[0]
@@ -113,8 +137,8 @@ def rope_cache(qkv, n_heads, n_kv_heads, head_dim, *, tok_seq, tok_pos, cos=None
                 continue
             page, r = _cache_index(pages.tables[seq], pos, pages.page_size, pages.ring_pages)
             for g in range(n_kv_heads):
-                pages.k[page, g, r] = rows[t, n_heads + g]
-                pages.v[page, g, r] = rows[t, n_heads + n_kv_heads + g]
+                cache_store(pages.k[page, g, r], rows[t, n_heads + g], r)
+                cache_store(pages.v[page, g, r], rows[t, n_heads + n_kv_heads + g], r)
     return qkv
 
 
@@ -138,8 +162,8 @@ def attention(q, b, pages, *, n_heads, n_kv_heads, head_dim, score_scale, softca
             for j in range(lo, p + 1):
                 if j < cached:
                     page, r = _cache_index(pages.tables[seq], j, pages.page_size, pages.ring_pages)
-                    ks.append(pages.k[page, g, r])
-                    vs.append(pages.v[page, g, r])
+                    ks.append(cache_load(pages.k[page, g, r], r))
+                    vs.append(cache_load(pages.v[page, g, r], r))
                 else:
                     rows, k_col, v_col = new_kv
                     ks.append(rows[row0 + j, k_col + g * head_dim:k_col + (g + 1) * head_dim])

@@ -259,7 +259,7 @@ def test_attention_finds_one_far_key():
         c.k[page, 0, r] = 8.0                       # score 128 against about 0 +- 4 elsewhere
         want = ref.attention(c.qkv, b, c.pages, **c.kw(scale=1.0))
         visible = window is None or 1000 - far < window
-        target = c.v[page, 0, r].double().cpu()
+        target = ref.cache_load(c.v[page, 0, r], r).double().cpu()
         hit = (want[0, :64].double().cpu() - target).abs().max().item() < 1e-2
         assert hit == visible
         for kind in ("decode", "plain"):
