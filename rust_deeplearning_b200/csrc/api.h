@@ -10,10 +10,13 @@ extern "C" {
 #define RDL_ACT_GELU_TANH 0
 #define RDL_ACT_SILU 1
 
-#define RDL_ABI_VERSION 3
+#define RDL_ABI_VERSION 4
 
 const char* rdl_last_error(void);
 int rdl_abi_version(void);
+// 1 (the default): the decode-path kernels are launched with programmatic dependent launch, so that a
+// kernel's start-up overlaps the end of the kernel before it; 0: ordinary launches.
+void rdl_set_programmatic_launch(int on);
 
 // One attention call over a batch of sequences: the new tokens of this step are the queries,
 // keys and values come from a paged cache and from the step's own packed rows.

@@ -23,6 +23,7 @@
 // an error in `status` and leaves.
 #include "api.h"
 #include "common.cuh"
+#include "launch.cuh"
 
 namespace {
 
@@ -118,14 +119,19 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
     const uint32_t row_bytes = (uint32_t)hd * 2;
 
     const int page_first = k_begin / ps, page_last = (k_end - 1) / ps;
-    // a run of several pages: ask L2 for all of them now, so that the copies below find them there
-    if (page_last > page_first && tid <= page_last - page_first) {
+    // Ask L2 for the run's pages now.  Nothing read up to here was written by an earlier kernel of this
+    // step (the batch description and page lists come from the host; the newest row of the last page is
+    // written by the kernel before this one, but a prefetch only moves lines into L2, where that write
+    // lands too), so this runs while the earlier kernel is still finishing.
+    if (tid <= page_last - page_first) {
         const int page = table[(page_first + tid) % a.ring_pages];
         const long long off = ((long long)page * a.n_kv_heads + g) * ps * hd;
         asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(kcache + off), "r"(ps * row_bytes) : "memory");
         asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(vcache + off), "r"(ps * row_bytes) : "memory");
     }
     if (tid == 0) mbar_init(bar, 1);
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
     // query tile: row h = head g * G + h of this token, rows from G on are zero
     for (int idx = tid; idx < QROWS * (HD / 8); idx += DEC_THREADS) {
         const int r = idx / (HD / 8), c = idx - r * (HD / 8);
@@ -163,6 +169,15 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
         const int r_begin = max(k_begin, lp * ps) - lp * ps, r_end = min(k_end, (lp + 1) * ps) - lp * ps;
         const int w0 = warp * 16;                  // this warp's 16 keys of the page
         if (w0 < r_end && w0 + 16 > r_begin) {
+            if (w0 < r_begin || w0 + 16 > r_end) {
+                // value rows outside the run get the weight 0; they may hold anything (rows beyond the
+                // sequence's end, an earlier occupant's rows), so make them zero: 0 * NaN is NaN
+                for (int idx = lane; idx < 16 * chunks; idx += 32) {
+                    const int r = w0 + idx / chunks;
+                    if (r < r_begin || r >= r_end) *(uint4*)(v_tile + (size_t)r * row_bytes + (idx % chunks) * 16) = make_uint4(0, 0, 0, 0);
+                }
+                __syncwarp();
+            }
             float s[2][4];
 #pragma unroll
             for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
@@ -328,8 +343,7 @@ int launch_decode(const AttentionArgs* a, cudaStream_t st) {
         granted = smem;
     }
     dim3 grid(a->max_splits, a->n_kv_heads, a->n_tokens);
-    attention_decode_kernel<HD><<<grid, DEC_THREADS, smem, st>>>(*a);
-    RDL_CHECK_LAUNCH("attention_decode");
+    RDL_CHECK_EX(rdl_launch(attention_decode_kernel<HD>, grid, dim3(DEC_THREADS), (size_t)smem, st, *a), "attention_decode");
     return 0;
 }
 

@@ -3,6 +3,11 @@
 
 #include "api.h"
 #include "common.cuh"
+#include "launch.cuh"
+
+int g_rdl_programmatic_launch = 1;
+
+extern "C" void rdl_set_programmatic_launch(int on) { g_rdl_programmatic_launch = on ? 1 : 0; }
 
 static thread_local char g_error[512] = "";
 

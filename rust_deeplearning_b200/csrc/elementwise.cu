@@ -8,6 +8,7 @@
 //   cap * tanh(z / cap)             nn/main/src/core/attention.rs:419-423
 #include "api.h"
 #include "common.cuh"
+#include "launch.cuh"
 
 // ---------------------------------------------------------------------------------------------
 // embedding
@@ -15,6 +16,8 @@
 __global__ void embed_rows_kernel(float* __restrict__ out, const void* __restrict__ table, int table_dtype,
                                   const int* __restrict__ ids, float scale, int hidden, int vocab,
                                   int* __restrict__ status) {
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (long long)t * hidden;
@@ -34,9 +37,8 @@ extern "C" int rdl_embed_rows(void* out_f32, const void* table, int table_dtype,
     RDL_REQUIRE(n_rows >= 0 && hidden > 0 && vocab > 0, "embed_rows: bad sizes rows=%d hidden=%d vocab=%d", n_rows, hidden, vocab);
     if (n_rows == 0) return 0;
     const int threads = hidden >= 1024 ? 256 : 128;
-    embed_rows_kernel<<<n_rows, threads, 0, (cudaStream_t)stream>>>((float*)out_f32, table, table_dtype, ids, scale,
-                                                                     hidden, vocab, status);
-    RDL_CHECK_LAUNCH("embed_rows");
+    RDL_CHECK_EX(rdl_launch(embed_rows_kernel, dim3(n_rows), dim3(threads), 0, (cudaStream_t)stream, (float*)out_f32, table,
+                            table_dtype, ids, scale, hidden, vocab, status), "embed_rows");
     return 0;
 }
 
@@ -60,6 +62,8 @@ struct NormArgs {
 __global__ void norm_residual_norm_kernel(NormArgs a) {
     extern __shared__ float row[];          // hidden floats
     __shared__ float scratch[33];
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
     const int r = blockIdx.x;
     const int H = a.hidden;
     const long long xin = (long long)(a.row_index ? a.row_index[r] : r) * H;
@@ -124,6 +128,8 @@ __device__ __forceinline__ void store4(void* p, long long i, int dtype, float4 v
 template <int ITER>
 __global__ void __launch_bounds__(256) norm_residual_norm_vec_kernel(NormArgs a) {
     __shared__ float scratch[33];
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
     const int r = blockIdx.x;
     const int H = a.hidden;
     const long long xin = (long long)(a.row_index ? a.row_index[r] : r) * H;
@@ -197,11 +203,12 @@ extern "C" int rdl_norm_residual_norm(const void* x, int x_dtype, const int* row
         aligned16(x) && aligned16(res_f32) && aligned16(w1) && aligned16(w2) && aligned16(y)) {
         NormArgs a{x, x_dtype, row_index, w1, w1_dtype, eps1, off1, (float*)res_f32, w2, w2_dtype, eps2, off2, y, y_dtype, hidden};
         cudaStream_t st = (cudaStream_t)stream;
-        if (hidden <= 1024) norm_residual_norm_vec_kernel<1><<<n_rows, 256, 0, st>>>(a);
-        else if (hidden <= 2048) norm_residual_norm_vec_kernel<2><<<n_rows, 256, 0, st>>>(a);
-        else if (hidden <= 4096) norm_residual_norm_vec_kernel<4><<<n_rows, 256, 0, st>>>(a);
-        else norm_residual_norm_vec_kernel<8><<<n_rows, 256, 0, st>>>(a);
-        RDL_CHECK_LAUNCH("norm_residual_norm");
+        cudaError_t e;
+        if (hidden <= 1024) e = rdl_launch(norm_residual_norm_vec_kernel<1>, dim3(n_rows), dim3(256), 0, st, a);
+        else if (hidden <= 2048) e = rdl_launch(norm_residual_norm_vec_kernel<2>, dim3(n_rows), dim3(256), 0, st, a);
+        else if (hidden <= 4096) e = rdl_launch(norm_residual_norm_vec_kernel<4>, dim3(n_rows), dim3(256), 0, st, a);
+        else e = rdl_launch(norm_residual_norm_vec_kernel<8>, dim3(n_rows), dim3(256), 0, st, a);
+        RDL_CHECK_EX(e, "norm_residual_norm");
         return 0;
     }
     RDL_REQUIRE(rdl_valid_dtype(x_dtype) && rdl_valid_dtype(y_dtype), "norm: bad dtype");
@@ -222,8 +229,7 @@ extern "C" int rdl_norm_residual_norm(const void* x, int x_dtype, const int* row
     }
     NormArgs a{x, x_dtype, row_index, w1, w1_dtype, eps1, off1, (float*)res_f32, w2, w2_dtype, eps2, off2, y, y_dtype, hidden};
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-    norm_residual_norm_kernel<<<n_rows, threads, smem, (cudaStream_t)stream>>>(a);
-    RDL_CHECK_LAUNCH("norm_residual_norm");
+    RDL_CHECK_EX(rdl_launch(norm_residual_norm_kernel, dim3(n_rows), dim3(threads), smem, (cudaStream_t)stream, a), "norm_residual_norm");
     return 0;
 }
 

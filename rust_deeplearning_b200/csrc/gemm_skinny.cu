@@ -16,6 +16,7 @@
 // bytes feed two instructions), which leaves every dot product unchanged.
 #include "api.h"
 #include "common.cuh"
+#include "launch.cuh"
 
 namespace {
 
@@ -83,6 +84,14 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(SkinnyArgs a) {
 #pragma unroll
         for (int i = 0; i < NT; ++i) acc[s][i][0] = acc[s][i][1] = acc[s][i][2] = acc[s][i][3] = 0.f;
 
+    // The weights are constants: ask L2 for this block's rows, then wait for the kernel that produces x.
+    if (threadIdx.x < NS * ROWS) {
+        const int s = threadIdx.x / ROWS, r = threadIdx.x % ROWS;
+        if (n0 + r < a.N)
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.w + (long long)(s * a.N + n0 + r) * K), "r"(K * 2) : "memory");
+    }
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
     const uint4 zero4 = make_uint4(0, 0, 0, 0);
     for (int kc = warp * KCHUNK; kc < K; kc += WARPS * KCHUNK) {
         uint4 wa[NS][4][2], xb[NT][4];
@@ -139,13 +148,15 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(SkinnyArgs a) {
     }
 }
 
+thread_local cudaError_t g_launch_error = cudaSuccess;
+
 template <int NT, int WARPS>
 void launch(const SkinnyArgs& a, cudaStream_t st) {
     const int blocks = (a.N + ROWS - 1) / ROWS;
     if (a.gated)
-        gemm_skinny_kernel<NT, WARPS, true><<<blocks, WARPS * 32, 0, st>>>(a);
+        g_launch_error = rdl_launch(gemm_skinny_kernel<NT, WARPS, true>, dim3(blocks), dim3(WARPS * 32), 0, st, a);
     else
-        gemm_skinny_kernel<NT, WARPS, false><<<blocks, WARPS * 32, 0, st>>>(a);
+        g_launch_error = rdl_launch(gemm_skinny_kernel<NT, WARPS, false>, dim3(blocks), dim3(WARPS * 32), 0, st, a);
 }
 
 }  // namespace
@@ -170,6 +181,6 @@ extern "C" int rdl_gemm_skinny(void* out, int out_dtype, const void* x, const vo
     } else {
         if (wide) launch<2, 4>(a, st); else launch<2, 8>(a, st);
     }
-    RDL_CHECK_LAUNCH("gemm_skinny");
+    RDL_CHECK_EX(g_launch_error, "gemm_skinny");
     return 0;
 }

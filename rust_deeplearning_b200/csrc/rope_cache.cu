@@ -9,6 +9,7 @@
 // length per sequence instead of one shared length.
 #include "api.h"
 #include "common.cuh"
+#include "launch.cuh"
 
 template <typename T>
 __global__ void rope_cache_kernel(T* __restrict__ qkv, int n_heads, int n_kv_heads, int head_dim, int rotary_dim,
@@ -17,6 +18,8 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int n_heads, int n_kv_hea
                                   int do_rope, int do_write, T* __restrict__ k_cache, T* __restrict__ v_cache,
                                   const int* __restrict__ tables, int table_width, int page_size, int ring_pages,
                                   const int* __restrict__ seq_end) {
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
     const int t = blockIdx.x;
     const int head = blockIdx.y;
     const int total_heads = n_heads + 2 * n_kv_heads;
@@ -69,14 +72,15 @@ extern "C" int rdl_rope_cache(void* qkv, int dtype, int n_tokens, int n_heads, i
     dim3 grid(n_tokens, total_heads);
     const int threads = head_dim >= 256 ? 128 : (head_dim >= 64 ? 64 : 32);
     cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
     if (dtype == RDL_BF16)
-        rope_cache_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>((__nv_bfloat16*)qkv, n_heads, n_kv_heads, head_dim, rotary_dim,
-            cos_table, sin_table, tok_seq, tok_pos, do_rope, do_write, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
-            tables, table_width, page_size, ring_pages, seq_end);
+        e = rdl_launch(rope_cache_kernel<__nv_bfloat16>, grid, dim3(threads), 0, st, (__nv_bfloat16*)qkv, n_heads, n_kv_heads, head_dim,
+                       rotary_dim, cos_table, sin_table, tok_seq, tok_pos, do_rope, do_write, (__nv_bfloat16*)k_cache,
+                       (__nv_bfloat16*)v_cache, tables, table_width, page_size, ring_pages, seq_end);
     else
-        rope_cache_kernel<float><<<grid, threads, 0, st>>>((float*)qkv, n_heads, n_kv_heads, head_dim, rotary_dim,
-            cos_table, sin_table, tok_seq, tok_pos, do_rope, do_write, (float*)k_cache, (float*)v_cache,
-            tables, table_width, page_size, ring_pages, seq_end);
-    RDL_CHECK_LAUNCH("rope_cache");
+        e = rdl_launch(rope_cache_kernel<float>, grid, dim3(threads), 0, st, (float*)qkv, n_heads, n_kv_heads, head_dim,
+                       rotary_dim, cos_table, sin_table, tok_seq, tok_pos, do_rope, do_write, (float*)k_cache,
+                       (float*)v_cache, tables, table_width, page_size, ring_pages, seq_end);
+    RDL_CHECK_EX(e, "rope_cache");
     return 0;
 }

@@ -16,6 +16,7 @@
 //     from an unseeded thread-local generator, generator.rs:199).
 #include "api.h"
 #include "common.cuh"
+#include "launch.cuh"
 
 namespace {
 
@@ -86,6 +87,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(int* __restrict_
     __shared__ int best_idx[32];
     __shared__ float chunk_sum[SAMPLE_THREADS];
     __shared__ int chosen;
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
     const int row = blockIdx.x, tid = threadIdx.x;
     const float* x = logits + (long long)row * vocab;
 
@@ -240,8 +243,7 @@ extern "C" int rdl_sample(int* out_tokens, const float* logits, int n_rows, int 
         RDL_REQUIRE(prm->repetition_penalty == 1.0f || !history || history_start, "sample: history without offsets");
     }
     if (n_rows == 0) return 0;
-    sample_kernel<<<n_rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(out_tokens, logits, vocab, *prm, row_stream, row_step,
-                                                                     history, history_start, work);
-    RDL_CHECK_LAUNCH("sample");
+    RDL_CHECK_EX(rdl_launch(sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, out_tokens, logits, vocab,
+                            *prm, row_stream, row_step, history, history_start, work), "sample");
     return 0;
 }

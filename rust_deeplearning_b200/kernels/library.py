@@ -23,7 +23,7 @@ from concurrent.futures import ThreadPoolExecutor
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(_PKG, "csrc")
 LIB_NAME = "librdl_b200_kernels.so"
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 # fast math is never enabled: the 32-bit path relies on exact tanhf/expf/sqrtf and plain FMA
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -211,6 +211,10 @@ def load():
         lib.rdl_attention_decode_scratch_bytes.restype = _LL
         lib.rdl_sampling_uniform.argtypes = [ctypes.c_ulonglong] * 3
         lib.rdl_sampling_uniform.restype = ctypes.c_float
+        lib.rdl_set_programmatic_launch.argtypes = [ctypes.c_int]
+        lib.rdl_set_programmatic_launch.restype = None
+        if os.environ.get("RDL_PROGRAMMATIC_LAUNCH") == "0":   # ordinary launches, for comparison
+            lib.rdl_set_programmatic_launch(0)
         _lib = lib
         _lib.path = path
     return _lib
