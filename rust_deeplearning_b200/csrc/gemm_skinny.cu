@@ -84,17 +84,9 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(SkinnyArgs a) {
 #pragma unroll
         for (int i = 0; i < NT; ++i) acc[s][i][0] = acc[s][i][1] = acc[s][i][2] = acc[s][i][3] = 0.f;
 
-    // The weights are constants: ask L2 for this block's rows, then wait for the kernel that produces x.
-    if (threadIdx.x < NS * ROWS) {
-        const int s = threadIdx.x / ROWS, r = threadIdx.x % ROWS;
-        if (n0 + r < a.N)
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.w + (long long)(s * a.N + n0 + r) * K), "r"(K * 2) : "memory");
-    }
-    rdl_grid_wait();
-    rdl_grid_launch_dependents();
     const uint4 zero4 = make_uint4(0, 0, 0, 0);
-    for (int kc = warp * KCHUNK; kc < K; kc += WARPS * KCHUNK) {
-        uint4 wa[NS][4][2], xb[NT][4];
+    // one chunk of this warp's weights: 4 steps of 32 k, two rows per lane and stream
+    auto load_weights = [&](int kc, uint4 (&wa)[NS][4][2]) {
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             const int k = kc + u * 32 + t * 8;
@@ -104,9 +96,25 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(SkinnyArgs a) {
                 wa[s][u][0] = (k_ok && row0_ok) ? ld_stream(wrow[s][0] + k) : zero4;
                 wa[s][u][1] = (k_ok && row1_ok) ? ld_stream(wrow[s][1] + k) : zero4;
             }
+        }
+    };
+    // The weights are constants: the first chunk is requested before waiting for the kernel that
+    // produces x, and every later chunk while the chunk before it is being multiplied.
+    uint4 wcur[NS][4][2], wnext[NS][4][2];
+    int kc = warp * KCHUNK;
+    if (kc < K) load_weights(kc, wcur);
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
+    for (; kc < K; kc += WARPS * KCHUNK) {
+        const int kn = kc + WARPS * KCHUNK;
+        if (kn < K) load_weights(kn, wnext);
+        uint4 xb[NT][4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int k = kc + u * 32 + t * 8;
 #pragma unroll
             for (int i = 0; i < NT; ++i)
-                xb[i][u] = (k_ok && x_ok[i]) ? __ldg(reinterpret_cast<const uint4*>(xrow[i] + k)) : zero4;
+                xb[i][u] = (k < K && x_ok[i]) ? __ldg(reinterpret_cast<const uint4*>(xrow[i] + k)) : zero4;
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u)
@@ -114,9 +122,18 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(SkinnyArgs a) {
             for (int s = 0; s < NS; ++s)
 #pragma unroll
                 for (int i = 0; i < NT; ++i) {
-                    mma_bf16(acc[s][i], wa[s][u][0].x, wa[s][u][1].x, wa[s][u][0].y, wa[s][u][1].y, xb[i][u].x, xb[i][u].y);
-                    mma_bf16(acc[s][i], wa[s][u][0].z, wa[s][u][1].z, wa[s][u][0].w, wa[s][u][1].w, xb[i][u].z, xb[i][u].w);
+                    mma_bf16(acc[s][i], wcur[s][u][0].x, wcur[s][u][1].x, wcur[s][u][0].y, wcur[s][u][1].y, xb[i][u].x, xb[i][u].y);
+                    mma_bf16(acc[s][i], wcur[s][u][0].z, wcur[s][u][1].z, wcur[s][u][0].w, wcur[s][u][1].w, xb[i][u].z, xb[i][u].w);
                 }
+        if (kn < K) {
+#pragma unroll
+            for (int s = 0; s < NS; ++s)
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    wcur[s][u][0] = wnext[s][u][0];
+                    wcur[s][u][1] = wnext[s][u][1];
+                }
+        }
     }
     // accumulator element e of a lane: weight row g + 8 * (e >> 1), activation row 2 t + (e & 1)
 #pragma unroll

@@ -285,11 +285,12 @@ def _attention_args(q, q_stride, k_new, v_new, kv_stride, out, b: AttentionBatch
 
 
 def choose_keys_per_split(n_tokens: int, n_kv_heads: int, max_keys: int, page_size: int) -> int:
-    """Keys per block of the decode kernel: the largest run (in pages) that still gives the GPU
-    about four blocks per multiprocessor; at least one page."""
-    for pages in (8, 4, 2):
+    """Keys per block of the decode kernel: runs of four pages (a block then streams its pages one after
+    the other, and fewer partial results are merged), shorter ones while that leaves the GPU with
+    fewer than about one and a half blocks per multiprocessor."""
+    for pages in (4, 2):
         keys = pages * page_size
-        if n_tokens * n_kv_heads * ((max_keys + keys - 1) // keys) >= 4 * 148:
+        if n_tokens * n_kv_heads * ((max_keys + keys - 1) // keys) >= 222:
             return keys
     return page_size
 
