@@ -165,6 +165,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="run one small case (for profiling) and print a short line instead of the full record")
+    ap.add_argument("--batch", type=int, default=8, help="batch of the --only decode case")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -198,6 +201,26 @@ def main():
     spec = arch.build_spec(arch.parse_config(cfg))
     wbytes = weight_bytes(spec)
     V = cfg["vocab_size"]
+
+    if args.only is not None:
+        # one case, few steps: what a profiler is pointed at
+        engine = Engine(model, max_tokens=args.batch * CONTEXT, max_seqs=args.batch, max_context=CONTEXT)
+        if args.only == "decode":
+            ms, launches, _ = decode_run(engine, args.batch, args.steps, args.warmup, V, torch, rng)
+            print(json.dumps({"case": "decode", "batch": args.batch, "layers": layers, "ms_per_step": round(ms, 4),
+                              "tokens_per_s": round(args.batch / (ms * 1e-3), 1), "launches": launches}))
+        else:
+            prompt = [int(v) for v in rng.integers(0, V, size=PROMPT)]
+            for _ in range(args.warmup + args.steps):
+                slot = engine.new_sequence()
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                engine.step([slot], [prompt], "last")
+                stop.record()
+                torch.cuda.synchronize()
+                engine.release(slot)
+            print(json.dumps({"case": "prefill", "tokens": PROMPT, "layers": layers, "ms": round(start.elapsed_time(stop), 3)}))
+        return 0
 
     clocks = ClockSampler()
     clocks.start()

@@ -157,6 +157,7 @@ class RunCache(NamedTuple):
     ring_pages: int
     state: Optional[torch.Tensor]   # [max_seqs, *shape], indexed by slot
     owns_kv: bool                   # False: the run reads another run's keys and values
+    is_ring: bool = False           # the group keeps a window of keys: a position's row is reused later
 
 
 class Cache:
@@ -270,19 +271,19 @@ class Cache:
         n = self.needs[run]
         owner = n.reads_cache_of if n.reads_cache_of is not None else run
         kv_group = k = v = None
-        page_size, ring = self.page_size, 0
+        page_size, ring, is_ring = self.page_size, 0, False
         if owner in self._kv_of_run:
             kv_group, idx = self._kv_of_run[owner]
             g = self.kv_groups[kv_group]
             k = g.k[idx] if g.k is not None else None
             v = g.v[idx] if g.v is not None else None
-            ring = g.ring_pages
+            ring, is_ring = g.ring_pages, g.is_ring
         state = None
         if run in self._state_of_run:
             gi, idx = self._state_of_run[run]
             data = self.state_groups[gi].data
             state = data[idx] if data is not None else None
-        return RunCache(kv_group, k, v, page_size, ring, state, n.reads_cache_of is None)
+        return RunCache(kv_group, k, v, page_size, ring, state, n.reads_cache_of is None, is_ring)
 
     def nbytes(self):
         return sum(g.nbytes() for g in self.kv_groups) + sum(

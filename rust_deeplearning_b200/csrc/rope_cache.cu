@@ -52,6 +52,104 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int n_heads, int n_kv_hea
     for (int i = threadIdx.x; i < head_dim; i += blockDim.x) dst[rdl_cache_col<T>(r, i, head_dim)] = row[i];
 }
 
+// The same work with 16-byte accesses: one block per token, a thread per 16-byte chunk (or pair of
+// chunks that rotate together).  Used when head_dim and rotary_dim / 2 are whole numbers of chunks.
+template <typename T> struct Chunk;
+template <> struct Chunk<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&f)[8]) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 v = __bfloat1622float2(h[i]); f[2 * i] = v.x; f[2 * i + 1] = v.y; }
+    }
+    static __device__ __forceinline__ uint4 pack(const float (&f)[8]) {
+        uint4 raw;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+        return raw;
+    }
+};
+template <> struct Chunk<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float (&f)[4]) {
+        const float4 v = *reinterpret_cast<const float4*>(p);
+        f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+    }
+    static __device__ __forceinline__ uint4 pack(const float (&f)[4]) {
+        uint4 raw;
+        raw.x = __float_as_uint(f[0]); raw.y = __float_as_uint(f[1]); raw.z = __float_as_uint(f[2]); raw.w = __float_as_uint(f[3]);
+        return raw;
+    }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) rope_cache_vec_kernel(T* __restrict__ qkv, int n_heads, int n_kv_heads, int head_dim, int rotary_dim,
+                                                             const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                                             const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                                                             int do_rope, int do_write, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                                             const int* __restrict__ tables, int table_width, int page_size,
+                                                             int ring_pages, const int* __restrict__ seq_end) {
+    constexpr int N = Chunk<T>::N;
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
+    const int t = blockIdx.x;
+    const int pos = tok_pos[t];
+    if (pos < 0) return;  // a padding row of a fixed-size batch
+    const int total_heads = n_heads + 2 * n_kv_heads;
+    const int chunks = head_dim / N;
+    const int half = rotary_dim >> 1, half_chunks = do_rope ? half / N : 0;
+    T* base = qkv + (long long)t * total_heads * head_dim;
+    bool write = do_write && n_kv_heads > 0;
+    int r = 0;
+    long long page_base = 0;
+    if (write) {
+        const int seq = tok_seq[t];
+        // In a ring a later token of this step may land on the same row: only the last writer writes.
+        if ((long long)pos + (long long)ring_pages * page_size < (long long)seq_end[seq]) write = false;
+        const int logical = pos / page_size;
+        r = pos - logical * page_size;
+        page_base = (long long)tables[(long long)seq * table_width + logical % ring_pages] * n_kv_heads;
+    }
+    const int first_head = do_rope ? 0 : n_heads;     // without rotation the query heads need nothing
+    for (int item = first_head * chunks + threadIdx.x; item < total_heads * chunks; item += blockDim.x) {
+        const int head = item / chunks, c = item - head * chunks;
+        const bool is_q = head < n_heads, is_v = head >= n_heads + n_kv_heads;
+        const bool rotated = !is_v && c < 2 * half_chunks;
+        if (rotated && c >= half_chunks) continue;    // done together with its partner chunk
+        T* row = base + (long long)head * head_dim;
+        T* dst = nullptr;
+        if (write && !is_q) {
+            const int kv_head = is_v ? head - n_heads - n_kv_heads : head - n_heads;
+            dst = (is_v ? v_cache : k_cache) + ((page_base + kv_head) * page_size + r) * head_dim;
+        }
+        float a[N];
+        Chunk<T>::load(row + c * N, a);
+        if (rotated) {
+            float b[N];
+            Chunk<T>::load(row + (c + half_chunks) * N, b);
+            const float* cs = cos_t + (long long)pos * half + c * N;
+            const float* sn = sin_t + (long long)pos * half + c * N;
+            float lo[N], hi[N];
+#pragma unroll
+            for (int i = 0; i < N; ++i) {
+                lo[i] = a[i] * cs[i] - b[i] * sn[i];
+                hi[i] = a[i] * sn[i] + b[i] * cs[i];
+            }
+            const uint4 plo = Chunk<T>::pack(lo), phi = Chunk<T>::pack(hi);
+            *reinterpret_cast<uint4*>(row + c * N) = plo;
+            *reinterpret_cast<uint4*>(row + (c + half_chunks) * N) = phi;
+            if (dst) {
+                *reinterpret_cast<uint4*>(dst + rdl_swizzled_chunk(r, c, chunks) * N) = plo;
+                *reinterpret_cast<uint4*>(dst + rdl_swizzled_chunk(r, c + half_chunks, chunks) * N) = phi;
+            }
+        } else if (dst) {
+            *reinterpret_cast<uint4*>(dst + rdl_swizzled_chunk(r, c, chunks) * N) = Chunk<T>::pack(a);
+        }
+    }
+}
+
 extern "C" int rdl_rope_cache(void* qkv, int dtype, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                               int rotary_dim, const float* cos_table, const float* sin_table,
                               const int* tok_seq, const int* tok_pos, int do_rope, int do_write,
@@ -69,10 +167,26 @@ extern "C" int rdl_rope_cache(void* qkv, int dtype, int n_tokens, int n_heads, i
     const int total_heads = n_heads + 2 * n_kv_heads;
     RDL_REQUIRE(total_heads <= 65535, "rope_cache: %d heads exceed the grid limit", total_heads);
     if (n_tokens == 0) return 0;
-    dim3 grid(n_tokens, total_heads);
-    const int threads = head_dim >= 256 ? 128 : (head_dim >= 64 ? 64 : 32);
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
+    const int per_chunk = dtype == RDL_BF16 ? 8 : 4;
+    const bool aligned = ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0;
+    if (aligned && head_dim % per_chunk == 0 && (!do_rope || (rotary_dim / 2) % per_chunk == 0)) {
+        const int items = total_heads * (head_dim / per_chunk);
+        const int vthreads = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
+        if (dtype == RDL_BF16)
+            e = rdl_launch(rope_cache_vec_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(vthreads), 0, st, (__nv_bfloat16*)qkv, n_heads,
+                           n_kv_heads, head_dim, rotary_dim, cos_table, sin_table, tok_seq, tok_pos, do_rope, do_write,
+                           (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, tables, table_width, page_size, ring_pages, seq_end);
+        else
+            e = rdl_launch(rope_cache_vec_kernel<float>, dim3(n_tokens), dim3(vthreads), 0, st, (float*)qkv, n_heads, n_kv_heads,
+                           head_dim, rotary_dim, cos_table, sin_table, tok_seq, tok_pos, do_rope, do_write, (float*)k_cache,
+                           (float*)v_cache, tables, table_width, page_size, ring_pages, seq_end);
+        RDL_CHECK_EX(e, "rope_cache");
+        return 0;
+    }
+    dim3 grid(n_tokens, total_heads);
+    const int threads = head_dim >= 256 ? 128 : (head_dim >= 64 ? 64 : 32);
     if (dtype == RDL_BF16)
         e = rdl_launch(rope_cache_kernel<__nv_bfloat16>, grid, dim3(threads), 0, st, (__nv_bfloat16*)qkv, n_heads, n_kv_heads, head_dim,
                        rotary_dim, cos_table, sin_table, tok_seq, tok_pos, do_rope, do_write, (__nv_bfloat16*)k_cache,

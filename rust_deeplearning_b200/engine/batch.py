@@ -82,6 +82,7 @@ class StepBatch:
     cache_owner_of: Dict[int, int] = field(default_factory=dict)     # run -> run whose keys and values it reads
     shared_runs: frozenset = frozenset()                             # runs whose keys and values a later run reads
     status: Optional[torch.Tensor] = None                            # int32 flag kernels set when they give up a wait
+    has_past: bool = True                                            # some sequence of the step has earlier positions in the cache
 
     def attention_batch(self, keys_in_cache: str, window: Optional[int] = None) -> AttentionBatch:
         """keys_in_cache: "past" - new keys are read from the step's packed rows;

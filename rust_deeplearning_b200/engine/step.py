@@ -133,6 +133,7 @@ class Engine:
             batch = batch_from_buffer(dev, layout, real_tokens=real_tokens, real_seqs=n, n_want=n_want, n_tiles=n_tiles,
                                       is_decode=is_decode, max_total_len=max(totals), scratch=self._scratch)
             batch.status = self.status
+            batch.has_past = max(past) > 0
             logits = self.model.forward(batch, self.cache)
             self.eager_steps += 1
         self.cache.advance(slots, lens)

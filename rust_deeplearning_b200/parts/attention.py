@@ -96,18 +96,24 @@ class Attention:
             ctx = ops.attention(qkv, ab, pages, kind="decode" if fast else "plain",
                                 scratch=lambda n: batch.scratch_buffer("decode", n), status=batch.status, **common)
         else:
-            # rotate; attend over the cache (earlier steps) and the packed rows (this step); then write.
-            # The write comes last because in a ring it may overwrite rows this step's early queries need.
+            # rotate; attend over the cache (earlier steps) and the packed rows (this step); write.
+            # In a ring the write may overwrite rows of earlier steps that this step's early queries still
+            # need, so there it comes last; otherwise it rides along with the rotation.
+            write_first = pages is not None and (not cache.is_ring or not batch.has_past)
             if tables is not None:
                 ops.rope_cache(qkv, nh, nkv, hd, tok_seq=batch.tok_seq, tok_pos=batch.tok_pos,
-                               cos=tables[0], sin=tables[1], rotary_dim=rotary_dim)
-            elif self.position is not None:
-                self.position.rotate(qkv, nh, nkv, hd, batch)
+                               cos=tables[0], sin=tables[1], rotary_dim=rotary_dim,
+                               pages=pages if write_first else None, seq_end=batch.seq_end)
+            else:
+                if self.position is not None:
+                    self.position.rotate(qkv, nh, nkv, hd, batch)
+                write_first = False
             ab = batch.attention_batch("past", self.window)
             ctx = ops.attention(qkv, ab, pages, new_kv=(qkv, self.q_width, self.q_width + self.kv_width),
                                 kind="prefill" if fast and batch.n_tiles else "plain", **common)
-            ops.rope_cache(qkv, nh, nkv, hd, tok_seq=batch.tok_seq, tok_pos=batch.tok_pos, pages=pages,
-                           seq_end=batch.seq_end)
+            if not write_first:
+                ops.rope_cache(qkv, nh, nkv, hd, tok_seq=batch.tok_seq, tok_pos=batch.tok_pos, pages=pages,
+                               seq_end=batch.seq_end)
             if run in batch.shared_runs:
                 batch.new_kv[run] = (qkv, self.q_width, self.q_width + self.kv_width)
         return ops.linear(ctx, self.w_o)
