@@ -57,10 +57,8 @@ __global__ void __launch_bounds__(NTHREADS) attention_prefill_kernel(AttentionAr
     const uint32_t sK = sQ + BM * HD * 2;
     const uint32_t sV = sK + BN * HD * 2;
     unsigned char* gQ = smem;
-    unsigned char* gK = smem + BM * HD * 2;
-    unsigned char* gV = gK + BN * HD * 2;
 
-    const int tile = blockIdx.x, h = blockIdx.y;
+    const int tile = a.n_tiles - 1 - blockIdx.x, h = blockIdx.y;   // later tiles of a sequence have more keys: start them first
     const int seq = a.tile_seq[tile], q0 = a.tile_q0[tile];
     const int row0 = a.seq_start[seq];
     const int n_new = a.seq_start[seq + 1] - row0;
@@ -102,33 +100,44 @@ __global__ void __launch_bounds__(NTHREADS) attention_prefill_kernel(AttentionAr
     const float inv_cap = a.softcap > 0.f ? 1.0f / a.softcap : 0.f;
     const int ksteps = (hd + 15) / 16;
 
-    for (int kv0 = (lo_first / BN) * BN; kv0 <= p_last; kv0 += BN) {
-        __syncthreads();  // the previous tile has been consumed (and the query tile is complete)
+    // One tile of keys (which == 0) or values (which == 1) on its way to shared memory: asynchronous
+    // 16-byte copies that bypass the registers, rows beyond the sequence and chunks beyond head_dim
+    // filled with zeros.  Each call is one commit group.
+    auto issue = [&](int kv0, int which) {
+        const uint32_t sdst = which ? sV : sK;
+        const __nv_bfloat16* cache_base = which ? vcache : kcache;
+        const __nv_bfloat16* new_base = which ? vnew : knew;
         for (int idx = tid; idx < BN * CH; idx += NTHREADS) {
             const int r = idx / CH, c = idx - r * CH;
             const int j = kv0 + r;
-            uint4 kvv = zero4, vvv = zero4;
+            const __nv_bfloat16* src = qbase;       // any valid address: nothing is read when the size is 0
+            uint32_t bytes = 0;
             if (j <= p_last && c * 8 < hd) {
-                if (j < cached) {
-                    // chunks of a cache row are stored swizzled by the row's place in its page
-                    const long long off = rdl_cache_offset(table, j, a.page_size, a.ring_pages, a.n_kv_heads, g, hd) +
-                                          rdl_swizzled_chunk(j % a.page_size, c, hd / 8) * 8;
-                    kvv = *(const uint4*)(kcache + off);
-                    vvv = *(const uint4*)(vcache + off);
-                } else {
-                    const long long off = (long long)(row0 + j - past) * a.kv_stride + (long long)g * hd + c * 8;
-                    kvv = *(const uint4*)(knew + off);
-                    vvv = *(const uint4*)(vnew + off);
-                }
+                bytes = 16;
+                if (j < cached)   // chunks of a cache row are stored swizzled by the row's place in its page
+                    src = cache_base + rdl_cache_offset(table, j, a.page_size, a.ring_pages, a.n_kv_heads, g, hd) +
+                          rdl_swizzled_chunk(j % a.page_size, c, hd / 8) * 8;
+                else
+                    src = new_base + (long long)(row0 + j - past) * a.kv_stride + (long long)g * hd + c * 8;
             }
-            const int dst = (r * CH + swizzled_chunk<HD>(r, c)) * 16;
-            *(uint4*)(gK + dst) = kvv;
-            *(uint4*)(gV + dst) = vvv;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(tile_addr<HD>(sdst, r, c)), "l"(src), "r"(bytes) : "memory");
         }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+
+    const int kv_first = (lo_first / BN) * BN;
+    if (kv_first <= p_last) {
+        issue(kv_first, 0);
+        issue(kv_first, 1);
+    }
+    for (int kv0 = kv_first; kv0 <= p_last; kv0 += BN) {
+        const bool has_next = kv0 + BN <= p_last;
+        asm volatile("cp.async.wait_group 1;\n" ::: "memory");   // this tile's keys have landed (its values may be on the way)
         __syncthreads();
 
         // this warp's rows see nothing of the tile: skip its arithmetic (barriers stay outside)
         const bool warp_active = kv0 <= pw_last && (a.window == 0 || pw_first - (kv0 + BN - 1) < a.window);
+        uint32_t pf[BN / 16][4];
         if (warp_active) {
             // ---- S = Q K^T ----
             float s[BN / 8][4];
@@ -175,7 +184,6 @@ __global__ void __launch_bounds__(NTHREADS) attention_prefill_kernel(AttentionAr
             const float c0 = exp2f(m0 - ms0), c1 = exp2f(m1 - ms1);
             m0 = mn0; m1 = mn1;
             float rs0 = 0.f, rs1 = 0.f;
-            uint32_t pf[BN / 16][4];
 #pragma unroll
             for (int nt = 0; nt < BN / 8; ++nt) {
                 const float e0 = exp2f(s[nt][0] - ms0), e1 = exp2f(s[nt][1] - ms0);
@@ -195,6 +203,13 @@ __global__ void __launch_bounds__(NTHREADS) attention_prefill_kernel(AttentionAr
             for (int i = 0; i < HD / 8; ++i) {
                 o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1;
             }
+        }
+        __syncthreads();                       // every warp is done with the key tile
+        if (has_next) issue(kv0 + BN, 0);      // the next keys travel while P V is computed
+        if (has_next) asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        else asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        __syncthreads();                       // this tile's values have landed
+        if (warp_active) {
             // ---- O += P V ----
 #pragma unroll
             for (int kk = 0; kk < BN / 16; ++kk) {
@@ -209,6 +224,8 @@ __global__ void __launch_bounds__(NTHREADS) attention_prefill_kernel(AttentionAr
                 }
             }
         }
+        __syncthreads();                       // every warp is done with the value tile
+        if (has_next) issue(kv0 + BN, 1);      // the next values travel while the next scores are computed
     }
 
     // ---- normalise and store ----
