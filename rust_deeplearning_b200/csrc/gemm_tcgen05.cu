@@ -1,0 +1,303 @@
+// Matrix product for many rows (prefill) on the fifth-generation tensor cores:
+//   out[m, n] = epilogue(sum_k x[m, k] * w[n, k]),  bfloat16 operands, float accumulation in TMEM.
+//
+// One block computes a 128 x BN tile.  Operand tiles of 64 k (128 bytes a row) are brought into
+// shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle) through a ring of stages guarded
+// by mbarriers; one thread issues tcgen05.mma (M 128, N BN, K 16) from shared-memory descriptors,
+// accumulating in tensor memory; tcgen05.commit hands stages back to the loader and the finished
+// accumulator to the epilogue warps, which read it with tcgen05.ld, apply the epilogue in float and
+// store.  Warp roles: warp 0 loads, warp 1 allocates tensor memory and issues the products, warps
+// 2-5 (one per 32-lane quarter of tensor memory) do the epilogue.
+//
+// Epilogues: store as bfloat16 or float; cap * tanh(v / cap); and, for a row-concatenated
+// [gate; up] matrix, act(gate) * up with both accumulators side by side in tensor memory, which
+// saves writing and re-reading the [rows, 2I] intermediate.
+// (y = x W^T, W [out, in]: rustml/nn/main/src/core/linear.rs:12-15; the gated form:
+// rustml/nn/main/src/core/feed_forward.rs:151-161.)
+//
+// Every wait is bounded (about a second of clock cycles); a block that gives up sets `status`,
+// and every path ends in the common tear-down that frees the tensor memory.
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128, BK = 64, STAGES = 4, TC_THREADS = 192;
+constexpr long long WAIT_CYCLES = 2000000000LL;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity))
+        if (clock64() - t0 > WAIT_CYCLES) return false;
+    return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+// K-major operand tile in shared memory, rows of 128 bytes, 128-byte swizzle: groups of 8 rows are 1024 bytes apart
+__device__ __forceinline__ uint64_t umma_desc(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// kind::f16 instruction descriptor: float accumulator, bfloat16 A and B, both K-major, N >> 3 at bit 17, M >> 4 at bit 24
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+                   "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+                   "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+    return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+}
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
+
+struct TcArgs {
+    void* out;
+    int M, N, K;
+    int out_dtype, activation;
+    float softcap;
+    int* status;
+};
+
+template <int BN, bool GATED>
+__global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
+                                                                const __grid_constant__ CUtensorMap map_w, TcArgs a) {
+    constexpr int NB = GATED ? 2 : 1;
+    constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + NB * B_BYTES;
+    constexpr int TMEM_COLS = NB * BN;
+    static_assert(TMEM_COLS == 32 || TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "tensor memory is allocated in powers of two");
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], done_bar;
+    __shared__ uint32_t tmem_slot;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int kblocks = (a.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        mbar_init(smem_u32(&done_bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- loader ----
+            for (int kb = 0; kb < kblocks; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t parity = ((kb / STAGES) & 1) ^ 1;        // the first pass finds every stage free
+                if (!mbar_wait_bounded(smem_u32(&empty_bar[s]), parity)) { ok = false; break; }
+                const uint32_t full = smem_u32(&full_bar[s]);
+                unsigned char* stage = smem + (size_t)s * STAGE_BYTES;
+                mbar_expect_tx(full, STAGE_BYTES);
+                tma_load_2d(smem_u32(stage), &map_x, kb * BK, m0, full);
+                tma_load_2d(smem_u32(stage + A_BYTES), &map_w, kb * BK, n0, full);
+                if (GATED) tma_load_2d(smem_u32(stage + A_BYTES + B_BYTES), &map_w, kb * BK, a.N + n0, full);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- product issuer ----
+            constexpr uint32_t idesc = umma_idesc(BM, BN);
+            for (int kb = 0; kb < kblocks && ok; ++kb) {
+                const int s = kb % STAGES;
+                if (!mbar_wait_bounded(smem_u32(&full_bar[s]), (kb / STAGES) & 1)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k) {
+                    const uint32_t acc = (kb | k) != 0;
+                    umma(tmem_base, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, acc);
+                    if (GATED) umma(tmem_base + BN, umma_desc(a_addr + k * 32), umma_desc(b_addr + B_BYTES + k * 32), idesc, acc);
+                }
+                umma_commit(smem_u32(&empty_bar[s]));     // the stage is free once these products have read it
+            }
+            umma_commit(smem_u32(&done_bar));             // the accumulator is complete
+        }
+    } else {
+        // ---- epilogue: warp q of these four owns tensor-memory lanes [32 q, 32 q + 32) ----
+        const int q = warp & 3;
+        const int row = m0 + q * 32 + lane;
+        if (!mbar_wait_bounded(smem_u32(&done_bar), 0)) ok = false;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+            const bool vec = (a.N % 8) == 0;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                if (n0 + c0 >= a.N) break;                 // uniform over the warp
+                float v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + c0, v);
+                if (GATED) {
+                    float u[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + BN + c0, u);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = (a.activation == RDL_ACT_GELU_TANH ? gelu_tanh(v[i]) : silu(v[i])) * u[i];
+                }
+                if (a.softcap > 0.f) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = a.softcap * tanhf(v[i] / a.softcap);
+                }
+                if (row < a.M) {
+                    const long long base = (long long)row * a.N + n0 + c0;
+                    if (vec && n0 + c0 + 32 <= a.N) {
+                        if (a.out_dtype == RDL_BF16) {
+                            __nv_bfloat16* o = (__nv_bfloat16*)a.out + base;
+#pragma unroll
+                            for (int i = 0; i < 32; i += 8) {
+                                uint4 raw;
+                                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+                                h[0] = __floats2bfloat162_rn(v[i], v[i + 1]);
+                                h[1] = __floats2bfloat162_rn(v[i + 2], v[i + 3]);
+                                h[2] = __floats2bfloat162_rn(v[i + 4], v[i + 5]);
+                                h[3] = __floats2bfloat162_rn(v[i + 6], v[i + 7]);
+                                *reinterpret_cast<uint4*>(o + i) = raw;
+                            }
+                        } else {
+                            float* o = (float*)a.out + base;
+#pragma unroll
+                            for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                        }
+                    } else {
+                        for (int i = 0; i < 32; ++i)
+                            if (n0 + c0 + i < a.N) rdl_store(a.out, base + i, a.out_dtype, v[i]);
+                    }
+                }
+            }
+        }
+    }
+    if (!ok && a.status) atomicExch(a.status, 4);
+    // ---- tear-down, reached by every thread ----
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+}
+
+// tensor map of a row-major bfloat16 matrix [rows, cols]: boxes of 64 columns (128 bytes, swizzled) x box_rows rows
+int make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols, int box_rows) {
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    // The driver's encoder is looked up at run time, so that the library itself does not link against the
+    // driver and loads (for a build check, say) on a machine that has none.
+    typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeTiled encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult found;
+        RDL_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &found), "gemm_tc: looking up cuTensorMapEncodeTiled");
+        RDL_REQUIRE(found == cudaDriverEntryPointSuccess && fn, "gemm_tc: this driver has no cuTensorMapEncodeTiled");
+        encode = (EncodeTiled)fn;
+    }
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    RDL_REQUIRE(r == CUDA_SUCCESS, "gemm_tc: cuTensorMapEncodeTiled failed with driver error %d for a [%lld, %lld] matrix", (int)r, rows, cols);
+    return 0;
+}
+
+// weight matrices are constant: their maps are made once
+std::mutex g_map_mutex;
+std::map<std::tuple<const void*, long long, long long, int>, CUtensorMap> g_weight_maps;
+
+template <int BN, bool GATED>
+int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs& a, cudaStream_t st) {
+    constexpr int NB = GATED ? 2 : 1;
+    const int smem = STAGES * (BM * BK * 2 + NB * BN * BK * 2) + 1024;
+    static bool opted = false;
+    if (!opted) {
+        RDL_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "gemm_tc");
+        opted = true;
+    }
+    dim3 grid((a.N + BN - 1) / BN, (a.M + BM - 1) / BM);
+    gemm_tc_kernel<BN, GATED><<<grid, TC_THREADS, smem, st>>>(mx, mw, a);
+    RDL_CHECK_LAUNCH("gemm_tc");
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int rdl_gemm_tc(void* out, int out_dtype, const void* x, const void* w, int m, int n, int k,
+                           int gated, int activation, float softcap, int* status, void* stream) {
+    RDL_REQUIRE(out && x && w, "gemm_tc: missing operand");
+    RDL_REQUIRE(rdl_valid_dtype(out_dtype), "gemm_tc: bad output dtype %d", out_dtype);
+    RDL_REQUIRE(m >= 0 && n > 0 && k > 0 && k % 8 == 0, "gemm_tc: m=%d n=%d k=%d; k must be a multiple of 8", m, n, k);
+    RDL_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0,
+                "gemm_tc: operands must start on 16-byte boundaries");
+    RDL_REQUIRE(!gated || activation == RDL_ACT_GELU_TANH || activation == RDL_ACT_SILU, "gemm_tc: unknown activation %d", activation);
+    RDL_REQUIRE(softcap >= 0.f, "gemm_tc: soft-cap must not be negative");
+    RDL_REQUIRE((long long)((m + BM - 1) / BM) <= 65535, "gemm_tc: %d rows exceed the grid limit", m);
+    if (m == 0) return 0;
+    const int bn = gated ? 128 : 256;
+    CUtensorMap mx, mw;
+    if (int e = make_map(&mx, x, m, k, BM)) return e;
+    {
+        std::lock_guard<std::mutex> lock(g_map_mutex);
+        const auto key = std::make_tuple(w, (long long)(gated ? 2 * n : n), (long long)k, bn);
+        auto it = g_weight_maps.find(key);
+        if (it == g_weight_maps.end()) {
+            CUtensorMap fresh;
+            if (int e = make_map(&fresh, w, gated ? 2LL * n : n, k, bn)) return e;
+            it = g_weight_maps.emplace(key, fresh).first;
+        }
+        mw = it->second;
+    }
+    TcArgs a{out, m, n, k, out_dtype, activation, softcap, status};
+    cudaStream_t st = (cudaStream_t)stream;
+    return gated ? launch_tc<128, true>(mx, mw, a, st) : launch_tc<256, false>(mx, mw, a, st);
+}

@@ -23,7 +23,7 @@ from concurrent.futures import ThreadPoolExecutor
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(_PKG, "csrc")
 LIB_NAME = "librdl_b200_kernels.so"
-ABI_VERSION = 4
+ABI_VERSION = 5
 
 # fast math is never enabled: the 32-bit path relies on exact tanhf/expf/sqrtf and plain FMA
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -107,7 +107,7 @@ def _compile(build_dir, stamp):
         objs = list(pool.map(one, srcs))
     out = os.path.join(build_dir, LIB_NAME)
     tmp = out + f".{os.getpid()}.tmp"
-    r = subprocess.run([nvcc, "-shared", "-o", tmp, *objs, "-lcuda"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+    r = subprocess.run([nvcc, "-shared", "-o", tmp, *objs], stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
                        text=True, env=env, cwd=build_dir)
     if r.returncode != 0:
         raise KernelLibraryError(f"linking {LIB_NAME} failed:\n{r.stdout}")
@@ -177,6 +177,7 @@ _SIGNATURES = {
     "rdl_rope_cache": [_P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P],
     "rdl_gemm_f32": [_P, _P, _P, _I, _I, _I, _P],
     "rdl_gemm_skinny": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P],
+    "rdl_gemm_tc": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
     "rdl_sample": [_P, _P, _I, _I, ctypes.POINTER(SamplingArgs), _P, _P, _P, _P, _P, _P],
 }
 

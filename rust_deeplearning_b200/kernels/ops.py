@@ -8,6 +8,7 @@ raise.  Parts call them as `ops.<name>` (attribute lookup at call time).
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import NamedTuple, Optional, Tuple
 
 import torch
@@ -149,22 +150,43 @@ def convert_rows(x: torch.Tensor, out_dtype: torch.dtype, row_index: Optional[to
 # matrix products
 # ------------------------------------------------------------------------------------------
 
-SKINNY_MAX_ROWS = 16     # up to this many rows the library's own weight-streaming kernel runs
+SKINNY_MAX_ROWS = 16     # up to this many rows the weight-streaming kernel runs; above, the tcgen05 kernel
+# "tcgen05": the library's own TMA + tcgen05 kernel for products with many rows; "cublas": the library
+# product through torch (kept for comparison; set RDL_PREFILL_GEMM=cublas)
+PREFILL_GEMM = os.environ.get("RDL_PREFILL_GEMM", "tcgen05")
 
 
-def _skinny_ok(x, weight):
-    return (x.dtype is torch.bfloat16 and x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0
+def _bf16_ok(x, weight):
+    return (x.dtype is torch.bfloat16 and weight.dtype is torch.bfloat16 and x.shape[1] % 8 == 0
             and x.is_contiguous() and weight.is_contiguous() and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
+def _skinny_ok(x, weight):
+    return _bf16_ok(x, weight) and x.shape[0] <= SKINNY_MAX_ROWS
+
+
+def _gemm_bf16(x, weight, n_out, out_dtype, gated, activation, softcap, status):
+    """The library's own bfloat16 products: weight streaming for few rows, tcgen05 for many."""
+    out = torch.empty((x.shape[0], n_out), dtype=out_dtype, device=x.device)
+    lib = library.load()
+    if x.shape[0] <= SKINNY_MAX_ROWS:
+        library.check(lib.rdl_gemm_skinny(_ptr(out), _dtype_code(out), _ptr(x), _ptr(weight), x.shape[0], n_out, x.shape[1],
+                                          int(gated), activation, float(softcap or 0.0), _stream(x)))
+    else:
+        library.check(lib.rdl_gemm_tc(_ptr(out), _dtype_code(out), _ptr(x), _ptr(weight), x.shape[0], n_out, x.shape[1],
+                                      int(gated), activation, float(softcap or 0.0), _ptr(status), _stream(x)))
+    return out
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-           softcap: Optional[float] = None):
+           softcap: Optional[float] = None, status: Optional[torch.Tensor] = None):
     """x [rows, in] times weight [out, in] transposed; optionally cap * tanh(. / cap) on the result.
 
     float32: the library's own FMA kernel (no tensor cores, no reduced-precision mode).
-    bfloat16, up to 16 rows (decode): the library's weight-streaming tensor-core kernel with the
-    soft-cap in its epilogue.  bfloat16, more rows: a library matrix product with float32
-    accumulation (cuBLAS through torch), where the reference's engine calls a GEMM library as well."""
+    bfloat16: up to 16 rows (decode) the weight-streaming tensor-core kernel, above that the TMA +
+    tcgen05 kernel, both with float accumulation and the soft-cap in their epilogue.  Operands that do
+    not meet their alignment rules go to a library product (cuBLAS through torch), which is what the
+    reference's engine uses for all its products."""
     _need(x.dim() == 2 and weight.dim() == 2 and x.shape[1] == weight.shape[1],
           f"linear: shapes {tuple(x.shape)} and {tuple(weight.shape)} do not fit")
     _need(x.dtype is weight.dtype, f"linear: input is {x.dtype}, weight is {weight.dtype}")
@@ -176,11 +198,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
         out = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.float32, device=x.device)
         library.check(library.load().rdl_gemm_f32(_ptr(out), _ptr(x), _ptr(weight), x.shape[0], weight.shape[0],
                                                   x.shape[1], _stream(x)))
-    elif _skinny_ok(x, weight):
-        out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=x.device)
-        library.check(library.load().rdl_gemm_skinny(_ptr(out), _dtype_code(out), _ptr(x), _ptr(weight), x.shape[0],
-                                                     weight.shape[0], x.shape[1], 0, 0, float(softcap or 0.0), _stream(x)))
-        return out
+    elif _bf16_ok(x, weight) and (x.shape[0] <= SKINNY_MAX_ROWS or PREFILL_GEMM == "tcgen05"):
+        return _gemm_bf16(x, weight, weight.shape[0], out_dtype, False, 0, softcap, status)
     else:
         _need(x.is_cuda, "kernels run on CUDA tensors only; there is no CPU path")
         out = torch.mm(x, weight.t(), out_dtype=torch.float32) if out_dtype is torch.float32 else torch.mm(x, weight.t())
@@ -189,18 +208,14 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     return out
 
 
-def linear_gated(x: torch.Tensor, weight_gate_up: torch.Tensor, activation: str):
+def linear_gated(x: torch.Tensor, weight_gate_up: torch.Tensor, activation: str, status: Optional[torch.Tensor] = None):
     """act(x Wg^T) * (x Wu^T) for the row-concatenated matrix [Wg; Wu] ([2I, in]) -> [rows, I].
-    Up to 16 bfloat16 rows this is one kernel; otherwise a product and the gated activation kernel."""
+    In bfloat16 this is one kernel (the activation is the product's epilogue); otherwise a product
+    and the gated activation kernel."""
     _need(activation in ACTIVATIONS, f"unknown activation '{activation}', known: {sorted(ACTIVATIONS)}")
     _need(weight_gate_up.shape[0] % 2 == 0, "linear_gated: the weight must hold gate rows and as many up rows")
-    if x.dtype is torch.bfloat16 and x.dtype is weight_gate_up.dtype and _skinny_ok(x, weight_gate_up):
-        inter = weight_gate_up.shape[0] // 2
-        out = torch.empty((x.shape[0], inter), dtype=x.dtype, device=x.device)
-        library.check(library.load().rdl_gemm_skinny(_ptr(out), _dtype_code(out), _ptr(x), _ptr(weight_gate_up),
-                                                     x.shape[0], inter, x.shape[1], 1, ACTIVATIONS[activation], 0.0,
-                                                     _stream(x)))
-        return out
+    if _bf16_ok(x, weight_gate_up) and (x.shape[0] <= SKINNY_MAX_ROWS or PREFILL_GEMM == "tcgen05"):
+        return _gemm_bf16(x, weight_gate_up, weight_gate_up.shape[0] // 2, x.dtype, True, ACTIVATIONS[activation], None, status)
     return gated_activation(linear(x, weight_gate_up), activation)
 
 

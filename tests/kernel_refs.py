@@ -75,14 +75,14 @@ def convert_rows(x, out_dtype, row_index=None):
     return v.to(out_dtype)
 
 
-def linear(x, weight, out_dtype=None, softcap=None):
+def linear(x, weight, out_dtype=None, softcap=None, status=None):
     z = x.to(F64) @ weight.to(F64).t()
     if softcap is not None:
         z = softcap * torch.tanh(z / softcap)
     return z.to(out_dtype or x.dtype)
 
 
-def linear_gated(x, weight_gate_up, activation):
+def linear_gated(x, weight_gate_up, activation, status=None):
     return gated_activation(x.to(F64) @ weight_gate_up.to(F64).t(), activation).to(x.dtype)
 
 

@@ -22,14 +22,15 @@ def rnd(shape, dtype, seed, scale=1.0):
     return (torch.randn(shape, generator=g) * scale).to(dtype).to(DEV)
 
 
-def assert_close(got, want, dtype, rel=4.0, what=""):
+def assert_close(got, want, dtype, rel=4.0, what="", f32_tol=2e-5):
     """float32 results agree to ~1e-5 relative to the tensor's scale; bfloat16 results to a few
-    units of bfloat16 rounding of that scale."""
+    units of bfloat16 rounding of that scale.  Products that sum thousands of terms in float32 pass
+    f32_tol = 1e-4: 2048 terms x 2^-24 per addition bounds the sum's rounding at 1.2e-4 of its scale."""
     got, want = got.double().cpu(), want.double().cpu()
     assert got.shape == want.shape, (got.shape, want.shape)
     assert torch.isfinite(got).all(), f"{what}: non-finite output"
     scale = max(want.abs().max().item(), 1e-6)
-    tol = (2e-5 if dtype is torch.float32 else rel * BF16_EPS) * scale
+    tol = (f32_tol if dtype is torch.float32 else rel * BF16_EPS) * scale
     err = (got - want).abs().max().item()
     assert err <= tol, f"{what}: max error {err:.3e} > {tol:.3e} (scale {scale:.3e})"
 
@@ -116,11 +117,27 @@ def test_skinny_gemm(m, n, k):
     wgu = rnd((2 * n, k), torch.bfloat16, 15, 0.2)
     for act in ("gelu_pytorch_tanh", "silu"):
         assert_close(ops.linear_gated(x, wgu, act), ref.linear_gated(x, wgu, act), torch.bfloat16, what=f"gated {act}")
-    # more rows than the kernel takes: the library product and the activation kernel give the same
+    # the library product and the activation kernel (the route of operands the own kernels do not take) give the same
     x17 = rnd((17, k), torch.bfloat16, 16)
     assert not ops._skinny_ok(x17, w)
-    assert_close(ops.linear_gated(x17, wgu, "gelu_pytorch_tanh"), ref.linear_gated(x17, wgu, "gelu_pytorch_tanh"),
-                 torch.bfloat16, what="gated, many rows")
+    assert_close(ops.gated_activation(torch.mm(x17, wgu.t()), "gelu_pytorch_tanh"), ref.linear_gated(x17, wgu, "gelu_pytorch_tanh"),
+                 torch.bfloat16, what="gated, library product")
+
+
+@pytest.mark.parametrize("m", [17, 128, 200, 2048])
+@pytest.mark.parametrize("n,k", [(256, 64), (384, 96), (131, 80), (2304, 2048), (520, 1160)])
+def test_tcgen05_gemm(m, n, k):
+    """The TMA + tcgen05 kernel for many rows: tiles, tails in every dimension, all epilogues."""
+    x, w = rnd((m, k), torch.bfloat16, 17), rnd((n, k), torch.bfloat16, 18, 0.2)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    assert ops.PREFILL_GEMM == "tcgen05" and not ops._skinny_ok(x, w)
+    assert_close(ops.linear(x, w, status=status), ref.linear(x, w), torch.bfloat16, what="plain")
+    assert_close(ops.linear(x, w, out_dtype=torch.float32, softcap=3.0, status=status), ref.linear(x, w, torch.float32, softcap=3.0),
+                 torch.float32, what="float32 out, soft-cap", f32_tol=1e-4)
+    wgu = rnd((2 * n, k), torch.bfloat16, 19, 0.2)
+    for act in ("gelu_pytorch_tanh", "silu"):
+        assert_close(ops.linear_gated(x, wgu, act, status=status), ref.linear_gated(x, wgu, act), torch.bfloat16, what=f"gated {act}")
+    assert status.item() == 0
 
 
 # ------------------------------------------------------------------------------------------
