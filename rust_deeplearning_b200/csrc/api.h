@@ -10,7 +10,7 @@ extern "C" {
 #define RDL_ACT_GELU_TANH 0
 #define RDL_ACT_SILU 1
 
-#define RDL_ABI_VERSION 5
+#define RDL_ABI_VERSION 6
 
 const char* rdl_last_error(void);
 int rdl_abi_version(void);
@@ -48,6 +48,9 @@ typedef struct {
 int rdl_attention_plain(const AttentionArgs* a, void* stream);
 int rdl_attention_prefill(const AttentionArgs* a, void* stream);
 int rdl_attention_decode(const AttentionArgs* a, void* stream);
+// prefill attention on tcgen05 tensor cores for sequences that start at position 0 and head sizes that are
+// multiples of 64; q, k_new and v_new must be the packed rows of one [tokens, row_width] buffer
+int rdl_attention_prefill_tc(const AttentionArgs* a, long long row_width, void* stream);
 long long rdl_attention_decode_counter_bytes(int n_tokens, int n_kv_heads);
 long long rdl_attention_decode_scratch_bytes(int n_tokens, int n_heads, int n_kv_heads, int head_dim, int max_splits);
 

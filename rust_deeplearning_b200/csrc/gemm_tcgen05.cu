@@ -28,7 +28,7 @@
 
 namespace {
 
-constexpr int BM = 128, BK = 64, STAGES = 4, TC_THREADS = 192;
+constexpr int BM = 128, BK = 64, TC_THREADS = 192;
 constexpr long long WAIT_CYCLES = 2000000000LL;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -85,10 +85,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// The activation feeds a bfloat16 result (8 bits of mantissa), so the hardware tanh (relative error about
+// 2^-11) and the fast exponential are accurate enough here and keep the epilogue short.
 __device__ __forceinline__ float gelu_tanh(float x) {
-    return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    return 0.5f * x * (1.0f + t);
 }
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
 
 struct TcArgs {
     void* out;
@@ -98,12 +102,15 @@ struct TcArgs {
     int* status;
 };
 
-template <int BN, bool GATED>
+// MT: row tiles of 128 a block computes (1 or 2).  Two tiles share every weight tile that is loaded,
+// which halves the bytes fetched per product: a 256 x 256 tile needs 64 KB of operands for 8.4 MFLOP.
+template <int BN, bool GATED, int MT>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                 const __grid_constant__ CUtensorMap map_w, TcArgs a) {
     constexpr int NB = GATED ? 2 : 1;
-    constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + NB * B_BYTES;
-    constexpr int TMEM_COLS = NB * BN;
+    constexpr int STAGES = MT == 2 ? 3 : 4;
+    constexpr int A_BYTES = MT * BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + NB * B_BYTES;
+    constexpr int TMEM_COLS = MT * NB * BN;
     static_assert(TMEM_COLS == 32 || TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "tensor memory is allocated in powers of two");
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -111,7 +118,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     __shared__ uint32_t tmem_slot;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int m0 = blockIdx.y * (MT * BM), n0 = blockIdx.x * BN;
     const int kblocks = (a.K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -160,8 +167,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
 #pragma unroll
                 for (int k = 0; k < BK / 16; ++k) {
                     const uint32_t acc = (kb | k) != 0;
-                    umma(tmem_base, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, acc);
-                    if (GATED) umma(tmem_base + BN, umma_desc(a_addr + k * 32), umma_desc(b_addr + B_BYTES + k * 32), idesc, acc);
+#pragma unroll
+                    for (int h = 0; h < MT; ++h) {
+                        const uint64_t adesc = umma_desc(a_addr + h * (BM * BK * 2) + k * 32);
+                        umma(tmem_base + h * NB * BN, adesc, umma_desc(b_addr + k * 32), idesc, acc);
+                        if (GATED) umma(tmem_base + h * NB * BN + BN, adesc, umma_desc(b_addr + B_BYTES + k * 32), idesc, acc);
+                    }
                 }
                 umma_commit(smem_u32(&empty_bar[s]));     // the stage is free once these products have read it
             }
@@ -170,19 +181,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     } else {
         // ---- epilogue: warp q of these four owns tensor-memory lanes [32 q, 32 q + 32) ----
         const int q = warp & 3;
-        const int row = m0 + q * 32 + lane;
         if (!mbar_wait_bounded(smem_u32(&done_bar), 0)) ok = false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok) {
-            const bool vec = (a.N % 8) == 0;
+        const bool vec = (a.N % 8) == 0;
+#pragma unroll 1
+        for (int h = 0; h < MT && ok; ++h) {
+            const int row = m0 + h * BM + q * 32 + lane;
+            if (m0 + h * BM >= a.M) break;                 // uniform over the block
+            const uint32_t tcol = tmem_base + ((uint32_t)(q * 32) << 16) + h * NB * BN;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 if (n0 + c0 >= a.N) break;                 // uniform over the warp
                 float v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + c0, v);
+                tmem_ld32(tcol + c0, v);
                 if (GATED) {
                     float u[32];
-                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + BN + c0, u);
+                    tmem_ld32(tcol + BN + c0, u);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = (a.activation == RDL_ACT_GELU_TANH ? gelu_tanh(v[i]) : silu(v[i])) * u[i];
                 }
@@ -255,17 +269,18 @@ int make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols, 
 std::mutex g_map_mutex;
 std::map<std::tuple<const void*, long long, long long, int>, CUtensorMap> g_weight_maps;
 
-template <int BN, bool GATED>
+template <int BN, bool GATED, int MT>
 int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs& a, cudaStream_t st) {
     constexpr int NB = GATED ? 2 : 1;
-    const int smem = STAGES * (BM * BK * 2 + NB * BN * BK * 2) + 1024;
+    constexpr int STAGES = MT == 2 ? 3 : 4;
+    const int smem = STAGES * (MT * BM * BK * 2 + NB * BN * BK * 2) + 1024;
     static bool opted = false;
     if (!opted) {
-        RDL_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "gemm_tc");
+        RDL_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, GATED, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "gemm_tc");
         opted = true;
     }
-    dim3 grid((a.N + BN - 1) / BN, (a.M + BM - 1) / BM);
-    gemm_tc_kernel<BN, GATED><<<grid, TC_THREADS, smem, st>>>(mx, mw, a);
+    dim3 grid((a.N + BN - 1) / BN, (a.M + MT * BM - 1) / (MT * BM));
+    gemm_tc_kernel<BN, GATED, MT><<<grid, TC_THREADS, smem, st>>>(mx, mw, a);
     RDL_CHECK_LAUNCH("gemm_tc");
     return 0;
 }
@@ -284,8 +299,11 @@ extern "C" int rdl_gemm_tc(void* out, int out_dtype, const void* x, const void* 
     RDL_REQUIRE((long long)((m + BM - 1) / BM) <= 65535, "gemm_tc: %d rows exceed the grid limit", m);
     if (m == 0) return 0;
     const int bn = gated ? 128 : 256;
+    // two row tiles a block when that still fills most of the 148 multiprocessors
+    const long long tiles2 = (long long)((n + bn - 1) / bn) * ((m + 2 * BM - 1) / (2 * BM));
+    const int mt = tiles2 >= 120 ? 2 : 1;
     CUtensorMap mx, mw;
-    if (int e = make_map(&mx, x, m, k, BM)) return e;
+    if (int e = make_map(&mx, x, m, k, mt * BM)) return e;
     {
         std::lock_guard<std::mutex> lock(g_map_mutex);
         const auto key = std::make_tuple(w, (long long)(gated ? 2 * n : n), (long long)k, bn);
@@ -299,5 +317,6 @@ extern "C" int rdl_gemm_tc(void* out, int out_dtype, const void* x, const void* 
     }
     TcArgs a{out, m, n, k, out_dtype, activation, softcap, status};
     cudaStream_t st = (cudaStream_t)stream;
-    return gated ? launch_tc<128, true>(mx, mw, a, st) : launch_tc<256, false>(mx, mw, a, st);
+    if (mt == 2) return gated ? launch_tc<128, true, 2>(mx, mw, a, st) : launch_tc<256, false, 2>(mx, mw, a, st);
+    return gated ? launch_tc<128, true, 1>(mx, mw, a, st) : launch_tc<256, false, 1>(mx, mw, a, st);
 }

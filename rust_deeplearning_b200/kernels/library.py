@@ -23,7 +23,7 @@ from concurrent.futures import ThreadPoolExecutor
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(_PKG, "csrc")
 LIB_NAME = "librdl_b200_kernels.so"
-ABI_VERSION = 5
+ABI_VERSION = 6
 
 # fast math is never enabled: the 32-bit path relies on exact tanhf/expf/sqrtf and plain FMA
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -168,6 +168,7 @@ _SIGNATURES = {
     "rdl_attention_plain": [ctypes.POINTER(AttentionArgs), _P],
     "rdl_attention_prefill": [ctypes.POINTER(AttentionArgs), _P],
     "rdl_attention_decode": [ctypes.POINTER(AttentionArgs), _P],
+    "rdl_attention_prefill_tc": [ctypes.POINTER(AttentionArgs), _LL, _P],
     "rdl_embed_rows": [_P, _P, _I, _P, _F, _I, _I, _I, _P, _P],
     "rdl_norm_residual_norm": [_P, _I, _P, _P, _I, _F, _F, _P, _P, _I, _F, _F, _P, _I, _I, _I, _P],
     "rdl_gated_activation": [_P, _P, _I, _I, _I, _I, _P],

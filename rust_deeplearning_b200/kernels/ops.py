@@ -320,8 +320,9 @@ def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n
     query heads; the row stride may be larger (packed q/k/v rows).
     new_kv: (rows, k_col, v_col) - this step's packed rows and the columns at which the rotated
     keys and the values start; needed when `b.seq_cached` says that new keys are not in the cache.
-    kind: "plain" (float arithmetic, any dtype), "prefill" (bfloat16, tensor cores), "decode"
-    (bfloat16, split keys; reads the cache only), or "auto".
+    kind: "plain" (float arithmetic, any dtype), "prefill" (bfloat16, mma.sync tensor cores, keys from
+    cache and packed rows), "prefill_tc" (bfloat16, TMA + tcgen05, for sequences that start at position 0
+    with head_dim a multiple of 64), "decode" (bfloat16, split keys; reads the cache only), or "auto".
     scratch: callable(nbytes) -> zero-initialised float32 tensor that only this kernel writes, for
     the decode kernel's counters and partial results.  status: int32 tensor that a kernel sets
     non-zero when it gives up on a bounded wait.
@@ -348,10 +349,16 @@ def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n
     lib = library.load()
     if kind == "plain":
         library.check(lib.rdl_attention_plain(ctypes.byref(a), _stream(q)))
-    elif kind == "prefill":
+    elif kind in ("prefill", "prefill_tc"):
         _need(b.tile_seq is not None and b.tile_q0 is not None, "attention: prefill needs query tiles")
         a.tile_seq, a.tile_q0, a.n_tiles = b.tile_seq.data_ptr(), b.tile_q0.data_ptr(), b.n_tiles
-        library.check(lib.rdl_attention_prefill(ctypes.byref(a), _stream(q)))
+        if kind == "prefill_tc":
+            # sequences that start at position 0, packed q/k/v rows, head_dim a multiple of 64
+            _need(new_kv is not None and new_kv[0] is q, "attention: the tcgen05 prefill kernel reads packed q/k/v rows")
+            a.status = status.data_ptr() if status is not None else None
+            library.check(lib.rdl_attention_prefill_tc(ctypes.byref(a), q.stride(0), _stream(q)))
+        else:
+            library.check(lib.rdl_attention_prefill(ctypes.byref(a), _stream(q)))
     elif kind == "decode":
         _need(pages is not None, "attention: decode reads the cache")
         ks = keys_per_split or choose_keys_per_split(b.n_tokens, n_kv_heads, b.max_keys, pages.page_size)

@@ -109,8 +109,13 @@ class Attention:
                     self.position.rotate(qkv, nh, nkv, hd, batch)
                 write_first = False
             ab = batch.attention_batch("past", self.window)
-            ctx = ops.attention(qkv, ab, pages, new_kv=(qkv, self.q_width, self.q_width + self.kv_width),
-                                kind="prefill" if fast and batch.n_tiles else "plain", **common)
+            if fast and batch.n_tiles:
+                # prompts that start at position 0 read nothing from the cache: the tcgen05 kernel takes them
+                kind = "prefill_tc" if (hd % 64 == 0 and not batch.has_past) else "prefill"
+            else:
+                kind = "plain"
+            ctx = ops.attention(qkv, ab, pages, new_kv=(qkv, self.q_width, self.q_width + self.kv_width), kind=kind,
+                                status=batch.status, **common)
             if not write_first:
                 ops.rope_cache(qkv, nh, nkv, hd, tok_seq=batch.tok_seq, tok_pos=batch.tok_pos, pages=pages,
                                seq_end=batch.seq_end)

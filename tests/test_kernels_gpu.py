@@ -239,6 +239,31 @@ def test_attention_over_cache_and_new_rows(shape, dtype, kind):
         assert_close(got, want, dtype, rel=6.0, what=f"{kind} softcap={softcap}")
 
 
+TC_SHAPES = [
+    dict(new=[1], n_heads=1, n_kv_heads=1, head_dim=64, window=None),
+    dict(new=[5, 129, 70], n_heads=4, n_kv_heads=2, head_dim=64, window=None),
+    dict(new=[300, 33, 128], n_heads=6, n_kv_heads=1, head_dim=128, window=100),
+    dict(new=[257, 64], n_heads=8, n_kv_heads=4, head_dim=256, window=None),
+    dict(new=[700], n_heads=2, n_kv_heads=2, head_dim=256, window=130),
+    dict(new=[130, 1, 260], n_heads=3, n_kv_heads=3, head_dim=192, window=64),
+]
+
+
+@pytest.mark.parametrize("shape", TC_SHAPES)
+def test_tcgen05_prefill_attention(shape):
+    """The TMA + tcgen05 prefill kernel (prompts that start at position 0) against the plain reference."""
+    shape = dict(shape)
+    new = shape.pop("new")
+    c = Case(past=[0] * len(new), new=new, dtype=torch.bfloat16, seed=35, page_size=64, **shape)
+    b = c.batch("past")
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for softcap in (None, 5.0):
+        got = ops.attention(c.qkv, b, c.pages, new_kv=c.new_kv(), kind="prefill_tc", status=status, **c.kw(softcap=softcap))
+        want = ref.attention(c.qkv, b, c.pages, new_kv=c.new_kv(), **c.kw(softcap=softcap))
+        assert status.item() == 0
+        assert_close(got, want, torch.bfloat16, rel=6.0, what=f"tcgen05 prefill softcap={softcap}")
+
+
 DECODE_SHAPES = [
     dict(past=[0, 63, 64, 700], n_heads=8, n_kv_heads=4, head_dim=256, page_size=64, window=None),
     dict(past=[5, 1000, 300], n_heads=6, n_kv_heads=1, head_dim=32, page_size=16, window=None),
