@@ -101,6 +101,11 @@ __device__ __forceinline__ float tanh_fast(float x) {
     asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ float exp2_fast(float x) {      // 2^x, -inf gives 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
 struct TcAttnArgs {
     void* out; long long out_stride;
@@ -223,7 +228,11 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
         const int pr = q0 + r;                                   // the row's position in its sequence
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
         const float LOG2E = 1.4426950408889634f;
-        const float inv_cap = a.softcap > 0.f ? 1.0f / a.softcap : 0.f;
+        // score -> base-2 logit: with a soft-cap, tanh(s * scale / cap) * cap * log2(e); else s * scale * log2(e)
+        const bool capped = a.softcap > 0.f;
+        const float c_in = capped ? a.score_scale / a.softcap : a.score_scale * LOG2E;
+        const float c_out = a.softcap * LOG2E;
+        const int pr_warp_first = q0 + q * 32, pr_warp_last = pr_warp_first + 31;
         float m_ref = -INFINITY, l = 0.f;
         for (int j = 0; j < n_kv && ok; ++j) {
             if (!mbar_wait_bounded(smem_u32(&s_full), j & 1)) { ok = false; break; }
@@ -242,24 +251,35 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&s_empty));      // the score buffer may be overwritten
             const int key0 = kv_first + j * KN;
-            float mx = -INFINITY;
+            if (capped) {
 #pragma unroll
-            for (int i = 0; i < KN; ++i) {
-                float v = t[i] * a.score_scale;
-                if (a.softcap > 0.f) v = a.softcap * tanh_fast(v * inv_cap);
-                v *= LOG2E;
-                const int key = key0 + i;
-                if (key > pr || (a.window > 0 && pr - key >= a.window)) v = -INFINITY;
-                t[i] = v;
-                mx = fmaxf(mx, v);
+                for (int i = 0; i < KN; ++i) t[i] = tanh_fast(t[i] * c_in) * c_out;
+            } else {
+#pragma unroll
+                for (int i = 0; i < KN; ++i) t[i] *= c_in;
             }
+            // tiles that every row of this warp sees whole need no masks (the test is the same for all lanes)
+            const bool interior = key0 + KN - 1 <= pr_warp_first && (a.window == 0 || pr_warp_last - key0 < a.window);
+            if (!interior) {
+                const int hi = pr - key0, lo = a.window > 0 ? pr - a.window + 1 - key0 : -1;   // tile columns [lo, hi] are visible
+#pragma unroll
+                for (int i = 0; i < KN; ++i)
+                    if (i > hi || i < lo) t[i] = -INFINITY;
+            }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < KN; i += 4) {
+                mx4[0] = fmaxf(mx4[0], t[i]); mx4[1] = fmaxf(mx4[1], t[i + 1]);
+                mx4[2] = fmaxf(mx4[2], t[i + 2]); mx4[3] = fmaxf(mx4[3], t[i + 3]);
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // P V of the tile before must be finished before its probabilities are overwritten or O is touched
             if (j > 0 && !mbar_wait_bounded(smem_u32(&pv_done), (j - 1) & 1)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const bool grow = mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
             if (__any_sync(0xffffffffu, grow)) {
                 const float m_new = grow ? mx : m_ref;
-                const float factor = (grow && m_ref > -INFINITY) ? exp2f(m_ref - m_new) : 1.0f;
+                const float factor = (grow && m_ref > -INFINITY) ? exp2_fast(m_ref - m_new) : 1.0f;
                 if (j > 0) {
                     for (int c = 0; c < hd; c += 32) {
                         float o[32];
@@ -274,13 +294,13 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
                 m_ref = m_new;
             }
             const float ms = m_ref == -INFINITY ? 0.f : m_ref;
-            float rs = 0.f;
+            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
             unsigned char* prow = sP + r * 128;
 #pragma unroll
             for (int c = 0; c < KN / 8; ++c) {
                 float e[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) { e[i] = exp2f(t[c * 8 + i] - ms); rs += e[i]; }
+                for (int i = 0; i < 8; ++i) { e[i] = exp2_fast(t[c * 8 + i] - ms); rs4[i & 3] += e[i]; }
                 uint4 raw;
                 __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&raw);
                 hp[0] = __floats2bfloat162_rn(e[0], e[1]);
@@ -289,7 +309,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
                 hp[3] = __floats2bfloat162_rn(e[6], e[7]);
                 *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) * 16)) = raw;
             }
-            l += rs;
+            l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // the tensor core reads these writes
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();

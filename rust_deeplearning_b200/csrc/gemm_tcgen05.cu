@@ -7,7 +7,7 @@
 // accumulating in tensor memory; tcgen05.commit hands stages back to the loader and the finished
 // accumulator to the epilogue warps, which read it with tcgen05.ld, apply the epilogue in float and
 // store.  Warp roles: warp 0 loads, warp 1 allocates tensor memory and issues the products, warps
-// 2-5 (one per 32-lane quarter of tensor memory) do the epilogue.
+// 2-9 do the epilogue (two per 32-lane quarter of tensor memory, half of the columns each).
 //
 // Epilogues: store as bfloat16 or float; cap * tanh(v / cap); and, for a row-concatenated
 // [gate; up] matrix, act(gate) * up with both accumulators side by side in tensor memory, which
@@ -28,7 +28,7 @@
 
 namespace {
 
-constexpr int BM = 128, BK = 64, TC_THREADS = 192;
+constexpr int BM = 128, BK = 64, TC_THREADS = 320;
 constexpr long long WAIT_CYCLES = 2000000000LL;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -181,6 +181,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     } else {
         // ---- epilogue: warp q of these four owns tensor-memory lanes [32 q, 32 q + 32) ----
         const int q = warp & 3;
+        const int col_half = (warp - 2) >> 2;              // two warps share a quarter: each takes half of the columns
         if (!mbar_wait_bounded(smem_u32(&done_bar), 0)) ok = false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const bool vec = (a.N % 8) == 0;
@@ -190,7 +191,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
             if (m0 + h * BM >= a.M) break;                 // uniform over the block
             const uint32_t tcol = tmem_base + ((uint32_t)(q * 32) << 16) + h * NB * BN;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = col_half * (BN / 2); c0 < (col_half + 1) * (BN / 2); c0 += 32) {
                 if (n0 + c0 >= a.N) break;                 // uniform over the warp
                 float v[32];
                 tmem_ld32(tcol + c0, v);
