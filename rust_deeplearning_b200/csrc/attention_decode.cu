@@ -6,9 +6,10 @@
 // values, each contiguous in the cache - is brought into shared memory by two bulk asynchronous
 // copies (TMA, cp.async.bulk + mbarrier).  The cache stores the 16-byte chunks of a row swizzled
 // by the row's place in its page (common.cuh), so the copied block is read by ldmatrix without
-// bank conflicts as it is.  The heads of the group are the rows of a 16-row query tile:
-// scores and P.V run on the tensor cores (mma.sync m16n8k16, float accumulators), each warp
-// taking 16 keys of the page; soft-cap, softmax state and output sums are float.
+// bank conflicts as it is.  The products run on the tensor cores (mma.sync m16n8k16, float
+// accumulators) with the keys as rows and the (up to 8) heads of the group as columns:
+// S^T = K Q^T and O^T += V^T P^T, each warp taking 16 keys of the page; soft-cap, softmax state
+// and output sums are float.
 //
 // A token with a single run writes its output directly.  Otherwise every block writes its
 // unnormalised partial result to scratch and the block that finishes last for a (token, kv head)
@@ -29,7 +30,7 @@ namespace {
 
 constexpr int DEC_THREADS = 128;
 constexpr int DEC_WARPS = DEC_THREADS / 32;
-constexpr int QROWS = 16;                         // rows of the query tile = most heads per kv head
+constexpr int QROWS = 8;                          // most query heads per kv head: the columns of one score product
 constexpr long long WAIT_CYCLES = 2000000000LL;
 
 __device__ __forceinline__ float tanh_fast(float x) {
@@ -86,9 +87,8 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
 // HD: head_dim padded to 64, 128 or 256 (head_dim itself is a multiple of 16).
 template <int HD>
 __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(AttentionArgs a) {
-    constexpr int QROWB = HD * 2 + 16;            // bytes between rows of the query tile (padded: no bank conflicts)
     extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ __align__(8) unsigned long long bar_storage;
+    __shared__ __align__(8) unsigned long long bar_storage[2];     // keys, values
     __shared__ float sm_m[DEC_WARPS][QROWS], sm_l[DEC_WARPS][QROWS];
     __shared__ int s_flag;
 
@@ -108,14 +108,13 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
     const int quad = lane >> 2, tq = lane & 3;
     const __nv_bfloat16* kcache = (const __nv_bfloat16*)a.k_cache;
     const __nv_bfloat16* vcache = (const __nv_bfloat16*)a.v_cache;
-    unsigned char* q_tile = smem;
-    unsigned char* k_tile = smem + QROWS * QROWB;                 // [page_size][head_dim] as stored: chunks swizzled by row
+    unsigned char* k_tile = smem;                                 // [page_size][head_dim] as stored: chunks swizzled by row
     unsigned char* v_tile = k_tile + (size_t)ps * hd * 2;
     const int chunks = hd / 8;
-    const uint32_t q_s = (uint32_t)__cvta_generic_to_shared(q_tile);
     const uint32_t k_s = (uint32_t)__cvta_generic_to_shared(k_tile);
     const uint32_t v_s = (uint32_t)__cvta_generic_to_shared(v_tile);
-    const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&bar_storage);
+    const uint32_t bar_k = (uint32_t)__cvta_generic_to_shared(&bar_storage[0]);
+    const uint32_t bar_v = (uint32_t)__cvta_generic_to_shared(&bar_storage[1]);
     const uint32_t row_bytes = (uint32_t)hd * 2;
 
     const int page_first = k_begin / ps, page_last = (k_end - 1) / ps;
@@ -129,46 +128,115 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
         asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(kcache + off), "r"(ps * row_bytes) : "memory");
         asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(vcache + off), "r"(ps * row_bytes) : "memory");
     }
-    if (tid == 0) mbar_init(bar, 1);
+    if (tid == 0) {
+        mbar_init(bar_k, 1);
+        mbar_init(bar_v, 1);
+    }
+    __syncthreads();   // nobody waits on the barrier before it is initialised
     rdl_grid_wait();
     rdl_grid_launch_dependents();
-    // query tile: row h = head g * G + h of this token, rows from G on are zero
-    for (int idx = tid; idx < QROWS * (HD / 8); idx += DEC_THREADS) {
-        const int r = idx / (HD / 8), c = idx - r * (HD / 8);
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < G && c * 8 < hd)
-            v = *(const uint4*)((const __nv_bfloat16*)a.q + (long long)t * a.q_stride + (long long)(g * G + r) * hd + c * 8);
-        *(uint4*)(q_tile + r * QROWB + c * 16) = v;
-    }
-    __syncthreads();
-
-    float o[HD / 8][4];
-#pragma unroll
-    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-    const float LOG2E = 1.4426950408889634f;
-    const float inv_cap = a.softcap > 0.f ? 1.0f / a.softcap : 0.f;
+    // The products are formed with the keys as rows: S^T [16 keys x 8 heads] = K [16 x d] Q^T [d x 8] and
+    // O^T [d x 8 heads] += V^T [d x 16 keys] P^T [16 x 8].  Q^T is the B operand of every score product
+    // of this block; it stays in registers: for k-step kk, {Q[head quad][16 kk + 2 tq .. +1], Q[..][16 kk + 8 + 2 tq .. +1]}.
     const int ksteps = hd / 16;
+    uint32_t qf[HD / 16][2];
+    {
+        const __nv_bfloat16* qrow = (const __nv_bfloat16*)a.q + (long long)t * a.q_stride + (long long)(g * G + quad) * hd;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+            qf[kk][0] = qf[kk][1] = 0u;
+            if (quad < G && kk < ksteps) {
+                qf[kk][0] = *reinterpret_cast<const uint32_t*>(qrow + 16 * kk + 2 * tq);
+                qf[kk][1] = *reinterpret_cast<const uint32_t*>(qrow + 16 * kk + 8 + 2 * tq);
+            }
+        }
+    }
+    // O^T accumulators: block db holds d = 16 db + quad (+ 8) for heads 2 tq, 2 tq + 1
+    float o[HD / 16][4];
+#pragma unroll
+    for (int i = 0; i < HD / 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;      // of heads 2 tq and 2 tq + 1
+    const float LOG2E = 1.4426950408889634f;
+    const bool capped = a.softcap > 0.f;
+    const float c_in = capped ? a.score_scale / a.softcap : a.score_scale * LOG2E;
+    const float c_out = a.softcap * LOG2E;
 
+    // A page's keys and its values are each one contiguous block: one bulk copy each (issued by thread 0).
+    // The copies of the next page are issued as soon as this page's tile is free: its keys travel while
+    // P V of this page is computed, its values while the next scores are.
+    auto issue = [&](int lp, bool values) {
+        const int page = table[lp % a.ring_pages];
+        const long long off = ((long long)page * a.n_kv_heads + g) * ps * hd;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_expect_tx(values ? bar_v : bar_k, ps * row_bytes);
+        bulk_load(values ? v_s : k_s, (values ? vcache : kcache) + off, ps * row_bytes, values ? bar_v : bar_k);
+    };
+    if (tid == 0) {
+        issue(page_first, false);
+        issue(page_first, true);
+    }
     uint32_t phase = 0;
     for (int lp = page_first; lp <= page_last; ++lp) {
-        if (tid == 0) {
-            // the page's keys and its values are each one contiguous block: two copies
-            const int page = table[lp % a.ring_pages];
-            const long long off = ((long long)page * a.n_kv_heads + g) * ps * hd;
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_expect_tx(bar, 2u * ps * row_bytes);
-            bulk_load(k_s, kcache + off, ps * row_bytes, bar);
-            bulk_load(v_s, vcache + off, ps * row_bytes, bar);
-        }
-        if (!mbar_wait_bounded(bar, phase)) {
+        if (!mbar_wait_bounded(bar_k, phase)) {
             if (a.status) atomicExch(a.status, 3);
             return;
         }
-        phase ^= 1;
         const int r_begin = max(k_begin, lp * ps) - lp * ps, r_end = min(k_end, (lp + 1) * ps) - lp * ps;
         const int w0 = warp * 16;                  // this warp's 16 keys of the page
-        if (w0 < r_end && w0 + 16 > r_begin) {
+        const bool active = w0 < r_end && w0 + 16 > r_begin;
+        float c0 = 1.f, c1 = 1.f;
+        uint32_t pb0 = 0u, pb1 = 0u;
+        if (active) {
+            // ---- scores: rows = keys w0 + quad (+ 8), columns = heads 2 tq, 2 tq + 1 ----
+            float s[4] = {0.f, 0.f, 0.f, 0.f};
+            const int kr = w0 + (lane & 15);
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk) {
+                if (kk < ksteps) {
+                    uint32_t af[4];
+                    ldmatrix_x4(af, k_s + kr * row_bytes + rdl_swizzled_chunk(kr, 2 * kk + (lane >> 4), chunks) * 16);
+                    mma_bf16(s, af, qf[kk][0], qf[kk][1]);
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float v = capped ? tanh_fast(s[e] * c_in) * c_out : s[e] * c_in;
+                const int r = w0 + quad + 8 * (e >> 1);
+                if (r < r_begin || r >= r_end) v = -INFINITY;
+                s[e] = v;
+            }
+            // maxima and sums over the 16 keys: over the two rows of a lane and over the lanes that differ in quad
+            float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
+#pragma unroll
+            for (int off = 4; off < 32; off <<= 1) {
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+            }
+            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+            const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
+            c0 = exp2f(m0 - ms0);
+            c1 = exp2f(m1 - ms1);
+            m0 = mn0; m1 = mn1;
+            const float e0 = exp2f(s[0] - ms0), e1 = exp2f(s[1] - ms1), e2 = exp2f(s[2] - ms0), e3 = exp2f(s[3] - ms1);
+            float rs0 = e0 + e2, rs1 = e1 + e3;
+#pragma unroll
+            for (int off = 4; off < 32; off <<= 1) {
+                rs0 += __shfl_xor_sync(0xffffffffu, rs0, off);
+                rs1 += __shfl_xor_sync(0xffffffffu, rs1, off);
+            }
+            l0 = l0 * c0 + rs0;
+            l1 = l1 * c1 + rs1;
+            // P^T as the B operand: the [key][head] fragments transposed to [head][key]
+            asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pb0) : "r"(pack_bf16(e0, e1)));
+            asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pb1) : "r"(pack_bf16(e2, e3)));
+        }
+        __syncthreads();                                   // every warp is done with the key tile
+        if (lp < page_last && tid == 0) issue(lp + 1, false);
+        if (!mbar_wait_bounded(bar_v, phase)) {
+            if (a.status) atomicExch(a.status, 3);
+            return;
+        }
+        if (active) {
             if (w0 < r_begin || w0 + 16 > r_end) {
                 // value rows outside the run get the weight 0; they may hold anything (rows beyond the
                 // sequence's end, an earlier occupant's rows), so make them zero: 0 * NaN is NaN
@@ -178,78 +246,38 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
                 }
                 __syncwarp();
             }
-            float s[2][4];
+            // ---- O^T += V^T P^T ----
 #pragma unroll
-            for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
-            for (int kk = 0; kk < ksteps; ++kk) {
-                uint32_t af[4], bf[4];
-                ldmatrix_x4(af, q_s + (lane & 15) * QROWB + (2 * kk + (lane >> 4)) * 16);
-                const int kr = w0 + (lane & 7) + 8 * (lane >> 4);
-                ldmatrix_x4(bf, k_s + kr * row_bytes + rdl_swizzled_chunk(kr, 2 * kk + ((lane >> 3) & 1), chunks) * 16);
-                mma_bf16(s[0], af, bf[0], bf[1]);
-                mma_bf16(s[1], af, bf[2], bf[3]);
-            }
-            float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    float v = s[nt][e] * a.score_scale;
-                    if (a.softcap > 0.f) v = a.softcap * tanh_fast(v * inv_cap);
-                    v *= LOG2E;
-                    const int r = w0 + nt * 8 + 2 * tq + (e & 1);
-                    if (r < r_begin || r >= r_end) v = -INFINITY;
-                    s[nt][e] = v;
-                }
-                mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
-                mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
-            }
-            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-            const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
-            const float c0 = exp2f(m0 - ms0), c1 = exp2f(m1 - ms1);
-            m0 = mn0; m1 = mn1;
-            const float e00 = exp2f(s[0][0] - ms0), e01 = exp2f(s[0][1] - ms0), e02 = exp2f(s[0][2] - ms1), e03 = exp2f(s[0][3] - ms1);
-            const float e10 = exp2f(s[1][0] - ms0), e11 = exp2f(s[1][1] - ms0), e12 = exp2f(s[1][2] - ms1), e13 = exp2f(s[1][3] - ms1);
-            float rs0 = e00 + e01 + e10 + e11, rs1 = e02 + e03 + e12 + e13;
-            rs0 += __shfl_xor_sync(0xffffffffu, rs0, 1);
-            rs0 += __shfl_xor_sync(0xffffffffu, rs0, 2);
-            rs1 += __shfl_xor_sync(0xffffffffu, rs1, 1);
-            rs1 += __shfl_xor_sync(0xffffffffu, rs1, 2);
-            l0 = l0 * c0 + rs0;
-            l1 = l1 * c1 + rs1;
-            uint32_t pf[4] = {pack_bf16(e00, e01), pack_bf16(e02, e03), pack_bf16(e10, e11), pack_bf16(e12, e13)};
-#pragma unroll
-            for (int dp = 0; dp < HD / 16; ++dp) {
-                if (dp * 16 < hd) {
-                    uint32_t bf[4];
-                    const int vr = w0 + (lane & 15);
-                    ldmatrix_x4_trans(bf, v_s + vr * row_bytes + rdl_swizzled_chunk(vr, 2 * dp + (lane >> 4), chunks) * 16);
-                    o[2 * dp][0] *= c0; o[2 * dp][1] *= c0; o[2 * dp][2] *= c1; o[2 * dp][3] *= c1;
-                    o[2 * dp + 1][0] *= c0; o[2 * dp + 1][1] *= c0; o[2 * dp + 1][2] *= c1; o[2 * dp + 1][3] *= c1;
-                    mma_bf16(o[2 * dp], pf, bf[0], bf[1]);
-                    mma_bf16(o[2 * dp + 1], pf, bf[2], bf[3]);
+            for (int db = 0; db < HD / 16; ++db) {
+                if (db * 16 < hd) {
+                    uint32_t af[4];
+                    const int vr = w0 + (lane & 7) + 8 * (lane >> 4);
+                    ldmatrix_x4_trans(af, v_s + vr * row_bytes + rdl_swizzled_chunk(vr, 2 * db + ((lane >> 3) & 1), chunks) * 16);
+                    o[db][0] *= c0; o[db][1] *= c1; o[db][2] *= c0; o[db][3] *= c1;
+                    mma_bf16(o[db], af, pb0, pb1);
                 }
             }
         }
-        __syncthreads();   // everyone is done with the tiles before the next copy lands
+        __syncthreads();                                   // every warp is done with the value tile
+        if (lp < page_last && tid == 0) issue(lp + 1, true);
+        phase ^= 1;
     }
 
     // ---- merge the four warps through shared memory, in warp order ----
-    float* sm_o = reinterpret_cast<float*>(k_tile);  // [warp][row][HD]; the tiles are no longer needed
-    if (tq == 0) {
-        sm_m[warp][quad] = m0; sm_m[warp][quad + 8] = m1;
-        sm_l[warp][quad] = l0; sm_l[warp][quad + 8] = l1;
+    float* sm_o = reinterpret_cast<float*>(k_tile);  // [warp][head][HD]; the tiles are no longer needed
+    if (quad == 0) {
+        sm_m[warp][2 * tq] = m0; sm_m[warp][2 * tq + 1] = m1;
+        sm_l[warp][2 * tq] = l0; sm_l[warp][2 * tq + 1] = l1;
     }
 #pragma unroll
-    for (int nt = 0; nt < HD / 8; ++nt) {
-        const int d = nt * 8 + 2 * tq;
+    for (int db = 0; db < HD / 16; ++db) {
+        const int d = db * 16 + quad;
         if (d < hd) {
-            if (quad < G) *(float2*)(sm_o + ((warp * QROWS + quad) * HD + d)) = make_float2(o[nt][0], o[nt][1]);
-            if (quad + 8 < G) *(float2*)(sm_o + ((warp * QROWS + quad + 8) * HD + d)) = make_float2(o[nt][2], o[nt][3]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int h = 2 * tq + (e & 1);
+                if (h < G) sm_o[(warp * QROWS + h) * HD + d + 8 * (e >> 1)] = o[db][e];
+            }
         }
     }
     __syncthreads();
@@ -327,13 +355,11 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
 
 template <int HD>
 int launch_decode(const AttentionArgs* a, cudaStream_t st) {
-    const int qtile = QROWS * (HD * 2 + 16);
     const int tiles = 2 * a->page_size * a->head_dim * 2;
     const int merge = DEC_WARPS * QROWS * HD * (int)sizeof(float);
     const int runs = (QROWS * a->max_splits + QROWS) * (int)sizeof(float);
     int smem = tiles > merge ? tiles : merge;
     if (runs > smem) smem = runs;
-    smem += qtile;
     RDL_REQUIRE(smem <= 200 * 1024, "attention_decode: page_size %d x head_dim %d needs %d bytes of shared memory, limit is 204800",
                 a->page_size, a->head_dim, smem);
     static int granted = 48 * 1024;

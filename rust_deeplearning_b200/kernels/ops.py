@@ -165,6 +165,19 @@ def _skinny_ok(x, weight):
     return _bf16_ok(x, weight) and x.shape[0] <= SKINNY_MAX_ROWS
 
 
+TC_MIN_ROWS = 128        # a tcgen05 tile holds 128 rows; between 17 and 127 rows a library product stands
+
+
+def _own_bf16_kernel(x, weight):
+    """Few rows: the weight-streaming kernel.  A tile's worth of rows or more: the tcgen05 kernel.
+    In between a 128-row tile would be mostly empty and too few blocks would stream the weights,
+    so the library product (cuBLAS through torch) takes those."""
+    if not _bf16_ok(x, weight):
+        return False
+    rows = x.shape[0]
+    return rows <= SKINNY_MAX_ROWS or (rows >= TC_MIN_ROWS and PREFILL_GEMM == "tcgen05")
+
+
 def _gemm_bf16(x, weight, n_out, out_dtype, gated, activation, softcap, status):
     """The library's own bfloat16 products: weight streaming for few rows, tcgen05 for many."""
     out = torch.empty((x.shape[0], n_out), dtype=out_dtype, device=x.device)
@@ -198,7 +211,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
         out = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.float32, device=x.device)
         library.check(library.load().rdl_gemm_f32(_ptr(out), _ptr(x), _ptr(weight), x.shape[0], weight.shape[0],
                                                   x.shape[1], _stream(x)))
-    elif _bf16_ok(x, weight) and (x.shape[0] <= SKINNY_MAX_ROWS or PREFILL_GEMM == "tcgen05"):
+    elif _own_bf16_kernel(x, weight):
         return _gemm_bf16(x, weight, weight.shape[0], out_dtype, False, 0, softcap, status)
     else:
         _need(x.is_cuda, "kernels run on CUDA tensors only; there is no CPU path")
@@ -214,7 +227,7 @@ def linear_gated(x: torch.Tensor, weight_gate_up: torch.Tensor, activation: str,
     and the gated activation kernel."""
     _need(activation in ACTIVATIONS, f"unknown activation '{activation}', known: {sorted(ACTIVATIONS)}")
     _need(weight_gate_up.shape[0] % 2 == 0, "linear_gated: the weight must hold gate rows and as many up rows")
-    if _bf16_ok(x, weight_gate_up) and (x.shape[0] <= SKINNY_MAX_ROWS or PREFILL_GEMM == "tcgen05"):
+    if _own_bf16_kernel(x, weight_gate_up):
         return _gemm_bf16(x, weight_gate_up, weight_gate_up.shape[0] // 2, x.dtype, True, ACTIVATIONS[activation], None, status)
     return gated_activation(linear(x, weight_gate_up), activation)
 

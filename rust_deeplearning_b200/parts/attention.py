@@ -55,7 +55,8 @@ class Attention:
     def forward(self, x: torch.Tensor, batch, cache: RunCache, run: int) -> torch.Tensor:
         nh, nkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
         pages = self._pages(batch, cache)
-        fast = x.dtype is torch.bfloat16 and hd % 16 == 0 and hd <= 256 and nh // nkv <= 16
+        fast = x.dtype is torch.bfloat16 and hd % 16 == 0 and hd <= 256
+        fast_decode = fast and nh // nkv <= 8 and cache.page_size % 16 == 0 and cache.page_size <= 64
         common = dict(n_heads=nh, n_kv_heads=nkv, head_dim=hd, score_scale=self.score_scale,
                       softcap=self.softcap, window=self.window)
         tables, rotary_dim = self._rotary_tables()
@@ -72,7 +73,7 @@ class Attention:
             owner = batch.new_kv.get(cache_owner(batch, run))
             if batch.is_decode or owner is None:
                 ab = batch.attention_batch("all", self.window)
-                kind = "decode" if (fast and batch.is_decode) else ("prefill" if fast and batch.n_tiles else "plain")
+                kind = "decode" if (fast_decode and batch.is_decode) else ("prefill" if fast and batch.n_tiles else "plain")
                 ctx = ops.attention(q, ab, pages, kind=kind, scratch=lambda n: batch.scratch_buffer("decode", n), status=batch.status, **common)
             else:
                 rows, k_col, v_col = owner
@@ -93,7 +94,7 @@ class Attention:
                 ops.rope_cache(qkv, nh, nkv, hd, tok_seq=batch.tok_seq, tok_pos=batch.tok_pos, pages=pages,
                                seq_end=batch.seq_end)
             ab = batch.attention_batch("all", self.window)
-            ctx = ops.attention(qkv, ab, pages, kind="decode" if fast else "plain",
+            ctx = ops.attention(qkv, ab, pages, kind="decode" if fast_decode else "plain",
                                 scratch=lambda n: batch.scratch_buffer("decode", n), status=batch.status, **common)
         else:
             # rotate; attend over the cache (earlier steps) and the packed rows (this step); write.

@@ -119,18 +119,19 @@ def test_skinny_gemm(m, n, k):
         assert_close(ops.linear_gated(x, wgu, act), ref.linear_gated(x, wgu, act), torch.bfloat16, what=f"gated {act}")
     # the library product and the activation kernel (the route of operands the own kernels do not take) give the same
     x17 = rnd((17, k), torch.bfloat16, 16)
-    assert not ops._skinny_ok(x17, w)
+    assert not ops._own_bf16_kernel(x17, w)
+    assert_close(ops.linear_gated(x17, wgu, "silu"), ref.linear_gated(x17, wgu, "silu"), torch.bfloat16, what="17 rows")
     assert_close(ops.gated_activation(torch.mm(x17, wgu.t()), "gelu_pytorch_tanh"), ref.linear_gated(x17, wgu, "gelu_pytorch_tanh"),
                  torch.bfloat16, what="gated, library product")
 
 
-@pytest.mark.parametrize("m", [17, 128, 200, 2048])
+@pytest.mark.parametrize("m", [128, 129, 200, 2048])
 @pytest.mark.parametrize("n,k", [(256, 64), (384, 96), (131, 80), (2304, 2048), (520, 1160)])
 def test_tcgen05_gemm(m, n, k):
     """The TMA + tcgen05 kernel for many rows: tiles, tails in every dimension, all epilogues."""
     x, w = rnd((m, k), torch.bfloat16, 17), rnd((n, k), torch.bfloat16, 18, 0.2)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    assert ops.PREFILL_GEMM == "tcgen05" and not ops._skinny_ok(x, w)
+    assert ops.PREFILL_GEMM == "tcgen05" and ops._own_bf16_kernel(x, w) and not ops._skinny_ok(x, w)
     assert_close(ops.linear(x, w, status=status), ref.linear(x, w), torch.bfloat16, what="plain")
     assert_close(ops.linear(x, w, out_dtype=torch.float32, softcap=3.0, status=status), ref.linear(x, w, torch.float32, softcap=3.0),
                  torch.float32, what="float32 out, soft-cap", f32_tol=1e-4)
@@ -270,6 +271,7 @@ DECODE_SHAPES = [
     dict(past=[2000, 17, 130], n_heads=4, n_kv_heads=2, head_dim=128, page_size=64, window=100),
     dict(past=[511, 512], n_heads=3, n_kv_heads=3, head_dim=48, page_size=32, window=512),
     dict(past=[77], n_heads=16, n_kv_heads=2, head_dim=80, page_size=64, window=33),
+    dict(past=[300, 9], n_heads=5, n_kv_heads=1, head_dim=64, page_size=48, window=None),
 ]
 
 
