@@ -102,6 +102,8 @@ struct TcArgs {
     int* status;
 };
 
+constexpr int RASTER_GROUP = 8;   // row tiles that share a weight tile and are scheduled together
+
 // MT: row tiles of 128 a block computes (1 or 2).  Two tiles share every weight tile that is loaded,
 // which halves the bytes fetched per product: a 256 x 256 tile needs 64 KB of operands for 8.4 MFLOP.
 template <int BN, bool GATED, int MT>
@@ -118,7 +120,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     __shared__ uint32_t tmem_slot;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * (MT * BM), n0 = blockIdx.x * BN;
+    // Blocks are numbered so that up to eight row tiles that share a weight tile follow one another: they
+    // run at the same time, the weight tile comes from HBM once and the eight row tiles stay in L2.
+    int m0, n0;
+    {
+        const int tiles_m = (a.M + MT * BM - 1) / (MT * BM), tiles_n = (a.N + BN - 1) / BN;
+        const int per_group = RASTER_GROUP * tiles_n;
+        const int group = blockIdx.x / per_group, in_group = blockIdx.x - group * per_group;
+        const int first_m = group * RASTER_GROUP;
+        const int gm = tiles_m - first_m < RASTER_GROUP ? tiles_m - first_m : RASTER_GROUP;
+        m0 = (first_m + in_group % gm) * (MT * BM);
+        n0 = (in_group / gm) * BN;
+    }
     const int kblocks = (a.K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -280,7 +293,9 @@ int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs& a, cud
         RDL_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, GATED, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "gemm_tc");
         opted = true;
     }
-    dim3 grid((a.N + BN - 1) / BN, (a.M + MT * BM - 1) / (MT * BM));
+    const long long tiles = (long long)((a.N + BN - 1) / BN) * ((a.M + MT * BM - 1) / (MT * BM));
+    RDL_REQUIRE(tiles <= 0x7fffffffLL, "gemm_tc: %lld tiles exceed the grid limit", tiles);
+    dim3 grid((unsigned)tiles);
     gemm_tc_kernel<BN, GATED, MT><<<grid, TC_THREADS, smem, st>>>(mx, mw, a);
     RDL_CHECK_LAUNCH("gemm_tc");
     return 0;
@@ -297,7 +312,6 @@ extern "C" int rdl_gemm_tc(void* out, int out_dtype, const void* x, const void* 
                 "gemm_tc: operands must start on 16-byte boundaries");
     RDL_REQUIRE(!gated || activation == RDL_ACT_GELU_TANH || activation == RDL_ACT_SILU, "gemm_tc: unknown activation %d", activation);
     RDL_REQUIRE(softcap >= 0.f, "gemm_tc: soft-cap must not be negative");
-    RDL_REQUIRE((long long)((m + BM - 1) / BM) <= 65535, "gemm_tc: %d rows exceed the grid limit", m);
     if (m == 0) return 0;
     const int bn = gated ? 128 : 256;
     // two row tiles a block when that still fills most of the 148 multiprocessors
