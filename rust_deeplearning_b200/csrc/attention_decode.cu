@@ -17,8 +17,9 @@
 // in attention_plain.cu; all keys are read from the cache (the step writes its new rows first).
 //
 // Scratch: int counters [tokens * kv_heads] (zero before the launch; the merging block puts its
-// counter back to zero), then float partials [token][head][run][head_dim + 2] = sums, maximum
-// (base-2 scale), normaliser.  Launches that share the scratch must not overlap on the device.
+// counter back to zero), then float partial sums [token][head][run][head_dim], then per run the
+// maximum (base-2 scale) and the normaliser [token][head][run][2].  Launches that share the scratch
+// must not overlap on the device.
 //
 // Every wait on a copy is bounded: after about a second without completion the block records
 // an error in `status` and leaves.
@@ -84,8 +85,10 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
     return true;
 }
 
-// HD: head_dim padded to 64, 128 or 256 (head_dim itself is a multiple of 16).
-template <int HD>
+// HD: head_dim padded to 64, 128 or 256 (head_dim itself is a multiple of 16).  EXACT: head_dim == HD;
+// row sizes and the swizzle are then compile-time constants and a fragment's address is a register
+// plus an immediate.
+template <int HD, bool EXACT>
 __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(AttentionArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) unsigned long long bar_storage[2];     // keys, values
@@ -93,7 +96,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
     __shared__ int s_flag;
 
     const int t = blockIdx.z, g = blockIdx.y, sp = blockIdx.x;
-    const int hd = a.head_dim, ps = a.page_size;
+    const int hd = EXACT ? HD : a.head_dim, ps = a.page_size;
     const int G = a.n_heads / a.n_kv_heads;
     const int seq = a.tok_seq[t], p = a.tok_pos[t];
     if (p < 0) return;  // a padding row of a fixed-size batch
@@ -133,6 +136,27 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
         mbar_init(bar_v, 1);
     }
     __syncthreads();   // nobody waits on the barrier before it is initialised
+    // A page's keys and its values are each one contiguous block: one bulk copy each (issued by thread 0).
+    // The copies of the next page are issued as soon as this page's tile is free: its keys travel while
+    // P V of this page is computed, its values while the next scores are.
+    auto issue = [&](int lp, bool values) {
+        const int page = table[lp % a.ring_pages];
+        const long long off = ((long long)page * a.n_kv_heads + g) * ps * hd;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_expect_tx(values ? bar_v : bar_k, ps * row_bytes);
+        bulk_load(values ? v_s : k_s, (values ? vcache : kcache) + off, ps * row_bytes, values ? bar_v : bar_k);
+    };
+    // The kernel before this one writes the step's new rows: positions from seq_past on.  A first page
+    // that lies wholly below seq_past does not change any more and is fetched before that kernel has
+    // finished.  (In a ring a new row of a later token of the same sequence could land in this page's
+    // place, so there only a sequence's last token does it: the row it overwrites itself lies below
+    // every page it reads.)
+    const bool early = a.seq_past != nullptr && (page_first + 1) * ps <= a.seq_past[seq] &&
+                       (a.window <= 0 || t == a.seq_start[seq + 1] - 1);
+    if (early && tid == 0) {
+        issue(page_first, false);
+        issue(page_first, true);
+    }
     rdl_grid_wait();
     rdl_grid_launch_dependents();
     // The products are formed with the keys as rows: S^T [16 keys x 8 heads] = K [16 x d] Q^T [d x 8] and
@@ -161,17 +185,31 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
     const float c_in = capped ? a.score_scale / a.softcap : a.score_scale * LOG2E;
     const float c_out = a.softcap * LOG2E;
 
-    // A page's keys and its values are each one contiguous block: one bulk copy each (issued by thread 0).
-    // The copies of the next page are issued as soon as this page's tile is free: its keys travel while
-    // P V of this page is computed, its values while the next scores are.
-    auto issue = [&](int lp, bool values) {
-        const int page = table[lp % a.ring_pages];
-        const long long off = ((long long)page * a.n_kv_heads + g) * ps * hd;
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_expect_tx(values ? bar_v : bar_k, ps * row_bytes);
-        bulk_load(values ? v_s : k_s, (values ? vcache : kcache) + off, ps * row_bytes, values ? bar_v : bar_k);
+    // Fragment addresses.  Keys (A of the score product): row w0 + (lane & 15), chunk 2 kk + (lane >> 4).
+    // Values (A of the output product, transposed on load): row w0 + (lane & 7) + 8 (lane >> 4), chunk
+    // 2 db + ((lane >> 3) & 1).  With c = 2 k + hi and the row's swizzle r: (c ^ r) * 16 =
+    // 128 (k >> 2) + (((k & 3) << 5) ^ ((hi ^ r) << 4)): four registers and an immediate.
+    const int kr = warp * 16 + (lane & 15);
+    const int vr = warp * 16 + (lane & 7) + 8 * (lane >> 4);
+    uint32_t ka[4], va[4];
+    {
+        const uint32_t kx = (uint32_t)(((kr & 7) ^ (lane >> 4)) << 4), vx = (uint32_t)(((vr & 7) ^ ((lane >> 3) & 1)) << 4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            ka[j] = k_s + kr * row_bytes + (kx ^ (uint32_t)(j << 5));
+            va[j] = v_s + vr * row_bytes + (vx ^ (uint32_t)(j << 5));
+        }
+    }
+    auto k_addr = [&](int kk) -> uint32_t {
+        if (EXACT) return ka[kk & 3] + (uint32_t)((kk >> 2) * 128);
+        return k_s + kr * row_bytes + rdl_swizzled_chunk(kr, 2 * kk + (lane >> 4), chunks) * 16;
     };
-    if (tid == 0) {
+    auto v_addr = [&](int db) -> uint32_t {
+        if (EXACT) return va[db & 3] + (uint32_t)((db >> 2) * 128);
+        return v_s + vr * row_bytes + rdl_swizzled_chunk(vr, 2 * db + ((lane >> 3) & 1), chunks) * 16;
+    };
+
+    if (!early && tid == 0) {
         issue(page_first, false);
         issue(page_first, true);
     }
@@ -188,16 +226,21 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
         uint32_t pb0 = 0u, pb1 = 0u;
         if (active) {
             // ---- scores: rows = keys w0 + quad (+ 8), columns = heads 2 tq, 2 tq + 1 ----
-            float s[4] = {0.f, 0.f, 0.f, 0.f};
-            const int kr = w0 + (lane & 15);
+            // four accumulators: the chain of dependent products is a quarter as long
+            float s4[4][4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) s4[j][0] = s4[j][1] = s4[j][2] = s4[j][3] = 0.f;
 #pragma unroll
             for (int kk = 0; kk < HD / 16; ++kk) {
-                if (kk < ksteps) {
+                if (EXACT || kk < ksteps) {
                     uint32_t af[4];
-                    ldmatrix_x4(af, k_s + kr * row_bytes + rdl_swizzled_chunk(kr, 2 * kk + (lane >> 4), chunks) * 16);
-                    mma_bf16(s, af, qf[kk][0], qf[kk][1]);
+                    ldmatrix_x4(af, k_addr(kk));
+                    mma_bf16(s4[kk & 3], af, qf[kk][0], qf[kk][1]);
                 }
             }
+            float s[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[e] = (s4[0][e] + s4[1][e]) + (s4[2][e] + s4[3][e]);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 float v = capped ? tanh_fast(s[e] * c_in) * c_out : s[e] * c_in;
@@ -249,10 +292,9 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
             // ---- O^T += V^T P^T ----
 #pragma unroll
             for (int db = 0; db < HD / 16; ++db) {
-                if (db * 16 < hd) {
+                if (EXACT || db * 16 < hd) {
                     uint32_t af[4];
-                    const int vr = w0 + (lane & 7) + 8 * (lane >> 4);
-                    ldmatrix_x4_trans(af, v_s + vr * row_bytes + rdl_swizzled_chunk(vr, 2 * db + ((lane >> 3) & 1), chunks) * 16);
+                    ldmatrix_x4_trans(af, v_addr(db));
                     o[db][0] *= c0; o[db][1] *= c1; o[db][2] *= c0; o[db][3] *= c1;
                     mma_bf16(o[db], af, pb0, pb1);
                 }
@@ -283,28 +325,34 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
     __syncthreads();
     __nv_bfloat16* out = (__nv_bfloat16*)a.out + (long long)t * a.out_stride;
     int* counters = (int*)a.scratch;
+    // partial sums [token][head][run][hd], then (maximum, normaliser) [token][head][run][2]
     float* partials = (float*)((char*)a.scratch + a.counter_bytes);
-    for (int idx = tid; idx < G * hd; idx += DEC_THREADS) {
-        const int h = idx / hd, d = idx - h * hd;
+    float* stats = partials + (long long)a.n_tokens * a.n_heads * a.max_splits * hd;
+    // four outputs per thread: the warps' sums weighted by exp2(their maximum - the block's)
+    for (int idx = tid; idx < G * hd / 4; idx += DEC_THREADS) {
+        const int h = (idx * 4) / hd, d = idx * 4 - h * hd;
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, sm_m[w][h]);
-        float osum = 0.f, lsum = 0.f;
+        float4 osum = make_float4(0.f, 0.f, 0.f, 0.f);
+        float lsum = 0.f;
 #pragma unroll
         for (int w = 0; w < DEC_WARPS; ++w) {
             const float wt = sm_m[w][h] == -INFINITY ? 0.f : exp2f(sm_m[w][h] - M);
-            osum = fmaf(wt, sm_o[(w * QROWS + h) * HD + d], osum);
+            const float4 v = *reinterpret_cast<const float4*>(sm_o + (w * QROWS + h) * HD + d);
+            osum.x = fmaf(wt, v.x, osum.x); osum.y = fmaf(wt, v.y, osum.y);
+            osum.z = fmaf(wt, v.z, osum.z); osum.w = fmaf(wt, v.w, osum.w);
             lsum = fmaf(wt, sm_l[w][h], lsum);
         }
         if (n_splits == 1) {
-            out[(long long)(g * G + h) * hd + d] = __float2bfloat16_rn(osum / lsum);
+            const float inv = 1.0f / lsum;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(out + (long long)(g * G + h) * hd + d);
+            o2[0] = __floats2bfloat162_rn(osum.x * inv, osum.y * inv);
+            o2[1] = __floats2bfloat162_rn(osum.z * inv, osum.w * inv);
         } else {
-            float* dst = partials + (((long long)t * a.n_heads + (g * G + h)) * a.max_splits + sp) * (hd + 2);
-            dst[d] = osum;
-            if (d == 0) {
-                dst[hd] = M;
-                dst[hd + 1] = lsum;
-            }
+            const long long run = ((long long)t * a.n_heads + (g * G + h)) * a.max_splits + sp;
+            *reinterpret_cast<float4*>(partials + run * hd + d) = osum;
+            if (d == 0) *reinterpret_cast<float2*>(stats + run * 2) = make_float2(M, lsum);
         }
     }
     if (n_splits == 1) return;
@@ -321,39 +369,79 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
     if (!s_flag) return;
     __threadfence();
     float* w_s = sm_o;                            // [G][n_splits] weights of the runs
-    float* stat = sm_o + G * n_splits;            // [G] 1 / normaliser
+    float* inv_s = sm_o + G * n_splits;           // [G] 1 / normaliser
+    const long long run0 = ((long long)t * a.n_heads + g * G) * a.max_splits;
+    // The first eight runs' sums of this thread's first outputs are requested before the weights are
+    // known: the two trips to L2 overlap.
+    constexpr int AHEAD = 8;
+    float4 ahead[AHEAD];
+    {
+        const int h = (tid * 4) / hd, d = tid * 4 - h * hd;
+        const float* base = partials + (run0 + (long long)h * a.max_splits) * hd + d;
+#pragma unroll
+        for (int r = 0; r < AHEAD; ++r)
+            ahead[r] = (tid < G * hd / 4 && r < n_splits) ? __ldcg(reinterpret_cast<const float4*>(base + (long long)r * hd))
+                                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     for (int h = warp; h < G; h += DEC_WARPS) {
-        const float* base = partials + ((long long)t * a.n_heads + (g * G + h)) * a.max_splits * (hd + 2);
-        float M = -INFINITY;
-        for (int s = lane; s < n_splits; s += 32) M = fmaxf(M, base[(long long)s * (hd + 2) + hd]);
+        const float2* st = reinterpret_cast<const float2*>(stats + (run0 + (long long)h * a.max_splits) * 2);
+        // a lane's first two runs stay in registers: maximum and normaliser come in one trip
+        float2 mine[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) mine[i] = lane + 32 * i < n_splits ? __ldcg(st + lane + 32 * i) : make_float2(-INFINITY, 0.f);
+        float M = fmaxf(mine[0].x, mine[1].x);
+        for (int r = lane + 64; r < n_splits; r += 32) M = fmaxf(M, __ldcg(st + r).x);
         M = warp_max(M);
         float L = 0.f;
-        for (int s = lane; s < n_splits; s += 32) {
-            const float wt = exp2f(base[(long long)s * (hd + 2) + hd] - M);
-            w_s[h * n_splits + s] = wt;
-            L = fmaf(wt, base[(long long)s * (hd + 2) + hd + 1], L);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            if (lane + 32 * i < n_splits) {
+                const float wt = exp2f(mine[i].x - M);
+                w_s[h * n_splits + lane + 32 * i] = wt;
+                L = fmaf(wt, mine[i].y, L);
+            }
+        }
+        for (int r = lane + 64; r < n_splits; r += 32) {
+            const float2 v = __ldcg(st + r);
+            const float wt = exp2f(v.x - M);
+            w_s[h * n_splits + r] = wt;
+            L = fmaf(wt, v.y, L);
         }
         L = warp_sum(L);
-        if (lane == 0) stat[h] = 1.0f / L;
+        if (lane == 0) inv_s[h] = 1.0f / L;
     }
     __syncthreads();
-    // two outputs per thread and eight runs in flight: the partials are read from L2 in few trips
-    for (int idx = tid; idx < G * hd / 2; idx += DEC_THREADS) {
-        const int h = (idx * 2) / hd, d = idx * 2 - h * hd;
-        const float* base = partials + ((long long)t * a.n_heads + (g * G + h)) * a.max_splits * (hd + 2) + d;
-        float ox = 0.f, oy = 0.f;
-#pragma unroll 8
-        for (int s = 0; s < n_splits; ++s) {
-            const float2 v = *(const float2*)(base + (long long)s * (hd + 2));
-            const float wt = w_s[h * n_splits + s];
-            ox = fmaf(wt, v.x, ox);
-            oy = fmaf(wt, v.y, oy);
+    for (int idx = tid; idx < G * hd / 4; idx += DEC_THREADS) {
+        const int h = (idx * 4) / hd, d = idx * 4 - h * hd;
+        const float* base = partials + (run0 + (long long)h * a.max_splits) * hd + d;
+        const float* wts = w_s + h * n_splits;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        int r = 0;
+        if (idx == tid) {                         // the outputs whose first runs are already here
+#pragma unroll
+            for (; r < AHEAD; ++r) {
+                if (r < n_splits) {
+                    const float wt = wts[r];
+                    acc.x = fmaf(wt, ahead[r].x, acc.x); acc.y = fmaf(wt, ahead[r].y, acc.y);
+                    acc.z = fmaf(wt, ahead[r].z, acc.z); acc.w = fmaf(wt, ahead[r].w, acc.w);
+                }
+            }
         }
-        *(__nv_bfloat162*)(out + (long long)(g * G + h) * hd + d) = __floats2bfloat162_rn(ox * stat[h], oy * stat[h]);
+#pragma unroll 8
+        for (; r < n_splits; ++r) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(base + (long long)r * hd));
+            const float wt = wts[r];
+            acc.x = fmaf(wt, v.x, acc.x); acc.y = fmaf(wt, v.y, acc.y);
+            acc.z = fmaf(wt, v.z, acc.z); acc.w = fmaf(wt, v.w, acc.w);
+        }
+        const float inv = inv_s[h];
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(out + (long long)(g * G + h) * hd + d);
+        o2[0] = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+        o2[1] = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
     }
 }
 
-template <int HD>
+template <int HD, bool EXACT>
 int launch_decode(const AttentionArgs* a, cudaStream_t st) {
     const int tiles = 2 * a->page_size * a->head_dim * 2;
     const int merge = DEC_WARPS * QROWS * HD * (int)sizeof(float);
@@ -364,12 +452,12 @@ int launch_decode(const AttentionArgs* a, cudaStream_t st) {
                 a->page_size, a->head_dim, smem);
     static int granted = 48 * 1024;
     if (smem > granted) {
-        RDL_CUDA(cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+        RDL_CUDA(cudaFuncSetAttribute(attention_decode_kernel<HD, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
                  "attention_decode");
         granted = smem;
     }
     dim3 grid(a->max_splits, a->n_kv_heads, a->n_tokens);
-    RDL_CHECK_EX(rdl_launch(attention_decode_kernel<HD>, grid, dim3(DEC_THREADS), (size_t)smem, st, *a), "attention_decode");
+    RDL_CHECK_EX(rdl_launch(attention_decode_kernel<HD, EXACT>, grid, dim3(DEC_THREADS), (size_t)smem, st, *a), "attention_decode");
     return 0;
 }
 
@@ -407,7 +495,10 @@ extern "C" int rdl_attention_decode(const AttentionArgs* a, void* stream) {
                 "attention_decode: rows must start on 16-byte boundaries");
     if (a->n_tokens == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
-    if (a->head_dim <= 64) return launch_decode<64>(a, st);
-    if (a->head_dim <= 128) return launch_decode<128>(a, st);
-    return launch_decode<256>(a, st);
+    if (a->head_dim == 64) return launch_decode<64, true>(a, st);
+    if (a->head_dim == 128) return launch_decode<128, true>(a, st);
+    if (a->head_dim == 256) return launch_decode<256, true>(a, st);
+    if (a->head_dim < 64) return launch_decode<64, false>(a, st);
+    if (a->head_dim < 128) return launch_decode<128, false>(a, st);
+    return launch_decode<256, false>(a, st);
 }
