@@ -214,12 +214,16 @@ def main():
             for _ in range(args.warmup + args.steps):
                 slot = engine.new_sequence()
                 start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
                 start.record()
                 engine.step([slot], [prompt], "last")
                 stop.record()
+                host_ms = (time.perf_counter() - t0) * 1e3     # the host's share: validation, batch description, launches
                 torch.cuda.synchronize()
                 engine.release(slot)
-            print(json.dumps({"case": "prefill", "tokens": PROMPT, "layers": layers, "ms": round(start.elapsed_time(stop), 3)}))
+            print(json.dumps({"case": "prefill", "tokens": PROMPT, "layers": layers, "ms": round(start.elapsed_time(stop), 3),
+                              "host_ms": round(host_ms, 3)}))
         return 0
 
     clocks = ClockSampler()

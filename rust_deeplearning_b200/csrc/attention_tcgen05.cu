@@ -117,17 +117,21 @@ struct TcAttnArgs {
     int* status;
 };
 
+// DB: 64-column blocks of a head (head_dim / 64)
+template <int DB>
 __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                       const __grid_constant__ CUtensorMap map_kv, TcAttnArgs a) {
     // 64-row tiles come from the host; a block takes two of them, so odd ones have nothing to do
-    const int tile = a.n_tiles - 1 - blockIdx.x;       // later tiles have more keys: start them first
+    // later tiles have more keys: they start first, and the heads of a tile follow one another, so that over
+    // the whole grid the blocks are handed out from the longest to the shortest
+    const int tile = a.n_tiles - 1 - blockIdx.y;
     const int q0 = a.tile_q0[tile];
     if (q0 % QM) return;
-    const int seq = a.tile_seq[tile], h = blockIdx.y;
+    const int seq = a.tile_seq[tile], h = blockIdx.x;
     const int row0 = a.seq_start[seq];
     const int n_new = a.seq_start[seq + 1] - row0;
     const int rows = min(QM, n_new - q0);
-    const int hd = a.head_dim, DB = hd / 64;           // 64-column blocks of a head
+    constexpr int hd = DB * 64;
     const int g = h / (a.n_heads / a.n_kv_heads);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -138,7 +142,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
     unsigned char* sK = sQ + q_bytes;                  // two stages
     unsigned char* sV = sK + 2 * kv_bytes;             // two stages
     unsigned char* sP = sV + 2 * kv_bytes;             // [128 rows][128 bytes]
-    __shared__ __align__(8) unsigned long long q_full, k_full[2], v_full[2], kv_empty[2], s_full, s_empty, p_full, pv_done;
+    __shared__ __align__(8) unsigned long long q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full, s_empty, p_full, pv_done;
     __shared__ uint32_t tmem_slot;
     const uint32_t tmem_cols = hd <= 64 ? 128 : (hd <= 192 ? 256 : 512);   // 64 for S, head_dim for O, a power of two
 
@@ -147,7 +151,8 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
         for (int s = 0; s < 2; ++s) {
             mbar_init(smem_u32(&k_full[s]), 1);
             mbar_init(smem_u32(&v_full[s]), 1);
-            mbar_init(smem_u32(&kv_empty[s]), 1);
+            mbar_init(smem_u32(&k_empty[s]), 1);
+            mbar_init(smem_u32(&v_empty[s]), 1);
         }
         mbar_init(smem_u32(&s_full), 1);
         mbar_init(smem_u32(&s_empty), 4);
@@ -177,30 +182,53 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
             mbar_expect_tx(smem_u32(&q_full), q_bytes);
             for (int c = 0; c < DB; ++c)
                 tma_load_2d(smem_u32(sQ + c * (QM * 128)), &map_q, h * hd + c * 64, row0 + q0, smem_u32(&q_full));
-            for (int j = 0; j < n_kv; ++j) {
+            // A key tile is free again as soon as its scores are computed, a value tile only after P V, one
+            // softmax later.  So the keys run one tile further ahead than the values: K(0), K(1), V(0), K(2),
+            // V(1), ...; this is also the order in which the buffers become free.
+            auto load_k = [&](int j) {
                 const int s = j & 1;
-                if (!mbar_wait_bounded(smem_u32(&kv_empty[s]), ((j >> 1) & 1) ^ 1)) { ok = false; break; }
-                const int y = row0 + kv_first + j * KN;
+                if (!mbar_wait_bounded(smem_u32(&k_empty[s]), ((j >> 1) & 1) ^ 1)) return false;
                 mbar_expect_tx(smem_u32(&k_full[s]), kv_bytes);
                 for (int c = 0; c < DB; ++c)
-                    tma_load_2d(smem_u32(sK + s * kv_bytes + c * (KN * 128)), &map_kv, (a.n_heads + g) * hd + c * 64, y, smem_u32(&k_full[s]));
+                    tma_load_2d(smem_u32(sK + s * kv_bytes + c * (KN * 128)), &map_kv, (a.n_heads + g) * hd + c * 64, row0 + kv_first + j * KN,
+                                smem_u32(&k_full[s]));
+                return true;
+            };
+            auto load_v = [&](int j) {
+                const int s = j & 1;
+                if (!mbar_wait_bounded(smem_u32(&v_empty[s]), ((j >> 1) & 1) ^ 1)) return false;
                 mbar_expect_tx(smem_u32(&v_full[s]), kv_bytes);
                 for (int c = 0; c < DB; ++c)
-                    tma_load_2d(smem_u32(sV + s * kv_bytes + c * (KN * 128)), &map_kv, (a.n_heads + a.n_kv_heads + g) * hd + c * 64, y,
-                                smem_u32(&v_full[s]));
+                    tma_load_2d(smem_u32(sV + s * kv_bytes + c * (KN * 128)), &map_kv, (a.n_heads + a.n_kv_heads + g) * hd + c * 64,
+                                row0 + kv_first + j * KN, smem_u32(&v_full[s]));
+                return true;
+            };
+            ok = load_k(0);
+            for (int j = 0; j < n_kv && ok; ++j) {
+                if (j + 1 < n_kv) ok = load_k(j + 1);
+                if (ok) ok = load_v(j);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             // ---- product issuer ----
             const uint32_t idesc_s = idesc_bf16(QM, KN, 0), idesc_o = idesc_bf16(QM, hd, 1);
+            // Descriptors are made once; a step along the head dimension adds to the address field (16-byte
+            // units): 2 for 16 elements inside a 64-column block, a block's size from one block to the next.
+            const uint64_t q_desc = desc_k_major(smem_u32(sQ));
+            const uint64_t k_desc0 = desc_k_major(smem_u32(sK)), k_desc1 = desc_k_major(smem_u32(sK + kv_bytes));
+            const uint64_t p_desc = desc_k_major(smem_u32(sP));
+            const uint64_t v_desc0 = desc_mn_major(smem_u32(sV), KN * 128), v_desc1 = desc_mn_major(smem_u32(sV + kv_bytes), KN * 128);
             auto issue_s = [&](int j) {
-                const uint32_t kaddr = smem_u32(sK + (j & 1) * kv_bytes);
+                const uint64_t kd = (j & 1) ? k_desc1 : k_desc0;
+#pragma unroll
                 for (int kk = 0; kk < hd / 16; ++kk) {
-                    const uint32_t blk = kk >> 2, in = (kk & 3) * 32;
-                    umma(tmem_s, desc_k_major(smem_u32(sQ) + blk * (QM * 128) + in), desc_k_major(kaddr + blk * (KN * 128) + in), idesc_s, kk != 0);
+                    const uint32_t qo = (uint32_t)((kk >> 2) * (QM * 128) + (kk & 3) * 32) >> 4;
+                    const uint32_t ko = (uint32_t)((kk >> 2) * (KN * 128) + (kk & 3) * 32) >> 4;
+                    umma(tmem_s, q_desc + qo, kd + ko, idesc_s, kk != 0);
                 }
                 umma_commit(smem_u32(&s_full));
+                umma_commit(smem_u32(&k_empty[j & 1]));
             };
             ok = mbar_wait_bounded(smem_u32(&q_full), 0) && mbar_wait_bounded(smem_u32(&k_full[0]), 0);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -208,17 +236,20 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
             for (int j = 0; j < n_kv && ok; ++j) {
                 if (j + 1 < n_kv) {
                     // the scores of the next tile are computed while the softmax of this one runs
-                    if (!mbar_wait_bounded(smem_u32(&s_empty), j & 1) || !mbar_wait_bounded(smem_u32(&k_full[(j + 1) & 1]), ((j + 1) >> 1) & 1)) { ok = false; break; }
+                    if (!mbar_wait_bounded(smem_u32(&s_empty), j & 1)) { ok = false; break; }
+                    if (!mbar_wait_bounded(smem_u32(&k_full[(j + 1) & 1]), ((j + 1) >> 1) & 1)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     issue_s(j + 1);
                 }
-                if (!mbar_wait_bounded(smem_u32(&p_full), j & 1) || !mbar_wait_bounded(smem_u32(&v_full[j & 1]), (j >> 1) & 1)) { ok = false; break; }
+                if (!mbar_wait_bounded(smem_u32(&p_full), j & 1)) { ok = false; break; }
+                if (!mbar_wait_bounded(smem_u32(&v_full[j & 1]), (j >> 1) & 1)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t vaddr = smem_u32(sV + (j & 1) * kv_bytes);
+                const uint64_t vd = (j & 1) ? v_desc1 : v_desc0;
+#pragma unroll
                 for (int kk = 0; kk < KN / 16; ++kk)
-                    umma(tmem_o, desc_k_major(smem_u32(sP) + kk * 32), desc_mn_major(vaddr + kk * (16 * 128), KN * 128), idesc_o, (j | kk) != 0);
+                    umma(tmem_o, p_desc + (uint32_t)(kk * 2), vd + (uint32_t)(kk * 128), idesc_o, (j | kk) != 0);
                 umma_commit(smem_u32(&pv_done));
-                umma_commit(smem_u32(&kv_empty[j & 1]));
+                umma_commit(smem_u32(&v_empty[j & 1]));
             }
         }
     } else {
@@ -317,24 +348,39 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
         }
         if (ok && !mbar_wait_bounded(smem_u32(&pv_done), (n_kv - 1) & 1)) ok = false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        // The rows go through shared memory (the query tile is no longer needed) so that the stores to
+        // global memory are whole 16-byte chunks of consecutive addresses: thread -> row on the way in
+        // (chunks swizzled by the row, no bank conflicts), thread -> chunk on the way out.
         if (ok) {
             const float inv = 1.0f / l;
-            __nv_bfloat16* orow = (__nv_bfloat16*)a.out + (long long)(row0 + q0 + r) * a.out_stride + (long long)h * hd;
+            unsigned char* srow = sQ + (size_t)r * (hd * 2);
+#pragma unroll
             for (int c = 0; c < hd; c += 32) {
                 float o[32];
                 tmem_ld32(tmem_o + lane_base + c, o);
-                if (r < rows) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        uint4 raw;
-                        __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&raw);
-                        hp[0] = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv);
-                        hp[1] = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
-                        hp[2] = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv);
-                        hp[3] = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);
-                        *reinterpret_cast<uint4*>(orow + c + i) = raw;
-                    }
+                for (int i = 0; i < 32; i += 8) {
+                    uint4 raw;
+                    __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&raw);
+                    hp[0] = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv);
+                    hp[1] = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
+                    hp[2] = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv);
+                    hp[3] = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);
+                    *reinterpret_cast<uint4*>(srow + ((((c + i) >> 3) ^ (r & 7)) * 16)) = raw;
                 }
+            }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");           // the four softmax warps, whatever became of their waits
+        {
+            constexpr int CHUNKS = hd / 8;                       // 16-byte chunks of a row
+            __nv_bfloat16* obase = (__nv_bfloat16*)a.out + (long long)(row0 + q0) * a.out_stride + (long long)h * hd;
+            const int tt = threadIdx.x - 64;
+#pragma unroll 4
+            for (int idx = tt; idx < QM * CHUNKS; idx += 128) {
+                const int row = idx / CHUNKS, c = idx - row * CHUNKS;
+                if (row < rows)
+                    *reinterpret_cast<uint4*>(obase + (long long)row * a.out_stride + c * 8) =
+                        *reinterpret_cast<const uint4*>(sQ + (size_t)row * (hd * 2) + ((c ^ (row & 7)) * 16));
             }
         }
     }
@@ -368,6 +414,18 @@ int make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols, 
     return 0;
 }
 
+template <int DB>
+int launch_tc(dim3 grid, int smem, cudaStream_t st, const CUtensorMap& map_q, const CUtensorMap& map_kv, const TcAttnArgs& t) {
+    static bool opted = false;
+    if (!opted) {
+        RDL_CUDA(cudaFuncSetAttribute(attention_tc_kernel<DB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "attention_prefill_tc");
+        opted = true;
+    }
+    attention_tc_kernel<DB><<<grid, ATC_THREADS, smem, st>>>(map_q, map_kv, t);
+    RDL_CHECK_LAUNCH("attention_prefill_tc");
+    return 0;
+}
+
 }  // namespace
 
 // Prefill attention of sequences that start at position 0, from packed rows [tokens, row_width] that hold
@@ -384,7 +442,7 @@ extern "C" int rdl_attention_prefill_tc(const AttentionArgs* a, long long row_wi
     RDL_REQUIRE(row_width >= (long long)(a->n_heads + 2 * a->n_kv_heads) * a->head_dim && row_width % 8 == 0 && (uintptr_t)a->q % 16 == 0,
                 "attention_prefill_tc: bad row width or alignment");
     RDL_REQUIRE(a->out_stride % 8 == 0 && (uintptr_t)a->out % 16 == 0, "attention_prefill_tc: output rows must start on 16-byte boundaries");
-    RDL_REQUIRE(a->n_heads <= 65535, "attention_prefill_tc: too many heads for the grid");
+    RDL_REQUIRE(a->n_tiles <= 65535, "attention_prefill_tc: %d query tiles exceed the grid limit", a->n_tiles);
     if (a->n_tiles == 0 || a->n_tokens == 0) return 0;
     CUtensorMap map_q, map_kv;
     if (int e = make_map(&map_q, a->q, a->n_tokens, row_width, QM)) return e;
@@ -392,13 +450,11 @@ extern "C" int rdl_attention_prefill_tc(const AttentionArgs* a, long long row_wi
     TcAttnArgs t{a->out, a->out_stride, a->tile_seq, a->tile_q0, a->n_tiles, a->seq_start, a->n_heads, a->n_kv_heads, a->head_dim,
                  a->score_scale, a->softcap, a->window, a->status};
     const int smem = QM * a->head_dim * 2 + 4 * KN * a->head_dim * 2 + QM * 128 + 1024;
-    static int granted = 0;
-    if (smem > granted) {
-        RDL_CUDA(cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "attention_prefill_tc");
-        granted = smem;
+    dim3 grid(a->n_heads, a->n_tiles);
+    switch (a->head_dim / 64) {
+        case 1: return launch_tc<1>(grid, smem, (cudaStream_t)stream, map_q, map_kv, t);
+        case 2: return launch_tc<2>(grid, smem, (cudaStream_t)stream, map_q, map_kv, t);
+        case 3: return launch_tc<3>(grid, smem, (cudaStream_t)stream, map_q, map_kv, t);
+        default: return launch_tc<4>(grid, smem, (cudaStream_t)stream, map_q, map_kv, t);
     }
-    dim3 grid(a->n_tiles, a->n_heads);
-    attention_tc_kernel<<<grid, ATC_THREADS, smem, (cudaStream_t)stream>>>(map_q, map_kv, t);
-    RDL_CHECK_LAUNCH("attention_prefill_tc");
-    return 0;
 }
