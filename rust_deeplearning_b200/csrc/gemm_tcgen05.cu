@@ -1,7 +1,10 @@
 // Matrix product for many rows (prefill) on the fifth-generation tensor cores:
 //   out[m, n] = epilogue(sum_k x[m, k] * w[n, k]),  bfloat16 operands, float accumulation in TMEM.
 //
-// One block computes a 128 x BN tile.  Operand tiles of 64 k (128 bytes a row) are brought into
+// Two kernels.  Where a tile's products are many (the gated form, sums of 4096 terms and more) a pair of
+// blocks on two multiprocessors computes a 256 x 256 tile with tcgen05.mma.cta_group::2 (further down).
+// Otherwise one block computes a 128 x BN tile (or two of them side by side):
+// one block computes a 128 x BN tile.  Operand tiles of 64 k (128 bytes a row) are brought into
 // shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle) through a ring of stages guarded
 // by mbarriers; one thread issues tcgen05.mma (M 128, N BN, K 16) from shared-memory descriptors,
 // accumulating in tensor memory; tcgen05.commit hands stages back to the loader and the finished
@@ -19,6 +22,7 @@
 // and every path ends in the common tear-down that frees the tensor memory.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -101,6 +105,33 @@ struct TcArgs {
     float softcap;
     int* status;
 };
+
+
+// 32 consecutive outputs of one row, from column `col`
+__device__ __forceinline__ void store_row_piece(const TcArgs& a, long long base, int col, bool vec, const float (&v)[32]) {
+    if (vec && col + 32 <= a.N) {
+        if (a.out_dtype == RDL_BF16) {
+            __nv_bfloat16* o = (__nv_bfloat16*)a.out + base;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+                uint4 raw;
+                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+                h[0] = __floats2bfloat162_rn(v[i], v[i + 1]);
+                h[1] = __floats2bfloat162_rn(v[i + 2], v[i + 3]);
+                h[2] = __floats2bfloat162_rn(v[i + 4], v[i + 5]);
+                h[3] = __floats2bfloat162_rn(v[i + 6], v[i + 7]);
+                *reinterpret_cast<uint4*>(o + i) = raw;
+            }
+        } else {
+            float* o = (float*)a.out + base;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        }
+    } else {
+        for (int i = 0; i < 32; ++i)
+            if (col + i < a.N) rdl_store(a.out, base + i, a.out_dtype, v[i]);
+    }
+}
 
 constexpr int RASTER_GROUP = 8;   // row tiles that share a weight tile and are scheduled together
 
@@ -218,31 +249,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = a.softcap * tanhf(v[i] / a.softcap);
                 }
-                if (row < a.M) {
-                    const long long base = (long long)row * a.N + n0 + c0;
-                    if (vec && n0 + c0 + 32 <= a.N) {
-                        if (a.out_dtype == RDL_BF16) {
-                            __nv_bfloat16* o = (__nv_bfloat16*)a.out + base;
-#pragma unroll
-                            for (int i = 0; i < 32; i += 8) {
-                                uint4 raw;
-                                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
-                                h[0] = __floats2bfloat162_rn(v[i], v[i + 1]);
-                                h[1] = __floats2bfloat162_rn(v[i + 2], v[i + 3]);
-                                h[2] = __floats2bfloat162_rn(v[i + 4], v[i + 5]);
-                                h[3] = __floats2bfloat162_rn(v[i + 6], v[i + 7]);
-                                *reinterpret_cast<uint4*>(o + i) = raw;
-                            }
-                        } else {
-                            float* o = (float*)a.out + base;
-#pragma unroll
-                            for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-                        }
-                    } else {
-                        for (int i = 0; i < 32; ++i)
-                            if (n0 + c0 + i < a.N) rdl_store(a.out, base + i, a.out_dtype, v[i]);
-                    }
-                }
+                if (row < a.M) store_row_piece(a, (long long)row * a.N + n0 + c0, n0 + c0, vec, v);
             }
         }
     }
@@ -251,6 +258,166 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+}
+
+
+// ---- two multiprocessors on one tile (cta_group::2) -------------------------------------------------
+//
+// A pair of blocks (a cluster of two) computes a 256 x 256 tile: block r of the pair holds rows
+// [128 r, 128 r + 128) of the activations and rows [128 r, 128 r + 128) of the weight tile, that is
+// half of each operand.  One thread of block 0 issues tcgen05.mma.cta_group::2 (M 256, N 256, K 16):
+// the tensor cores of both multiprocessors read both halves of the weight tile, and each writes its
+// 128 rows of the result into its own tensor memory.  Per product a multiprocessor then reads 8 KB of
+// shared memory for 64 cycles of arithmetic, where a single block that holds both operands whole reads
+// 12 KB - more than its shared memory delivers in that time.
+// Both blocks load their halves by TMA; all transfers of a stage report to one barrier in block 0,
+// and tcgen05.commit with a multicast to both blocks hands the stage back to both loaders.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_block(uint32_t addr, uint32_t rank) {      // the same place in the shared memory of block `rank`
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.aligned;\nbarrier.cluster.wait.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {        // arrives at `bar` in both blocks of the pair
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((unsigned short)3) : "memory");
+}
+
+constexpr int PAIR_BN = 256, PAIR_THREADS = 320;
+
+template <bool GATED>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, TcArgs a) {
+    constexpr int NB = GATED ? 2 : 1;
+    constexpr int HALF = PAIR_BN / 2;                                  // weight rows a block holds
+    constexpr int A_BYTES = BM * BK * 2, B_BYTES = HALF * BK * 2, STAGE_BYTES = A_BYTES + NB * B_BYTES;
+    constexpr int STAGES = GATED ? 4 : 6;
+    constexpr int TMEM_COLS = NB * PAIR_BN;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], done_bar;
+    __shared__ uint32_t tmem_slot;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    int m0, n0;                                                         // of the pair's tile
+    {
+        const int tiles_m = (a.M + 2 * BM - 1) / (2 * BM), tiles_n = (a.N + PAIR_BN - 1) / PAIR_BN;
+        const int pair = blockIdx.x >> 1;
+        const int per_group = RASTER_GROUP * tiles_n;
+        const int group = pair / per_group, in_group = pair - group * per_group;
+        const int first_m = group * RASTER_GROUP;
+        const int gm = tiles_m - first_m < RASTER_GROUP ? tiles_m - first_m : RASTER_GROUP;
+        m0 = (first_m + in_group % gm) * (2 * BM);
+        n0 = (in_group / gm) * PAIR_BN;
+    }
+    const int my_m0 = m0 + (int)rank * BM;
+    const int kblocks = (a.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        mbar_init(smem_u32(&done_bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {       // the same warp of both blocks: the allocation is made for the pair
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync();        // both blocks have their barriers and their tensor memory before anything crosses
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- loader (in both blocks): own half of each operand; every transfer reports to block 0 ----
+            for (int kb = 0; kb < kblocks; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t parity = ((kb / STAGES) & 1) ^ 1;
+                if (!mbar_wait_bounded(smem_u32(&empty_bar[s]), parity)) { ok = false; break; }
+                const uint32_t full = map_to_block(smem_u32(&full_bar[s]), 0);
+                unsigned char* stage = smem + (size_t)s * STAGE_BYTES;
+                if (rank == 0) mbar_expect_tx(smem_u32(&full_bar[s]), 2 * STAGE_BYTES);
+                tma_load_2d_pair(smem_u32(stage), &map_x, kb * BK, my_m0, full);
+                tma_load_2d_pair(smem_u32(stage + A_BYTES), &map_w, kb * BK, n0 + (int)rank * HALF, full);
+                if (GATED) tma_load_2d_pair(smem_u32(stage + A_BYTES + B_BYTES), &map_w, kb * BK, a.N + n0 + (int)rank * HALF, full);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            // ---- product issuer: one thread for the pair ----
+            constexpr uint32_t idesc = umma_idesc(2 * BM, PAIR_BN);
+            const uint64_t desc0 = umma_desc(smem_u32(smem));
+            for (int kb = 0; kb < kblocks && ok; ++kb) {
+                const int s = kb % STAGES;
+                if (!mbar_wait_bounded(smem_u32(&full_bar[s]), (kb / STAGES) & 1)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t adesc = desc0 + (uint32_t)((s * STAGE_BYTES) >> 4);
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k) {
+                    const uint32_t acc = (kb | k) != 0;
+                    umma_pair(tmem_base, adesc + (uint32_t)(k * 2), adesc + (uint32_t)((A_BYTES >> 4) + k * 2), idesc, acc);
+                    if (GATED) umma_pair(tmem_base + PAIR_BN, adesc + (uint32_t)(k * 2), adesc + (uint32_t)(((A_BYTES + B_BYTES) >> 4) + k * 2), idesc, acc);
+                }
+                umma_commit_pair(smem_u32(&empty_bar[s]));
+            }
+            umma_commit_pair(smem_u32(&done_bar));
+        }
+    } else {
+        // ---- epilogue: each block stores its own 128 rows ----
+        const int q = warp & 3;
+        const int col_half = (warp - 2) >> 2;
+        if (!mbar_wait_bounded(smem_u32(&done_bar), 0)) ok = false;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const bool vec = (a.N % 8) == 0;
+        const int row = my_m0 + q * 32 + lane;
+        const uint32_t tcol = tmem_base + ((uint32_t)(q * 32) << 16);
+        if (ok && my_m0 < a.M) {
+#pragma unroll 1
+            for (int c0 = col_half * (PAIR_BN / 2); c0 < (col_half + 1) * (PAIR_BN / 2); c0 += 32) {
+                if (n0 + c0 >= a.N) break;
+                float v[32];
+                tmem_ld32(tcol + c0, v);
+                if (GATED) {
+                    float u[32];
+                    tmem_ld32(tcol + PAIR_BN + c0, u);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = (a.activation == RDL_ACT_GELU_TANH ? gelu_tanh(v[i]) : silu(v[i])) * u[i];
+                }
+                if (a.softcap > 0.f) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = a.softcap * tanhf(v[i] / a.softcap);
+                }
+                if (row < a.M) store_row_piece(a, (long long)row * a.N + n0 + c0, n0 + c0, vec, v);
+            }
+        }
+    }
+    if (!ok && a.status) atomicExch(a.status, 4);
+    // ---- tear-down, reached by every thread of both blocks ----
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync();        // neither block leaves while the other may still read its shared memory or report to its barriers
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
 }
 
 // tensor map of a row-major bfloat16 matrix [rows, cols]: boxes of 64 columns (128 bytes, swizzled) x box_rows rows
@@ -301,6 +468,23 @@ int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs& a, cud
     return 0;
 }
 
+template <bool GATED>
+int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs& a, cudaStream_t st) {
+    constexpr int NB = GATED ? 2 : 1;
+    constexpr int STAGES = GATED ? 4 : 6;
+    const int smem = STAGES * (BM * BK * 2 + NB * (PAIR_BN / 2) * BK * 2) + 1024;
+    static bool opted = false;
+    if (!opted) {
+        RDL_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "gemm_tc");
+        opted = true;
+    }
+    const long long tiles = (long long)((a.N + PAIR_BN - 1) / PAIR_BN) * ((a.M + 2 * BM - 1) / (2 * BM));
+    RDL_REQUIRE(2 * tiles <= 0x7fffffffLL, "gemm_tc: %lld tiles exceed the grid limit", tiles);
+    gemm_tc_pair_kernel<GATED><<<dim3((unsigned)(2 * tiles)), PAIR_THREADS, smem, st>>>(mx, mw, a);
+    RDL_CHECK_LAUNCH("gemm_tc");
+    return 0;
+}
+
 }  // namespace
 
 extern "C" int rdl_gemm_tc(void* out, int out_dtype, const void* x, const void* w, int m, int n, int k,
@@ -313,10 +497,15 @@ extern "C" int rdl_gemm_tc(void* out, int out_dtype, const void* x, const void* 
     RDL_REQUIRE(!gated || activation == RDL_ACT_GELU_TANH || activation == RDL_ACT_SILU, "gemm_tc: unknown activation %d", activation);
     RDL_REQUIRE(softcap >= 0.f, "gemm_tc: soft-cap must not be negative");
     if (m == 0) return 0;
-    const int bn = gated ? 128 : 256;
+    // Pairs of multiprocessors on 256 x 256 tiles where a tile's products are many (the gated form, or a long
+    // sum): measured 5 to 10 % faster there; with a short sum the pair's longer set-up and drain cost more than
+    // they bring.  RDL_GEMM_PAIR=0 / 1 forces single blocks / pairs, for comparison.
+    static const int pair_mode = getenv("RDL_GEMM_PAIR") ? atoi(getenv("RDL_GEMM_PAIR")) : -1;
+    const bool pair = m > BM && (pair_mode == 1 || (pair_mode != 0 && (gated || k >= 4096)));
+    const int bn = pair ? PAIR_BN / 2 : (gated ? 128 : 256);      // weight rows per TMA box
     // two row tiles a block when that still fills most of the 148 multiprocessors
     const long long tiles2 = (long long)((n + bn - 1) / bn) * ((m + 2 * BM - 1) / (2 * BM));
-    const int mt = tiles2 >= 120 ? 2 : 1;
+    const int mt = pair ? 1 : (tiles2 >= 120 ? 2 : 1);
     CUtensorMap mx, mw;
     if (int e = make_map(&mx, x, m, k, mt * BM)) return e;
     {
@@ -332,6 +521,7 @@ extern "C" int rdl_gemm_tc(void* out, int out_dtype, const void* x, const void* 
     }
     TcArgs a{out, m, n, k, out_dtype, activation, softcap, status};
     cudaStream_t st = (cudaStream_t)stream;
+    if (pair) return gated ? launch_pair<true>(mx, mw, a, st) : launch_pair<false>(mx, mw, a, st);
     if (mt == 2) return gated ? launch_tc<128, true, 2>(mx, mw, a, st) : launch_tc<256, false, 2>(mx, mw, a, st);
     return gated ? launch_tc<128, true, 1>(mx, mw, a, st) : launch_tc<256, false, 1>(mx, mw, a, st);
 }

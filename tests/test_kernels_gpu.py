@@ -141,6 +141,19 @@ def test_tcgen05_gemm(m, n, k):
     assert status.item() == 0
 
 
+@pytest.mark.parametrize("m,n,k", [(300, 520, 4160), (129, 256, 4096), (513, 131, 4104)])
+def test_tcgen05_gemm_pair_long_sum(m, n, k):
+    """Sums of 4096 terms and more with more than one tile of rows go to the kernel that puts two
+    multiprocessors on one tile (as the gated products above do): tails in every dimension."""
+    x, w = rnd((m, k), torch.bfloat16, 27), rnd((n, k), torch.bfloat16, 28, 0.2)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    assert_close(ops.linear(x, w, status=status), ref.linear(x, w), torch.bfloat16, what="plain")
+    # float accumulation over k terms: k x 2^-24 bounds the sum's rounding relative to its scale
+    assert_close(ops.linear(x, w, out_dtype=torch.float32, status=status), ref.linear(x, w, torch.float32), torch.float32,
+                 what="float32 out", f32_tol=k * 2.0 ** -24)
+    assert status.item() == 0
+
+
 # ------------------------------------------------------------------------------------------
 # position encoding, cache write and attention
 # ------------------------------------------------------------------------------------------
