@@ -3,8 +3,8 @@
 //
 // Two kernels.  Where a tile's products are many (the gated form, sums of 4096 terms and more) a pair of
 // blocks on two multiprocessors computes a 256 x 256 tile with tcgen05.mma.cta_group::2 (further down).
-// Otherwise one block computes a 128 x BN tile (or two of them side by side):
-// one block computes a 128 x BN tile.  Operand tiles of 64 k (128 bytes a row) are brought into
+// Otherwise one block computes a 128 x BN tile (or two of them, one above the other, that share the
+// weight tile).  Operand tiles of 64 k (128 bytes a row) are brought into
 // shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle) through a ring of stages guarded
 // by mbarriers; one thread issues tcgen05.mma (M 128, N BN, K 16) from shared-memory descriptors,
 // accumulating in tensor memory; tcgen05.commit hands stages back to the loader and the finished
