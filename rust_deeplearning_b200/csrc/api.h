@@ -10,7 +10,7 @@ extern "C" {
 #define RDL_ACT_GELU_TANH 0
 #define RDL_ACT_SILU 1
 
-#define RDL_ABI_VERSION 6
+#define RDL_ABI_VERSION 7
 
 const char* rdl_last_error(void);
 int rdl_abi_version(void);
@@ -43,6 +43,10 @@ typedef struct {
     void* scratch; long long scratch_bytes;
     long long counter_bytes;   // size of the counter area at the start of scratch (rdl_attention_decode_counter_bytes)
     int* status;               // optional: set non-zero when a kernel gives up on a bounded wait
+    // decode kernel, optional (new_rows != 0): q, k_new and v_new are this step's rows as the projection left
+    // them, one token per sequence; the kernel rotates the query and key heads itself (float tables
+    // [position][rotary_dim / 2]; rotary_dim 0: no rotation) and writes the new key and value rows to the cache
+    const float* rope_cos; const float* rope_sin; int rotary_dim; int new_rows;
 } AttentionArgs;
 
 int rdl_attention_plain(const AttentionArgs* a, void* stream);

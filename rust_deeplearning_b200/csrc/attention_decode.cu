@@ -21,6 +21,11 @@
 // maximum (base-2 scale) and the normaliser [token][head][run][2].  Launches that share the scratch
 // must not overlap on the device.
 //
+// Optionally (new_rows) the kernel also does what otherwise a kernel of its own does before it: it
+// rotates the step's query heads and the new key row by the position's angles (rope_cache.cu has the
+// formula), writes the new key and value rows to the cache, and puts them into the copied page in
+// shared memory; one launch less per layer of a decode step.
+//
 // Every wait on a copy is bounded: after about a second without completion the block records
 // an error in `status` and leaves.
 #include "api.h"
@@ -94,6 +99,8 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
     __shared__ __align__(8) unsigned long long bar_storage[2];     // keys, values
     __shared__ float sm_m[DEC_WARPS][QROWS], sm_l[DEC_WARPS][QROWS];
     __shared__ int s_flag;
+    // new_rows: the rotated query heads of the group, then the new key row and the new value row
+    __shared__ __align__(16) __nv_bfloat16 new_s[(QROWS + 2) * 256];
 
     const int t = blockIdx.z, g = blockIdx.y, sp = blockIdx.x;
     const int hd = EXACT ? HD : a.head_dim, ps = a.page_size;
@@ -151,21 +158,69 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
     // finished.  (In a ring a new row of a later token of the same sequence could land in this page's
     // place, so there only a sequence's last token does it: the row it overwrites itself lies below
     // every page it reads.)
-    const bool early = a.seq_past != nullptr && (page_first + 1) * ps <= a.seq_past[seq] &&
-                       (a.window <= 0 || t == a.seq_start[seq + 1] - 1);
+    // With new_rows no other kernel writes the cache in this step: every first page is fetched early.
+    const bool fuse = a.new_rows != 0;
+    const bool early = fuse || (a.seq_past != nullptr && (page_first + 1) * ps <= a.seq_past[seq] &&
+                                (a.window <= 0 || t == a.seq_start[seq + 1] - 1));
     if (early && tid == 0) {
         issue(page_first, false);
         issue(page_first, true);
     }
     rdl_grid_wait();
     rdl_grid_launch_dependents();
+    const bool has_new = fuse && sp == n_splits - 1;          // this block's run ends with the token's own position
+    if (fuse) {
+        // 16-byte chunks of the group's query heads and, in the block that reads position p, of the new key
+        // and value rows: rotate (queries and key), keep in shared memory, write the new rows to the cache
+        const int half = a.rotary_dim >> 1;
+        const float* cs = a.rope_cos + (long long)p * half;
+        const float* sn = a.rope_sin + (long long)p * half;
+        const int items = (G + (has_new ? 2 : 0)) * chunks;
+        for (int idx = tid; idx < items; idx += DEC_THREADS) {
+            const int which = idx / chunks, c = idx - which * chunks, d0 = c * 8;
+            const __nv_bfloat16* src =
+                which < G ? (const __nv_bfloat16*)a.q + (long long)t * a.q_stride + (long long)(g * G + which) * hd
+                          : (const __nv_bfloat16*)(which == G ? a.k_new : a.v_new) + (long long)t * a.kv_stride + (long long)g * hd;
+            uint4 raw = *reinterpret_cast<const uint4*>(src + d0);
+            if (which <= G && d0 < a.rotary_dim) {
+                const bool first = d0 < half;                  // x[i] pairs with x[i + half]
+                const uint4 other = *reinterpret_cast<const uint4*>(src + (first ? d0 + half : d0 - half));
+                const int j = first ? d0 : d0 - half;
+                const float4 c0 = *reinterpret_cast<const float4*>(cs + j), c1 = *reinterpret_cast<const float4*>(cs + j + 4);
+                const float4 s0 = *reinterpret_cast<const float4*>(sn + j), s1 = *reinterpret_cast<const float4*>(sn + j + 4);
+                const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+                const float ss[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+                const __nv_bfloat162* xo = reinterpret_cast<const __nv_bfloat162*>(&raw);
+                const __nv_bfloat162* yo = reinterpret_cast<const __nv_bfloat162*>(&other);
+                uint4 res;
+                __nv_bfloat162* ro = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 x = __bfloat1622float2(xo[e]), y = __bfloat1622float2(yo[e]);
+                    // first half: x cos - y sin; second half (x is x[i + half], y is x[i]): y sin + x cos
+                    const float r0 = first ? x.x * cc[2 * e] - y.x * ss[2 * e] : y.x * ss[2 * e] + x.x * cc[2 * e];
+                    const float r1 = first ? x.y * cc[2 * e + 1] - y.y * ss[2 * e + 1] : y.y * ss[2 * e + 1] + x.y * cc[2 * e + 1];
+                    ro[e] = __floats2bfloat162_rn(r0, r1);
+                }
+                raw = res;
+            }
+            *reinterpret_cast<uint4*>(new_s + (which < G ? which : QROWS + which - G) * 256 + d0) = raw;
+            if (which >= G) {
+                __nv_bfloat16* cache = const_cast<__nv_bfloat16*>(which == G ? kcache : vcache);
+                *reinterpret_cast<uint4*>(cache + rdl_cache_offset(table, p, ps, a.ring_pages, a.n_kv_heads, g, hd) +
+                                          rdl_swizzled_chunk(p % ps, c, chunks) * 8) = raw;
+            }
+        }
+        __syncthreads();
+    }
     // The products are formed with the keys as rows: S^T [16 keys x 8 heads] = K [16 x d] Q^T [d x 8] and
     // O^T [d x 8 heads] += V^T [d x 16 keys] P^T [16 x 8].  Q^T is the B operand of every score product
     // of this block; it stays in registers: for k-step kk, {Q[head quad][16 kk + 2 tq .. +1], Q[..][16 kk + 8 + 2 tq .. +1]}.
     const int ksteps = hd / 16;
     uint32_t qf[HD / 16][2];
     {
-        const __nv_bfloat16* qrow = (const __nv_bfloat16*)a.q + (long long)t * a.q_stride + (long long)(g * G + quad) * hd;
+        const __nv_bfloat16* qrow = fuse ? new_s + (quad < G ? quad : 0) * 256
+                                         : (const __nv_bfloat16*)a.q + (long long)t * a.q_stride + (long long)(g * G + quad) * hd;
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
             qf[kk][0] = qf[kk][1] = 0u;
@@ -218,6 +273,14 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
         if (!mbar_wait_bounded(bar_k, phase)) {
             if (a.status) atomicExch(a.status, 3);
             return;
+        }
+        if (has_new && lp == page_last) {
+            // the copied page holds the row of position p as it was: put the new key there
+            const int r = p - lp * ps;
+            if (tid < chunks)
+                *reinterpret_cast<uint4*>(k_tile + (size_t)r * row_bytes + rdl_swizzled_chunk(r, tid, chunks) * 16) =
+                    *reinterpret_cast<const uint4*>(new_s + QROWS * 256 + tid * 8);
+            __syncthreads();
         }
         const int r_begin = max(k_begin, lp * ps) - lp * ps, r_end = min(k_end, (lp + 1) * ps) - lp * ps;
         const int w0 = warp * 16;                  // this warp's 16 keys of the page
@@ -278,6 +341,13 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
         if (!mbar_wait_bounded(bar_v, phase)) {
             if (a.status) atomicExch(a.status, 3);
             return;
+        }
+        if (has_new && lp == page_last) {
+            const int r = p - lp * ps;
+            if (tid < chunks)
+                *reinterpret_cast<uint4*>(v_tile + (size_t)r * row_bytes + rdl_swizzled_chunk(r, tid, chunks) * 16) =
+                    *reinterpret_cast<const uint4*>(new_s + (QROWS + 1) * 256 + tid * 8);
+            __syncthreads();
         }
         if (active) {
             if (w0 < r_begin || w0 + 16 > r_end) {
@@ -493,6 +563,15 @@ extern "C" int rdl_attention_decode(const AttentionArgs* a, void* stream) {
     RDL_REQUIRE(a->q_stride % 8 == 0 && (uintptr_t)a->q % 16 == 0 && (uintptr_t)a->k_cache % 16 == 0 &&
                     (uintptr_t)a->v_cache % 16 == 0 && (uintptr_t)a->scratch % 16 == 0 && a->out_stride % 2 == 0,
                 "attention_decode: rows must start on 16-byte boundaries");
+    if (a->new_rows) {
+        RDL_REQUIRE(a->k_new && a->v_new && a->kv_stride % 8 == 0 && (uintptr_t)a->k_new % 16 == 0 && (uintptr_t)a->v_new % 16 == 0,
+                    "attention_decode: the step's key and value rows must be given and start on 16-byte boundaries");
+        RDL_REQUIRE(a->rotary_dim >= 0 && a->rotary_dim <= a->head_dim && a->rotary_dim % 16 == 0,
+                    "attention_decode: rotary_dim %d must be a multiple of 16 and at most head_dim %d", a->rotary_dim, a->head_dim);
+        RDL_REQUIRE(a->rotary_dim == 0 || (a->rope_cos && a->rope_sin && (uintptr_t)a->rope_cos % 16 == 0 && (uintptr_t)a->rope_sin % 16 == 0),
+                    "attention_decode: rotation tables are missing or not on 16-byte boundaries");
+        RDL_REQUIRE(a->n_tokens <= a->n_seqs, "attention_decode: new rows are written for one token per sequence");
+    }
     if (a->n_tokens == 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
     if (a->head_dim == 64) return launch_decode<64, true>(a, st);

@@ -23,7 +23,7 @@ from concurrent.futures import ThreadPoolExecutor
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(_PKG, "csrc")
 LIB_NAME = "librdl_b200_kernels.so"
-ABI_VERSION = 6
+ABI_VERSION = 7
 
 # fast math is never enabled: the 32-bit path relies on exact tanhf/expf/sqrtf and plain FMA
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -155,6 +155,7 @@ class AttentionArgs(ctypes.Structure):
         ("keys_per_split", ctypes.c_int), ("max_splits", ctypes.c_int),
         ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_longlong),
         ("counter_bytes", ctypes.c_longlong), ("status", ctypes.c_void_p),
+        ("rope_cos", ctypes.c_void_p), ("rope_sin", ctypes.c_void_p), ("rotary_dim", ctypes.c_int), ("new_rows", ctypes.c_int),
     ]
 
 

@@ -329,7 +329,8 @@ def choose_keys_per_split(n_tokens: int, n_kv_heads: int, max_keys: int, page_si
 def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n_heads: int, n_kv_heads: int,
               head_dim: int, score_scale: float, softcap: Optional[float], window: Optional[int],
               new_kv: Optional[Tuple[torch.Tensor, int, int]] = None, kind: str = "auto",
-              scratch=None, keys_per_split: Optional[int] = None, status: Optional[torch.Tensor] = None):
+              scratch=None, keys_per_split: Optional[int] = None, status: Optional[torch.Tensor] = None,
+              rotate_and_write: Optional[Tuple[Optional[torch.Tensor], Optional[torch.Tensor], int]] = None):
     """Attention of the step's tokens over cache and new rows.
 
     q: [tokens, >= n_heads * head_dim] rows whose first n_heads * head_dim values are the (rotated)
@@ -342,6 +343,11 @@ def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n
     scratch: callable(nbytes) -> zero-initialised float32 tensor that only this kernel writes, for
     the decode kernel's counters and partial results.  status: int32 tensor that a kernel sets
     non-zero when it gives up on a bounded wait.
+    rotate_and_write (kind "decode", one token per sequence, `b` describing all keys as cached):
+    (cos, sin, rotary_dim) - q and new_kv are the rows as the projection left them; the kernel rotates
+    the query and key heads by the float32 tables [positions, rotary_dim / 2] (None, None, 0: no
+    rotation), writes the new key and value rows into the cache and attends over the cache including
+    them.  The packed rows themselves stay as they are.
     Returns [tokens, n_heads * head_dim] in the dtype of q."""
     _need(q.dim() == 2 and q.stride(1) == 1 and q.shape[1] >= n_heads * head_dim, "attention: bad query rows")
     T = q.shape[0]
@@ -388,7 +394,15 @@ def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n
         a.scratch, a.scratch_bytes = buf.data_ptr(), buf.numel() * 4
         a.counter_bytes = lib.rdl_attention_decode_counter_bytes(b.n_tokens, n_kv_heads)
         a.status = status.data_ptr() if status is not None else None
-        library.check(lib.rdl_attention_decode(ctypes.byref(a), _stream(q)), kernels=2)
+        if rotate_and_write is not None:
+            cos, sin, rotary_dim = rotate_and_write
+            _need(new_kv is not None, "attention: rotate_and_write needs the step's key and value rows")
+            if rotary_dim:
+                _need(cos.dtype is torch.float32 and sin.dtype is torch.float32 and cos.is_contiguous() and sin.is_contiguous()
+                      and cos.shape == sin.shape and cos.shape[1] * 2 == rotary_dim, "rotary tables must be float32 [positions, rotary_dim/2]")
+                a.rope_cos, a.rope_sin = cos.data_ptr(), sin.data_ptr()
+            a.rotary_dim, a.new_rows = int(rotary_dim), 1
+        library.check(lib.rdl_attention_decode(ctypes.byref(a), _stream(q)))
     else:
         raise KernelError(f"attention: unknown kind '{kind}'")
     return out

@@ -83,7 +83,14 @@ class Attention:
             return ops.linear(ctx, self.w_o)
 
         qkv = ops.linear(x, self.w_qkv)
-        if batch.is_decode:
+        if batch.is_decode and fast_decode and pages is not None and (tables is not None or self.position is None) \
+                and rotary_dim % 16 == 0:
+            # one kernel rotates, writes the new rows and attends over the cache
+            ab = batch.attention_batch("all", self.window)
+            ctx = ops.attention(qkv, ab, pages, new_kv=(qkv, self.q_width, self.q_width + self.kv_width), kind="decode",
+                                rotate_and_write=(tables[0], tables[1], rotary_dim) if tables is not None else (None, None, 0),
+                                scratch=lambda n: batch.scratch_buffer("decode", n), status=batch.status, **common)
+        elif batch.is_decode:
             # rotate, write the new row, then read everything from the cache
             if tables is not None or self.position is None:
                 ops.rope_cache(qkv, nh, nkv, hd, tok_seq=batch.tok_seq, tok_pos=batch.tok_pos,

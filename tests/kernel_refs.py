@@ -143,7 +143,14 @@ def rope_cache(qkv, n_heads, n_kv_heads, head_dim, *, tok_seq, tok_pos, cos=None
 
 
 def attention(q, b, pages, *, n_heads, n_kv_heads, head_dim, score_scale, softcap, window, new_kv=None,
-              kind="auto", scratch=None, keys_per_split=None, status=None):
+              kind="auto", scratch=None, keys_per_split=None, status=None, rotate_and_write=None):
+    if rotate_and_write is not None:
+        # the step's rows as the projection left them: rotate a copy, write the cache, then read everything from it
+        cos, sin, rotary_dim = rotate_and_write
+        assert new_kv is not None and new_kv[0] is q and q.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim
+        q = q.clone()
+        rope_cache(q, n_heads, n_kv_heads, head_dim, tok_seq=b.tok_seq, tok_pos=b.tok_pos, cos=cos if rotary_dim else None,
+                   sin=sin if rotary_dim else None, rotary_dim=rotary_dim, pages=pages, seq_end=b.seq_cached)
     T = q.shape[0]
     out = torch.zeros((T, n_heads * head_dim), dtype=q.dtype, device=q.device)
     group = n_heads // n_kv_heads

@@ -304,6 +304,37 @@ def test_decode_attention_over_cache(shape, keys_per_split):
         assert_close(plain, want, torch.bfloat16, rel=6.0, what="plain on the same case")
 
 
+@pytest.mark.parametrize("shape", DECODE_SHAPES)
+@pytest.mark.parametrize("rotary", ["whole", "half", "none"])
+def test_decode_attention_rotates_and_writes_the_new_rows(shape, rotary):
+    """The decode kernel doing the rotation and the cache write itself: output, both caches and the
+    untouched packed rows against the rotation + cache write + attention of the reference."""
+    shape = dict(shape)
+    past = shape.pop("past")
+    c = Case(past=past, new=[1] * len(past), dtype=torch.bfloat16, seed=45, **shape)
+    hd = c.head_dim
+    rotary_dim = {"whole": hd, "half": hd // 2, "none": 0}[rotary]
+    if rotary_dim % 16:
+        pytest.skip("the kernel takes rotations over a multiple of 16 elements")
+    b = c.batch("all")
+    half = max(rotary_dim // 2, 1)
+    ang = torch.arange(max(past) + 2, dtype=torch.float64)[:, None] / (50.0 ** (torch.arange(half, dtype=torch.float64) / half))
+    cos, sin = ang.cos().float().to(DEV).contiguous(), ang.sin().float().to(DEV).contiguous()
+    rw = (cos, sin, rotary_dim) if rotary_dim else (None, None, 0)
+    ref_pages = ops.KVPages(c.k.clone(), c.v.clone(), c.pages.tables, c.page_size, c.ring_pages)
+    want = ref.attention(c.qkv, b, ref_pages, new_kv=c.new_kv(), rotate_and_write=rw, **c.kw(softcap=9.0))
+    rows_before = c.qkv.clone()
+    for ks in (None, c.page_size):
+        got_pages = ops.KVPages(c.k.clone(), c.v.clone(), c.pages.tables, c.page_size, c.ring_pages)
+        got = ops.attention(c.qkv, b, got_pages, new_kv=c.new_kv(), kind="decode", keys_per_split=ks, rotate_and_write=rw,
+                            **c.kw(softcap=9.0))
+        assert_close(got, want, torch.bfloat16, rel=6.0, what=f"output, keys_per_split={ks}")
+        assert torch.equal(c.qkv, rows_before), "the packed rows must stay as the projection left them"
+        # value rows are copied (equal bits); key rows are rotated in float and rounded once, as the reference does
+        assert torch.equal(got_pages.v, ref_pages.v)
+        assert_close(got_pages.k, ref_pages.k, torch.bfloat16, rel=1.0, what="key cache")
+
+
 def test_attention_finds_one_far_key():
     """One key among a thousand is made to dominate: the output must be that key's value row.
     Shows a wrong page, a missed split or a window edge that random data would average away."""
