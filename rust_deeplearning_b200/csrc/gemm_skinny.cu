@@ -14,6 +14,8 @@
 //
 // The k index inside a 32-wide step is permuted identically for both operands (a lane's 16
 // bytes feed two instructions), which leaves every dot product unchanged.
+#include <cstdlib>
+
 #include "api.h"
 #include "common.cuh"
 #include "launch.cuh"
@@ -55,7 +57,9 @@ struct SkinnyArgs {
 };
 
 // NT: activation row tiles of 8 (M <= 8 * NT).  WARPS: warps that split K.  GATED: two weight streams.
-template <int NT, int WARPS, bool GATED>
+// DEPTH: chunks of weights a warp has in registers, one being multiplied and DEPTH - 1 on their way; a
+// narrow output has one block per multiprocessor and needs the deeper queue to keep HBM busy.
+template <int NT, int WARPS, bool GATED, int DEPTH>
 __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(SkinnyArgs a) {
     constexpr int NS = GATED ? 2 : 1;
     __shared__ float partial[WARPS][NS][NT][ROWS * 8];
@@ -98,41 +102,42 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(SkinnyArgs a) {
             }
         }
     };
-    // The weights are constants: the first chunk is requested before waiting for the kernel that
-    // produces x, and every later chunk while the chunk before it is being multiplied.
-    uint4 wcur[NS][4][2], wnext[NS][4][2];
+    // The weights are constants: the first chunks are requested before waiting for the kernel that
+    // produces x, and every later chunk while the chunks before it are being multiplied.
+    uint4 wbuf[DEPTH][NS][4][2];
+    constexpr int STEP = WARPS * KCHUNK;
     int kc = warp * KCHUNK;
-    if (kc < K) load_weights(kc, wcur);
+#pragma unroll
+    for (int d = 0; d < DEPTH - 1; ++d)
+        if (kc + d * STEP < K) load_weights(kc + d * STEP, wbuf[d]);
     rdl_grid_wait();
     rdl_grid_launch_dependents();
-    for (; kc < K; kc += WARPS * KCHUNK) {
-        const int kn = kc + WARPS * KCHUNK;
-        if (kn < K) load_weights(kn, wnext);
-        uint4 xb[NT][4];
+    while (kc < K) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int k = kc + u * 32 + t * 8;
-#pragma unroll
-            for (int i = 0; i < NT; ++i)
-                xb[i][u] = (k < K && x_ok[i]) ? __ldg(reinterpret_cast<const uint4*>(xrow[i] + k)) : zero4;
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-#pragma unroll
-            for (int s = 0; s < NS; ++s)
-#pragma unroll
-                for (int i = 0; i < NT; ++i) {
-                    mma_bf16(acc[s][i], wcur[s][u][0].x, wcur[s][u][1].x, wcur[s][u][0].y, wcur[s][u][1].y, xb[i][u].x, xb[i][u].y);
-                    mma_bf16(acc[s][i], wcur[s][u][0].z, wcur[s][u][1].z, wcur[s][u][0].w, wcur[s][u][1].w, xb[i][u].z, xb[i][u].w);
-                }
-        if (kn < K) {
-#pragma unroll
-            for (int s = 0; s < NS; ++s)
+        for (int d = 0; d < DEPTH; ++d) {          // buffer indices are compile-time: the ring lives in registers
+            if (kc < K) {
+                const int kn = kc + (DEPTH - 1) * STEP;
+                if (kn < K) load_weights(kn, wbuf[(d + DEPTH - 1) % DEPTH]);
+                uint4 xb[NT][4];
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
-                    wcur[s][u][0] = wnext[s][u][0];
-                    wcur[s][u][1] = wnext[s][u][1];
+                    const int k = kc + u * 32 + t * 8;
+#pragma unroll
+                    for (int i = 0; i < NT; ++i)
+                        xb[i][u] = (k < K && x_ok[i]) ? __ldg(reinterpret_cast<const uint4*>(xrow[i] + k)) : zero4;
                 }
+                const uint4 (&wcur)[NS][4][2] = wbuf[d];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int s = 0; s < NS; ++s)
+#pragma unroll
+                        for (int i = 0; i < NT; ++i) {
+                            mma_bf16(acc[s][i], wcur[s][u][0].x, wcur[s][u][1].x, wcur[s][u][0].y, wcur[s][u][1].y, xb[i][u].x, xb[i][u].y);
+                            mma_bf16(acc[s][i], wcur[s][u][0].z, wcur[s][u][1].z, wcur[s][u][0].w, wcur[s][u][1].w, xb[i][u].z, xb[i][u].w);
+                        }
+                kc += STEP;
+            }
         }
     }
     // accumulator element e of a lane: weight row g + 8 * (e >> 1), activation row 2 t + (e & 1)
@@ -167,13 +172,13 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(SkinnyArgs a) {
 
 thread_local cudaError_t g_launch_error = cudaSuccess;
 
-template <int NT, int WARPS>
+template <int NT, int WARPS, int DEPTH>
 void launch(const SkinnyArgs& a, cudaStream_t st) {
     const int blocks = (a.N + ROWS - 1) / ROWS;
     if (a.gated)
-        g_launch_error = rdl_launch(gemm_skinny_kernel<NT, WARPS, true>, dim3(blocks), dim3(WARPS * 32), 0, st, a);
+        g_launch_error = rdl_launch(gemm_skinny_kernel<NT, WARPS, true, 2>, dim3(blocks), dim3(WARPS * 32), 0, st, a);
     else
-        g_launch_error = rdl_launch(gemm_skinny_kernel<NT, WARPS, false>, dim3(blocks), dim3(WARPS * 32), 0, st, a);
+        g_launch_error = rdl_launch(gemm_skinny_kernel<NT, WARPS, false, DEPTH>, dim3(blocks), dim3(WARPS * 32), 0, st, a);
 }
 
 }  // namespace
@@ -193,10 +198,19 @@ extern "C" int rdl_gemm_skinny(void* out, int out_dtype, const void* x, const vo
     // few blocks (a narrow output): more warps per block keep enough loads in flight
     const int blocks = (n + ROWS - 1) / ROWS;
     const bool wide = blocks >= 2 * 148 || k < 8 * KCHUNK;
+    static const int depth_env = getenv("RDL_SKINNY_DEPTH") ? atoi(getenv("RDL_SKINNY_DEPTH")) : 0;
+    // at most one block per multiprocessor: four chunks in registers (measured: the 2304 x 9216 product 13.5 ->
+    // 11.2 us); otherwise two (three was slower than either)
+    const int depth = depth_env ? depth_env : (!wide && blocks <= 148 ? 4 : 2);
     if (m <= 8) {
-        if (wide) launch<1, 4>(a, st); else launch<1, 8>(a, st);
+        if (wide) launch<1, 4, 2>(a, st);
+        else if (depth >= 4) launch<1, 8, 4>(a, st);
+        else if (depth == 3) launch<1, 8, 3>(a, st);
+        else launch<1, 8, 2>(a, st);
     } else {
-        if (wide) launch<2, 4>(a, st); else launch<2, 8>(a, st);
+        if (wide) launch<2, 4, 2>(a, st);
+        else if (depth >= 3) launch<2, 8, 3>(a, st);
+        else launch<2, 8, 2>(a, st);
     }
     RDL_CHECK_EX(g_launch_error, "gemm_skinny");
     return 0;
