@@ -3,9 +3,15 @@
 // tensor-core fragments; the few activation rows come through L1/L2.  bfloat16 operands, float
 // accumulation (mma.sync m16n8k16: 16 weight rows x 8 activation rows per instruction).
 //
-// One block owns 16 weight rows (and, for the gated form, the 16 rows of the second matrix with
-// the same indices); its warps split K between them in interleaved chunks of 128 and their
-// partial sums are added in warp order through shared memory.
+// A unit of work is 16 weight rows (for the gated form: 8 gate rows and the 8 up rows of the same
+// outputs, which are the two halves of one 16-row fragment).  The warps of a block split K between
+// them in interleaved chunks of 128 and their partial sums are added in warp order through shared
+// memory.  A warp keeps a ring of chunks in registers (one being multiplied, the others on their way
+// from HBM; deeper where the output is so narrow that one block runs per multiprocessor).  When
+// there are more units than blocks fit the GPU at once, the grid is that many blocks and each goes
+// on to further units, requesting the next unit's first weights before it adds up the current one.
+// Under programmatic dependent launch the first weights are requested before the wait for the
+// kernel that produces the activations.
 //
 // Epilogues: plain store (bfloat16 or float), cap * tanh(v / cap) (the output head), and
 // act(gate) * up for a row-concatenated [gate; up] matrix (the feed-forward), all in float.
@@ -56,25 +62,39 @@ struct SkinnyArgs {
     float softcap;              // > 0: cap * tanh(v / cap)
 };
 
-// NT: activation row tiles of 8 (M <= 8 * NT).  WARPS: warps that split K.  GATED: two weight streams.
+// NT: activation row tiles of 8 (M <= 8 * NT).  WARPS: warps that split K.
 // DEPTH: chunks of weights a warp has in registers, one being multiplied and DEPTH - 1 on their way; a
 // narrow output has one block per multiprocessor and needs the deeper queue to keep HBM busy.
-template <int NT, int WARPS, bool GATED, int DEPTH>
+// GMODE: 0 plain; 1 gated, 16 outputs a block from two streams of 16 weight rows; 2 gated, 8 outputs a
+// block from one stream whose 16 rows are 8 gate rows and the 8 up rows of the same outputs (half the
+// registers of mode 1 and twice as many, smaller blocks).
+// PERSIST: a block goes on to further units (when there are more units than blocks fit the GPU at once).
+template <int NT, int WARPS, int GMODE, int DEPTH, bool PERSIST>
 __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(SkinnyArgs a) {
-    constexpr int NS = GATED ? 2 : 1;
+    constexpr bool GATED = GMODE != 0;
+    constexpr int NS = GMODE == 1 ? 2 : 1;
+    constexpr int OUT_ROWS = GMODE == 2 ? 8 : ROWS;          // outputs per activation row and block
     __shared__ float partial[WARPS][NS][NT][ROWS * 8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.x * ROWS;
     const int K = a.K;
-    const bool row0_ok = n0 + g < a.N, row1_ok = n0 + g + 8 < a.N;
+    const int n_units = (a.N + OUT_ROWS - 1) / OUT_ROWS;       // a unit: OUT_ROWS outputs for every activation row
+    // A block takes units blockIdx.x, blockIdx.x + gridDim.x, ...: the first weights of its next unit are
+    // requested before the sums of the current one are added up and stored.
+    int n0 = blockIdx.x * OUT_ROWS;
+    bool row0_ok, row1_ok;
     const __nv_bfloat16* wrow[NS][2];
+    auto set_unit = [&](int first_row) {
+        row0_ok = first_row + g < a.N;
+        row1_ok = GMODE == 2 ? row0_ok : first_row + g + 8 < a.N;
 #pragma unroll
-    for (int s = 0; s < NS; ++s) {
-        const long long base = (long long)(s * a.N + n0 + g) * K;
-        wrow[s][0] = a.w + base;
-        wrow[s][1] = a.w + base + 8LL * K;
-    }
+        for (int s = 0; s < NS; ++s) {
+            const long long base = (long long)(s * a.N + first_row + g) * K;
+            wrow[s][0] = a.w + base;
+            wrow[s][1] = a.w + base + (GMODE == 2 ? (long long)a.N : 8LL) * K;
+        }
+    };
+    set_unit(n0);
     const __nv_bfloat16* xrow[NT];
     bool x_ok[NT];
 #pragma unroll
@@ -82,12 +102,6 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(SkinnyArgs a) {
         x_ok[i] = i * 8 + g < a.M;
         xrow[i] = a.x + (long long)(i * 8 + g) * K;
     }
-    float acc[NS][NT][4];
-#pragma unroll
-    for (int s = 0; s < NS; ++s)
-#pragma unroll
-        for (int i = 0; i < NT; ++i) acc[s][i][0] = acc[s][i][1] = acc[s][i][2] = acc[s][i][3] = 0.f;
-
     const uint4 zero4 = make_uint4(0, 0, 0, 0);
     // one chunk of this warp's weights: 4 steps of 32 k, two rows per lane and stream
     auto load_weights = [&](int kc, uint4 (&wa)[NS][4][2]) {
@@ -106,79 +120,120 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(SkinnyArgs a) {
     // produces x, and every later chunk while the chunks before it are being multiplied.
     uint4 wbuf[DEPTH][NS][4][2];
     constexpr int STEP = WARPS * KCHUNK;
-    int kc = warp * KCHUNK;
+    auto request_first_chunks = [&]() {
 #pragma unroll
-    for (int d = 0; d < DEPTH - 1; ++d)
-        if (kc + d * STEP < K) load_weights(kc + d * STEP, wbuf[d]);
+        for (int d = 0; d < DEPTH - 1; ++d)
+            if (warp * KCHUNK + d * STEP < K) load_weights(warp * KCHUNK + d * STEP, wbuf[d]);
+    };
+    request_first_chunks();
     rdl_grid_wait();
     rdl_grid_launch_dependents();
-    while (kc < K) {
+    for (int unit = blockIdx.x;;) {
+        float acc[NS][NT][4];
 #pragma unroll
-        for (int d = 0; d < DEPTH; ++d) {          // buffer indices are compile-time: the ring lives in registers
-            if (kc < K) {
-                const int kn = kc + (DEPTH - 1) * STEP;
-                if (kn < K) load_weights(kn, wbuf[(d + DEPTH - 1) % DEPTH]);
-                uint4 xb[NT][4];
+        for (int s = 0; s < NS; ++s)
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int k = kc + u * 32 + t * 8;
+            for (int i = 0; i < NT; ++i) acc[s][i][0] = acc[s][i][1] = acc[s][i][2] = acc[s][i][3] = 0.f;
+        int kc = warp * KCHUNK;
+        while (kc < K) {
 #pragma unroll
-                    for (int i = 0; i < NT; ++i)
-                        xb[i][u] = (k < K && x_ok[i]) ? __ldg(reinterpret_cast<const uint4*>(xrow[i] + k)) : zero4;
+            for (int d = 0; d < DEPTH; ++d) {          // buffer indices are compile-time: the ring lives in registers
+                if (kc < K) {
+                    const int kn = kc + (DEPTH - 1) * STEP;
+                    if (kn < K) load_weights(kn, wbuf[(d + DEPTH - 1) % DEPTH]);
+                    uint4 xb[NT][4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int k = kc + u * 32 + t * 8;
+#pragma unroll
+                        for (int i = 0; i < NT; ++i)
+                            xb[i][u] = (k < K && x_ok[i]) ? __ldg(reinterpret_cast<const uint4*>(xrow[i] + k)) : zero4;
+                    }
+                    const uint4 (&wcur)[NS][4][2] = wbuf[d];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+#pragma unroll
+                        for (int s = 0; s < NS; ++s)
+#pragma unroll
+                            for (int i = 0; i < NT; ++i) {
+                                mma_bf16(acc[s][i], wcur[s][u][0].x, wcur[s][u][1].x, wcur[s][u][0].y, wcur[s][u][1].y, xb[i][u].x, xb[i][u].y);
+                                mma_bf16(acc[s][i], wcur[s][u][0].z, wcur[s][u][1].z, wcur[s][u][0].w, wcur[s][u][1].w, xb[i][u].z, xb[i][u].w);
+                            }
+                    kc += STEP;
                 }
-                const uint4 (&wcur)[NS][4][2] = wbuf[d];
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-#pragma unroll
-                    for (int s = 0; s < NS; ++s)
-#pragma unroll
-                        for (int i = 0; i < NT; ++i) {
-                            mma_bf16(acc[s][i], wcur[s][u][0].x, wcur[s][u][1].x, wcur[s][u][0].y, wcur[s][u][1].y, xb[i][u].x, xb[i][u].y);
-                            mma_bf16(acc[s][i], wcur[s][u][0].z, wcur[s][u][1].z, wcur[s][u][0].w, wcur[s][u][1].w, xb[i][u].z, xb[i][u].w);
-                        }
-                kc += STEP;
             }
         }
-    }
-    // accumulator element e of a lane: weight row g + 8 * (e >> 1), activation row 2 t + (e & 1)
+        // accumulator element e of a lane: weight row g + 8 * (e >> 1), activation row 2 t + (e & 1)
 #pragma unroll
-    for (int s = 0; s < NS; ++s)
+        for (int s = 0; s < NS; ++s)
 #pragma unroll
-        for (int i = 0; i < NT; ++i)
+            for (int i = 0; i < NT; ++i)
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-                partial[warp][s][i][(2 * t + (e & 1)) * ROWS + g + 8 * (e >> 1)] = acc[s][i][e];
-    __syncthreads();
-    // thread -> (activation row, weight row): 16 consecutive threads write 16 consecutive outputs
-    for (int idx = threadIdx.x; idx < NT * 8 * ROWS; idx += WARPS * 32) {
-        const int m = idx / ROWS, r = idx - m * ROWS;
-        const int n = n0 + r;
-        if (m >= a.M || n >= a.N) continue;
-        const int i = m >> 3, slot = (m & 7) * ROWS + r;
-        float v[NS];
-#pragma unroll
-        for (int s = 0; s < NS; ++s) {
-            float sum = 0.f;
-#pragma unroll
-            for (int w = 0; w < WARPS; ++w) sum += partial[w][s][i][slot];
-            v[s] = sum;
+                for (int e = 0; e < 4; ++e)
+                    partial[warp][s][i][(2 * t + (e & 1)) * ROWS + g + 8 * (e >> 1)] = acc[s][i][e];
+        const int next = unit + (int)gridDim.x;
+        const bool more = PERSIST && next < n_units;
+        if (more) {                       // the ring is empty now: the next unit's first weights set out
+            set_unit(next * OUT_ROWS);
+            request_first_chunks();
         }
-        float y = v[0];
-        if (GATED) y = (a.activation == RDL_ACT_GELU_TANH ? gelu_tanh(v[0]) : silu(v[0])) * v[NS - 1];
-        if (a.softcap > 0.f) y = a.softcap * tanhf(y / a.softcap);
-        rdl_store(a.out, (long long)m * a.N + n, a.out_dtype, y);
+        __syncthreads();
+        // thread -> (activation row, weight row): consecutive threads write consecutive outputs
+        for (int idx = threadIdx.x; idx < NT * 8 * OUT_ROWS; idx += WARPS * 32) {
+            const int m = idx / OUT_ROWS, r = idx - m * OUT_ROWS;
+            const int n = n0 + r;
+            if (m >= a.M || n >= a.N) continue;
+            const int i = m >> 3, slot = (m & 7) * ROWS + r;
+            float v[2];
+#pragma unroll
+            for (int s = 0; s < 2; ++s) {
+                float sum = 0.f;
+                if (s == 0 || GATED) {
+#pragma unroll
+                    for (int w = 0; w < WARPS; ++w) sum += GMODE == 2 ? partial[w][0][i][slot + 8 * s] : partial[w][s < NS ? s : 0][i][slot];
+                }
+                v[s] = sum;
+            }
+            float y = v[0];
+            if (GATED) y = (a.activation == RDL_ACT_GELU_TANH ? gelu_tanh(v[0]) : silu(v[0])) * v[1];
+            if (a.softcap > 0.f) y = a.softcap * tanhf(y / a.softcap);
+            rdl_store(a.out, (long long)m * a.N + n, a.out_dtype, y);
+        }
+        if (!more) break;
+        __syncthreads();                  // the partial sums are free again
+        unit = next;
+        n0 = unit * OUT_ROWS;
     }
 }
 
 thread_local cudaError_t g_launch_error = cudaSuccess;
 
+// blocks that fit the GPU at once for a kernel (asked of the runtime once per kernel)
+template <typename Kernel>
+int resident_blocks(Kernel kernel, int threads) {
+    int per_sm = 0, sms = 0, dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) != cudaSuccess || per_sm < 1 || sms < 1)
+        return 1 << 30;                   // unknown: one block per unit
+    return per_sm * sms;
+}
+
+template <int NT, int WARPS, int GMODE, int DEPTH>
+void launch_units(const SkinnyArgs& a, cudaStream_t st) {
+    static const int fit = resident_blocks(gemm_skinny_kernel<NT, WARPS, GMODE, DEPTH, true>, WARPS * 32);
+    static const bool persistent = !(getenv("RDL_SKINNY_PERSISTENT") && atoi(getenv("RDL_SKINNY_PERSISTENT")) == 0);
+    const int units = (a.N + (GMODE == 2 ? 8 : ROWS) - 1) / (GMODE == 2 ? 8 : ROWS);
+    if (persistent && units > fit)
+        g_launch_error = rdl_launch(gemm_skinny_kernel<NT, WARPS, GMODE, DEPTH, true>, dim3(fit), dim3(WARPS * 32), 0, st, a);
+    else
+        g_launch_error = rdl_launch(gemm_skinny_kernel<NT, WARPS, GMODE, DEPTH, false>, dim3(units), dim3(WARPS * 32), 0, st, a);
+}
+
 template <int NT, int WARPS, int DEPTH>
 void launch(const SkinnyArgs& a, cudaStream_t st) {
-    const int blocks = (a.N + ROWS - 1) / ROWS;
-    if (a.gated)
-        g_launch_error = rdl_launch(gemm_skinny_kernel<NT, WARPS, true, 2>, dim3(blocks), dim3(WARPS * 32), 0, st, a);
-    else
-        g_launch_error = rdl_launch(gemm_skinny_kernel<NT, WARPS, false, DEPTH>, dim3(blocks), dim3(WARPS * 32), 0, st, a);
+    if (a.gated == 2) launch_units<NT, 8, 2, 2>(a, st);
+    else if (a.gated) launch_units<NT, WARPS, 1, 2>(a, st);
+    else launch_units<NT, WARPS, 0, DEPTH>(a, st);
 }
 
 }  // namespace
@@ -193,7 +248,8 @@ extern "C" int rdl_gemm_skinny(void* out, int out_dtype, const void* x, const vo
     RDL_REQUIRE(!gated || activation == RDL_ACT_GELU_TANH || activation == RDL_ACT_SILU, "gemm_skinny: unknown activation %d", activation);
     RDL_REQUIRE(softcap >= 0.f, "gemm_skinny: soft-cap must not be negative");
     if (m == 0) return 0;
-    SkinnyArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, out, m, n, k, out_dtype, gated, activation, softcap};
+    static const int gmode_env = getenv("RDL_SKINNY_GATED") ? atoi(getenv("RDL_SKINNY_GATED")) : 2;
+    SkinnyArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, out, m, n, k, out_dtype, gated ? gmode_env : 0, activation, softcap};
     cudaStream_t st = (cudaStream_t)stream;
     // few blocks (a narrow output): more warps per block keep enough loads in flight
     const int blocks = (n + ROWS - 1) / ROWS;
