@@ -4,7 +4,8 @@
 // `keys_per_split` positions (a whole number of pages).  One block handles one run for all query
 // heads that share a kv head.  Each page of the run - [page_size][head_dim] keys and as many
 // values, each contiguous in the cache - is brought into shared memory by two bulk asynchronous
-// copies (TMA, cp.async.bulk + mbarrier).  The cache stores the 16-byte chunks of a row swizzled
+// copies (TMA, cp.async.bulk + mbarrier) into a ring of three tiles, so that a copy is requested a
+// page and a half before it is read.  The cache stores the 16-byte chunks of a row swizzled
 // by the row's place in its page (common.cuh), so the copied block is read by ldmatrix without
 // bank conflicts as it is.  The products run on the tensor cores (mma.sync m16n8k16, float
 // accumulators) with the keys as rows and the (up to 8) heads of the group as columns:
@@ -96,7 +97,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
 template <int HD, bool EXACT>
 __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(AttentionArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ __align__(8) unsigned long long bar_storage[2];     // keys, values
+    __shared__ __align__(8) unsigned long long bar_storage[3];     // one per tile of the ring
     __shared__ float sm_m[DEC_WARPS][QROWS], sm_l[DEC_WARPS][QROWS];
     __shared__ int s_flag;
     // new_rows: the rotated query heads of the group, then the new key row and the new value row
@@ -118,14 +119,14 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
     const int quad = lane >> 2, tq = lane & 3;
     const __nv_bfloat16* kcache = (const __nv_bfloat16*)a.k_cache;
     const __nv_bfloat16* vcache = (const __nv_bfloat16*)a.v_cache;
-    unsigned char* k_tile = smem;                                 // [page_size][head_dim] as stored: chunks swizzled by row
-    unsigned char* v_tile = k_tile + (size_t)ps * hd * 2;
+    // Three tiles of [page_size][head_dim] (as stored: chunks swizzled by row) used in turn by the run's
+    // key and value pages: K0 V0 K1 V1 ...; tile i of that sequence lives in place i % 3.  While one is read,
+    // the next two are on their way, so a copy is asked for a page and a half before it is needed.
     const int chunks = hd / 8;
-    const uint32_t k_s = (uint32_t)__cvta_generic_to_shared(k_tile);
-    const uint32_t v_s = (uint32_t)__cvta_generic_to_shared(v_tile);
-    const uint32_t bar_k = (uint32_t)__cvta_generic_to_shared(&bar_storage[0]);
-    const uint32_t bar_v = (uint32_t)__cvta_generic_to_shared(&bar_storage[1]);
     const uint32_t row_bytes = (uint32_t)hd * 2;
+    const uint32_t tile_bytes = (uint32_t)ps * row_bytes;
+    const uint32_t tiles_s = (uint32_t)__cvta_generic_to_shared(smem);
+    const uint32_t bars = (uint32_t)__cvta_generic_to_shared(&bar_storage[0]);
 
     const int page_first = k_begin / ps, page_last = (k_end - 1) / ps;
     // Ask L2 for the run's pages now.  Nothing read up to here was written by an earlier kernel of this
@@ -139,20 +140,23 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
         asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(vcache + off), "r"(ps * row_bytes) : "memory");
     }
     if (tid == 0) {
-        mbar_init(bar_k, 1);
-        mbar_init(bar_v, 1);
+        mbar_init(bars, 1);
+        mbar_init(bars + 8, 1);
+        mbar_init(bars + 16, 1);
     }
     __syncthreads();   // nobody waits on the barrier before it is initialised
     // A page's keys and its values are each one contiguous block: one bulk copy each (issued by thread 0).
-    // The copies of the next page are issued as soon as this page's tile is free: its keys travel while
-    // P V of this page is computed, its values while the next scores are.
-    auto issue = [&](int lp, bool values) {
-        const int page = table[lp % a.ring_pages];
+    // Tile i of the run is the keys (i even) or the values (i odd) of page page_first + i / 2.
+    const int n_tiles = 2 * (page_last - page_first + 1);
+    auto issue = [&](int i) {
+        const int page = table[(page_first + (i >> 1)) % a.ring_pages];
         const long long off = ((long long)page * a.n_kv_heads + g) * ps * hd;
+        const uint32_t place = (uint32_t)(i % 3);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_expect_tx(values ? bar_v : bar_k, ps * row_bytes);
-        bulk_load(values ? v_s : k_s, (values ? vcache : kcache) + off, ps * row_bytes, values ? bar_v : bar_k);
+        mbar_expect_tx(bars + 8 * place, tile_bytes);
+        bulk_load(tiles_s + place * tile_bytes, ((i & 1) ? vcache : kcache) + off, tile_bytes, bars + 8 * place);
     };
+    auto wait_tile = [&](int i) { return mbar_wait_bounded(bars + 8 * (uint32_t)(i % 3), (uint32_t)((i / 3) & 1)); };
     // The kernel before this one writes the step's new rows: positions from seq_past on.  A first page
     // that lies wholly below seq_past does not change any more and is fetched before that kernel has
     // finished.  (In a ring a new row of a later token of the same sequence could land in this page's
@@ -163,8 +167,9 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
     const bool early = fuse || (a.seq_past != nullptr && (page_first + 1) * ps <= a.seq_past[seq] &&
                                 (a.window <= 0 || t == a.seq_start[seq + 1] - 1));
     if (early && tid == 0) {
-        issue(page_first, false);
-        issue(page_first, true);
+        issue(0);
+        issue(1);
+        if (fuse && n_tiles > 2) issue(2);       // with new_rows no page of the run changes any more
     }
     rdl_grid_wait();
     rdl_grid_launch_dependents();
@@ -251,28 +256,39 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
         const uint32_t kx = (uint32_t)(((kr & 7) ^ (lane >> 4)) << 4), vx = (uint32_t)(((vr & 7) ^ ((lane >> 3) & 1)) << 4);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            ka[j] = k_s + kr * row_bytes + (kx ^ (uint32_t)(j << 5));
-            va[j] = v_s + vr * row_bytes + (vx ^ (uint32_t)(j << 5));
+            ka[j] = kr * row_bytes + (kx ^ (uint32_t)(j << 5));       // relative to the tile
+            va[j] = vr * row_bytes + (vx ^ (uint32_t)(j << 5));
         }
     }
+    uint32_t kb[4] = {0, 0, 0, 0}, vb[4] = {0, 0, 0, 0};   // ka, va in the tile that is being read
     auto k_addr = [&](int kk) -> uint32_t {
-        if (EXACT) return ka[kk & 3] + (uint32_t)((kk >> 2) * 128);
-        return k_s + kr * row_bytes + rdl_swizzled_chunk(kr, 2 * kk + (lane >> 4), chunks) * 16;
+        if (EXACT) return kb[kk & 3] + (uint32_t)((kk >> 2) * 128);
+        return kb[0] - ka[0] + kr * row_bytes + rdl_swizzled_chunk(kr, 2 * kk + (lane >> 4), chunks) * 16;
     };
     auto v_addr = [&](int db) -> uint32_t {
-        if (EXACT) return va[db & 3] + (uint32_t)((db >> 2) * 128);
-        return v_s + vr * row_bytes + rdl_swizzled_chunk(vr, 2 * db + ((lane >> 3) & 1), chunks) * 16;
+        if (EXACT) return vb[db & 3] + (uint32_t)((db >> 2) * 128);
+        return vb[0] - va[0] + vr * row_bytes + rdl_swizzled_chunk(vr, 2 * db + ((lane >> 3) & 1), chunks) * 16;
     };
 
-    if (!early && tid == 0) {
-        issue(page_first, false);
-        issue(page_first, true);
+    if (tid == 0) {
+        if (!early) {
+            issue(0);
+            issue(1);
+        }
+        if (!(early && fuse) && n_tiles > 2) issue(2);
     }
-    uint32_t phase = 0;
     for (int lp = page_first; lp <= page_last; ++lp) {
-        if (!mbar_wait_bounded(bar_k, phase)) {
+        const int ti = 2 * (lp - page_first);              // the tile of this page's keys; its values: ti + 1
+        if (!wait_tile(ti)) {
             if (a.status) atomicExch(a.status, 3);
             return;
+        }
+        unsigned char* k_tile = smem + (size_t)(ti % 3) * tile_bytes;
+        unsigned char* v_tile = smem + (size_t)((ti + 1) % 3) * tile_bytes;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            kb[j] = tiles_s + (uint32_t)(ti % 3) * tile_bytes + ka[j];
+            vb[j] = tiles_s + (uint32_t)((ti + 1) % 3) * tile_bytes + va[j];
         }
         if (has_new && lp == page_last) {
             // the copied page holds the row of position p as it was: put the new key there
@@ -336,9 +352,9 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
             asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pb0) : "r"(pack_bf16(e0, e1)));
             asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pb1) : "r"(pack_bf16(e2, e3)));
         }
-        __syncthreads();                                   // every warp is done with the key tile
-        if (lp < page_last && tid == 0) issue(lp + 1, false);
-        if (!mbar_wait_bounded(bar_v, phase)) {
+        __syncthreads();                                   // every warp is done with the key tile: its place takes tile ti + 3
+        if (ti + 3 < n_tiles && tid == 0) issue(ti + 3);
+        if (!wait_tile(ti + 1)) {
             if (a.status) atomicExch(a.status, 3);
             return;
         }
@@ -371,12 +387,11 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
             }
         }
         __syncthreads();                                   // every warp is done with the value tile
-        if (lp < page_last && tid == 0) issue(lp + 1, true);
-        phase ^= 1;
+        if (ti + 4 < n_tiles && tid == 0) issue(ti + 4);
     }
 
     // ---- merge the four warps through shared memory, in warp order ----
-    float* sm_o = reinterpret_cast<float*>(k_tile);  // [warp][head][HD]; the tiles are no longer needed
+    float* sm_o = reinterpret_cast<float*>(smem);    // [warp][head][HD]; the tiles are no longer needed
     if (quad == 0) {
         sm_m[warp][2 * tq] = m0; sm_m[warp][2 * tq + 1] = m1;
         sm_l[warp][2 * tq] = l0; sm_l[warp][2 * tq + 1] = l1;
@@ -513,14 +528,14 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
 
 template <int HD, bool EXACT>
 int launch_decode(const AttentionArgs* a, cudaStream_t st) {
-    const int tiles = 2 * a->page_size * a->head_dim * 2;
+    const int tiles = 3 * a->page_size * a->head_dim * 2;
     const int merge = DEC_WARPS * QROWS * HD * (int)sizeof(float);
     const int runs = (QROWS * a->max_splits + QROWS) * (int)sizeof(float);
     int smem = tiles > merge ? tiles : merge;
     if (runs > smem) smem = runs;
     RDL_REQUIRE(smem <= 200 * 1024, "attention_decode: page_size %d x head_dim %d needs %d bytes of shared memory, limit is 204800",
                 a->page_size, a->head_dim, smem);
-    static int granted = 48 * 1024;
+    static int granted = 32 * 1024;      // above this the kernel (which also has a few KB of static shared memory) opts in
     if (smem > granted) {
         RDL_CUDA(cudaFuncSetAttribute(attention_decode_kernel<HD, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
                  "attention_decode");

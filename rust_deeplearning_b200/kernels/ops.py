@@ -315,11 +315,8 @@ def _attention_args(q, q_stride, k_new, v_new, kv_stride, out, b: AttentionBatch
 def choose_keys_per_split(n_tokens: int, n_kv_heads: int, max_keys: int, page_size: int) -> int:
     """Keys per block of the decode kernel: runs of four pages (a block then streams its pages one after
     the other, and fewer partial results are merged), shorter ones while that leaves the GPU with
-    fewer than about one and a half blocks per multiprocessor, or when there are blocks for several
-    rounds in any case."""
+    fewer than about one and a half blocks per multiprocessor."""
     blocks = lambda pages: n_tokens * n_kv_heads * ((max_keys + pages * page_size - 1) // (pages * page_size))
-    if blocks(4) >= 888:        # several rounds of blocks anyway: shorter runs measured faster (less tail per block)
-        return 2 * page_size
     for pages in (4, 2):
         if blocks(pages) >= 222:
             return pages * page_size
