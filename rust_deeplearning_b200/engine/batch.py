@@ -36,6 +36,7 @@ class BatchLayout:
             off += -(-n // 4) * 4     # keep every field 16-byte aligned
 
         add("tokens", n_tokens)
+        add("token_src", n_tokens)
         add("tok_seq", n_tokens)
         add("tok_pos", n_tokens)
         add("seq_start", n_seqs + 1)
@@ -65,6 +66,7 @@ class StepBatch:
     is_decode: bool               # every sequence brings exactly one token
     max_total_len: int            # longest sequence after this step
     tokens: torch.Tensor
+    token_src: torch.Tensor       # for tokens taken from an earlier sampling on the device: the row of that result
     tok_seq: torch.Tensor
     tok_pos: torch.Tensor
     seq_start: torch.Tensor
@@ -102,9 +104,11 @@ class StepBatch:
 
 
 def fill_batch(host: np.ndarray, layout: BatchLayout, *, tokens: Sequence[Sequence[int]], past: Sequence[int],
-               slots: Sequence[int], want: Sequence[Sequence[int]], tables: Sequence[np.ndarray]):
+               slots: Sequence[int], want: Sequence[Sequence[int]], tables: Sequence[np.ndarray],
+               token_src: Optional[Sequence[int]] = None):
     """Write the batch description into `host` (int32, layout.size entries).  Returns
-    (real_tokens, n_want, n_tiles_used)."""
+    (real_tokens, n_want, n_tiles_used).  token_src: one-token sequences whose token ids are not known
+    on the host yet; entry i is the row of an earlier sampling's result that holds sequence i's token."""
     host[:] = 0
     v = lambda name: layout.view(host, name)
     tok, tok_seq, tok_pos = v("tokens"), v("tok_seq"), v("tok_pos")
@@ -135,6 +139,8 @@ def fill_batch(host: np.ndarray, layout: BatchLayout, *, tokens: Sequence[Sequen
                 n_tiles += 1
         row += n
     seq_start[len(tokens):] = row      # padding sequences are empty
+    if token_src is not None:
+        v("token_src")[:len(token_src)] = token_src
     for g, t in enumerate(tables):
         dst = v(f"table{g}").reshape(layout.n_seqs, layout.table_widths[g])
         dst[:t.shape[0]] = t
@@ -152,7 +158,7 @@ def batch_from_buffer(dev: torch.Tensor, layout: BatchLayout, *, real_tokens, re
     return StepBatch(
         layout=layout, n_tokens=layout.n_tokens, n_seqs=layout.n_seqs, real_tokens=real_tokens, real_seqs=real_seqs,
         n_want=n_want, is_decode=is_decode, max_total_len=max_total_len,
-        tokens=v("tokens"), tok_seq=v("tok_seq"), tok_pos=v("tok_pos"), seq_start=v("seq_start"),
+        tokens=v("tokens"), token_src=v("token_src"), tok_seq=v("tok_seq"), tok_pos=v("tok_pos"), seq_start=v("seq_start"),
         seq_past=v("seq_past"), seq_end=v("seq_end"), slots=v("slots"), want_rows=v("want_rows")[:n_want],
         tile_seq=v("tile_seq"), tile_q0=v("tile_q0"), n_tiles=n_tiles, tables=tables, device=dev.device,
         scratch=scratch if scratch is not None else {})

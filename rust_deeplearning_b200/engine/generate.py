@@ -9,12 +9,21 @@ that is still alive.  Sequences that end earlier leave the batch (their slot is 
 no request joins a running batch; requests that do not fit run as further batches, one after
 another, on the same cache.
 
+The loop runs one step ahead of what it has read: the step that feeds the sampled tokens back is
+queued with the ids still on the device (`Engine.step(..., fed=...)`), and only then are the ids of
+the step before read, so the device does not wait for the host between steps.  A sequence whose
+last token turns out to be a stop token has then been part of one step too many; that step's token
+for it is dropped.  With a repetition penalty the sampler needs every token on the host first, and
+the loop waits for each step.
+
 `plan_batches` and `SequenceState` hold the loop's decisions and need no device.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass, field
 from typing import Callable, Iterable, List, Optional, Sequence
+
+import torch
 
 from ..sampling.sampler import Sampler, SamplingParams
 
@@ -62,6 +71,11 @@ class SequenceState:
             return False
         return True
 
+    def may_go_on_after_one_more(self) -> bool:
+        """By the counts alone: could `accept` of one more token, whatever it is, let the sequence go on?"""
+        return (not self.finished and len(self.new_tokens) + 1 < self.max_new_tokens
+                and len(self.prompt) + len(self.new_tokens) + 1 <= self.max_context)
+
     def history(self) -> List[int]:
         return self.prompt + self.new_tokens
 
@@ -91,15 +105,36 @@ def plan_batches(prompt_lens: Sequence[int], max_new_tokens: int, *, max_seqs: i
     return batches
 
 
+class _Readback:
+    """Sampled ids on their way to the host: the copy into pinned memory is queued right behind the
+    sampling, and `tokens()` waits for that copy alone - not for whatever was queued after it."""
+
+    def __init__(self, sampled, pinned):
+        self.sampled, self.n = sampled, sampled.numel()
+        self.event = None
+        if sampled.device.type == "cuda":
+            self.host = pinned[:self.n]
+            self.host.copy_(sampled, non_blocking=True)
+            self.event = torch.cuda.Event()
+            self.event.record()
+
+    def tokens(self) -> List[int]:
+        if self.event is None:
+            return self.sampled.tolist()
+        self.event.synchronize()
+        return self.host.tolist()
+
+
 def generate(engine, prompts: Sequence[Sequence[int]], *, max_new_tokens: int = 256,
              sampling: Optional[SamplingParams] = None, stop_token_ids: Optional[Iterable[int]] = None,
              include_stop: bool = False, stream: Optional[Callable[[int, int], Optional[bool]]] = None,
-             max_batch: Optional[int] = None) -> List[GenerationResult]:
+             max_batch: Optional[int] = None, run_ahead: bool = True) -> List[GenerationResult]:
     """Generate for every prompt (lists of token ids).
 
     stop_token_ids: default, the model's end-of-sequence ids.  stream(request index, token) is
     called for every kept token; returning False ends that request (as the reference's streaming
-    callback does, generator.rs:277-318)."""
+    callback does, generator.rs:277-318).  run_ahead False waits for every step's tokens before the
+    next step is queued (the results are the same)."""
     sampling = sampling or SamplingParams()
     model, cache = engine.model, engine.cache
     stops = frozenset(model.spec.stop_token_ids if stop_token_ids is None else stop_token_ids)
@@ -118,29 +153,57 @@ def generate(engine, prompts: Sequence[Sequence[int]], *, max_new_tokens: int = 
         seqs = [SequenceState(i, prompts[i], max_new_tokens, max_context, stops, include_stop) for i in members]
         slots = [engine.new_sequence() for _ in seqs]
         try:
-            live = list(range(len(seqs)))
-            feed = [s.prompt for s in seqs]
-            while live:
-                logits = engine.step([slots[j] for j in live], feed, "last")
-                tokens = sampler.sample(logits, [seqs[j].request for j in live], [seqs[j].sampled for j in live],
-                                        [seqs[j].history() for j in live] if need_history else None)
-                tokens = tokens.tolist()
+            issued = [0] * len(seqs)            # samplings queued per sequence (keys its random stream)
+            pinned = None
+            if engine.device.type == "cuda":    # two buffers: one being read on the host, one being written by the device
+                pinned = [torch.empty(len(seqs), dtype=torch.int32).pin_memory() for _ in range(2)]
+            flip = [0]
+
+            def sample(rows, logits):
+                toks = sampler.sample(logits, [seqs[j].request for j in rows], [issued[j] for j in rows],
+                                      [seqs[j].history() for j in rows] if need_history else None)
+                for j in rows:
+                    issued[j] += 1
+                flip[0] ^= 1
+                return _Readback(toks, pinned[flip[0]] if pinned is not None else None)
+
+            rows = list(range(len(seqs)))       # the sequences whose tokens `sampled` holds, row by row
+            sampled = sample(rows, engine.step([slots[j] for j in rows], [s.prompt for s in seqs], "last"))
+            ahead = run_ahead and not need_history
+            while rows:
+                nxt_rows, nxt = [], None
+                if ahead:
+                    # queue the next step before this one's ids are read: everybody who, by the counts, may go on
+                    nxt_rows = [j for j in rows if seqs[j].may_go_on_after_one_more()]
+                    if nxt_rows:
+                        place = {j: i for i, j in enumerate(rows)}
+                        logits = engine.step([slots[j] for j in nxt_rows], None, "last",
+                                             fed=(sampled.sampled, [place[j] for j in nxt_rows]))
+                        nxt = sample(nxt_rows, logits)
+                tokens = sampled.tokens()
                 engine.check_status()
-                nxt_live, feed = [], []
-                for j, tok in zip(live, tokens):
+                go_on = []
+                for j, tok in zip(rows, tokens):
                     s = seqs[j]
+                    if s.finished:
+                        continue                # ended a step ago; this token comes from the step queued before that was known
                     before = len(s.new_tokens)
                     goes_on = s.accept(int(tok))
                     if stream is not None and len(s.new_tokens) > before:
                         if stream(s.request, int(tok)) is False and goes_on:
                             s.finish_reason, goes_on = "stop", False
                     if goes_on:
-                        nxt_live.append(j)
-                        feed.append([int(tok)])
+                        go_on.append((j, int(tok)))
                     else:
                         engine.release(slots[j])
                         slots[j] = None
-                live = nxt_live
+                if ahead:
+                    rows, sampled = nxt_rows, nxt
+                elif go_on:
+                    rows = [j for j, _ in go_on]
+                    sampled = sample(rows, engine.step([slots[j] for j in rows], [[tok] for _, tok in go_on], "last"))
+                else:
+                    rows = []
         finally:
             for sl in slots:
                 if sl is not None:

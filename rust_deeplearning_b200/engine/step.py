@@ -13,7 +13,7 @@ context bucket); everything else runs eagerly.  Padding changes no result.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence, Union
+from typing import Tuple, Dict, List, Optional, Sequence, Union
 
 import numpy as np
 import torch
@@ -85,15 +85,27 @@ class Engine:
             raise RuntimeError(f"a kernel reported fault {code} (1: token outside the vocabulary, 3: a copy did not complete)")
 
     # ---- the step ----
-    def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
-             want: Union[str, Sequence[Sequence[int]]] = "last") -> torch.Tensor:
+    def step(self, slots: Sequence[int], tokens: Optional[Sequence[Sequence[int]]],
+             want: Union[str, Sequence[Sequence[int]]] = "last",
+             fed: Optional[Tuple[torch.Tensor, Sequence[int]]] = None) -> torch.Tensor:
         """Run `tokens[i]` as the next tokens of sequence `slots[i]`.
+
+        fed (instead of tokens): every sequence brings one token whose id is still on the device:
+        (int32 result of an earlier sampling, for each sequence the row of that result).  The host
+        need not have read the ids, so this step can be queued while the one before it still runs.
 
         want: "last", "all", or for each sequence the places among its new tokens whose logits
         are wanted.  Returns float32 logits [wanted places, vocab] on the device, in the order of
         the sequences and of their wanted places.  When it comes from a graph the tensor is
         reused by the next step of the same shape: consume it before stepping again."""
         n = len(slots)
+        if fed is not None:
+            prev, src = fed
+            if tokens is not None or len(src) != n or prev.dtype is not torch.int32 or prev.dim() != 1:
+                raise StepError("fed tokens: an int32 vector of sampled ids and one row of it for each sequence, and no host tokens")
+            if n and not 0 <= min(src) <= max(src) < prev.numel():
+                raise StepError("fed tokens: a row outside the sampled result")
+            tokens = [[0]] * n
         if n == 0 or len(tokens) != n:
             raise StepError("a step needs at least one sequence and tokens for each")
         lens = [len(t) for t in tokens]
@@ -121,15 +133,18 @@ class Engine:
         is_decode = max(lens) == 1
 
         if is_decode and self.use_graphs:
-            logits = self._graph_step(slots, tokens, past, want, tables, widths, max(totals))
+            logits = self._graph_step(slots, tokens, past, want, tables, widths, max(totals), fed)
         else:
             n_want = sum(len(w) for w in want)
             layout = BatchLayout(sum(lens), n, max(n_want, 1), count_tiles(lens), widths)
             host = self._host_buffer(layout.size)
             real_tokens, n_want, n_tiles = fill_batch(host.numpy()[:layout.size], layout, tokens=tokens, past=past,
-                                                      slots=slots, want=want, tables=tables)
+                                                      slots=slots, want=want, tables=tables,
+                                                      token_src=fed[1] if fed is not None else None)
             dev = torch.empty(layout.size, dtype=torch.int32, device=self.device)
             self._upload(dev, host, layout.size)
+            if fed is not None:
+                self._take_fed_tokens(dev, layout, fed[0], n)
             batch = batch_from_buffer(dev, layout, real_tokens=real_tokens, real_seqs=n, n_want=n_want, n_tiles=n_tiles,
                                       is_decode=is_decode, max_total_len=max(totals), scratch=self._scratch)
             batch.status = self.status
@@ -158,7 +173,12 @@ class Engine:
             ev.record()
             self._pinned_event[self._flip] = ev
 
-    def _graph_step(self, slots, tokens, past, want, tables, widths, max_total):
+    @staticmethod
+    def _take_fed_tokens(dev: torch.Tensor, layout: BatchLayout, sampled: torch.Tensor, n: int):
+        """tokens[i] = sampled[token_src[i]], on the device."""
+        torch.index_select(sampled, 0, layout.view(dev, "token_src")[:n], out=layout.view(dev, "tokens")[:n])
+
+    def _graph_step(self, slots, tokens, past, want, tables, widths, max_total, fed=None):
         n = len(slots)
         n_pad = _next_pow2(n)
         len_bucket = min(max(_next_pow2(max_total), 256), self.cache.max_context)
@@ -175,8 +195,10 @@ class Engine:
         all_rows = [[0]] * n
         host = self._host_buffer(g.layout.size)
         fill_batch(host.numpy()[:g.layout.size], g.layout, tokens=tokens, past=past, slots=slots, want=all_rows,
-                   tables=tables)
+                   tables=tables, token_src=fed[1] if fed is not None else None)
         self._upload(g.dev, host, g.layout.size)
+        if fed is not None:
+            self._take_fed_tokens(g.dev, g.layout, fed[0], n)
         g.seen += 1
         if g.graph is None and g.seen >= 2:
             # the first step of a shape ran eagerly (and warmed the libraries up); capture now

@@ -104,6 +104,26 @@ def test_generate_batches_stop_tokens_and_early_ends(engine):
     assert r.tokens == plain.generate_greedy(cfg, w, long_prompt, 3)
 
 
+def test_running_one_step_ahead_changes_no_result(engine):
+    """The loop queues a step before it has read the tokens of the step before; with that switched off it
+    waits for every step.  Same tokens, same reasons, every slot and page given back - also when stop
+    tokens end sequences that are already part of a queued step."""
+    eng, _ = engine
+    rng = np.random.default_rng(8)
+    prompts = [[int(v) for v in rng.integers(0, 256, size=n)] for n in (3, 12, 7, 1, 9)]
+    for sampling in (SamplingParams(temperature=0.0), SamplingParams(temperature=0.8, top_k=50, seed=3)):
+        waited = generate(eng, prompts, max_new_tokens=7, sampling=sampling, stop_token_ids=[], run_ahead=False)
+        ahead = generate(eng, prompts, max_new_tokens=7, sampling=sampling, stop_token_ids=[])
+        assert [(r.tokens, r.finish_reason) for r in ahead] == [(r.tokens, r.finish_reason) for r in waited]
+        # stop at tokens that some sequences produce early, in the middle and as their last token
+        stops = {waited[0].tokens[0], waited[1].tokens[3], waited[2].tokens[6]}
+        waited = generate(eng, prompts, max_new_tokens=7, sampling=sampling, stop_token_ids=stops, run_ahead=False)
+        ahead = generate(eng, prompts, max_new_tokens=7, sampling=sampling, stop_token_ids=stops)
+        assert [(r.tokens, r.finish_reason) for r in ahead] == [(r.tokens, r.finish_reason) for r in waited]
+        assert any(r.finish_reason == "stop" for r in ahead)
+        assert eng.cache.n_free_slots == 3 and all(g.pool.n_free == g.pool.n_pages for g in eng.cache.kv_groups)
+
+
 def test_seeded_sampling_does_not_depend_on_the_batch(engine):
     eng, _ = engine
     rng = np.random.default_rng(6)

@@ -125,6 +125,22 @@ def test_skinny_gemm(m, n, k):
                  torch.bfloat16, what="gated, library product")
 
 
+@pytest.mark.parametrize("m", [2, 8, 13])
+def test_skinny_gemm_with_more_units_than_blocks_fit(m):
+    """A wide output has more 16-row units than blocks fit the GPU at once: blocks then go on to further
+    units (a few thousand here, with a tail that does not fill the last unit), in every form."""
+    n, k = 40003, 264
+    x, w = rnd((m, k), torch.bfloat16, 33), rnd((n, k), torch.bfloat16, 34, 0.2)
+    # the reference forms [m, n, k] in float64: in pieces of the output
+    got = ops.linear(x, w, out_dtype=torch.float32, softcap=2.0)
+    for lo in range(0, n, 8192):
+        assert_close(got[:, lo:lo + 8192], ref.linear(x, w[lo:lo + 8192], torch.float32, softcap=2.0), torch.float32, what=f"columns from {lo}")
+    n2 = 9001
+    wgu = rnd((2 * n2, k), torch.bfloat16, 35, 0.2)
+    assert_close(ops.linear_gated(x, wgu, "gelu_pytorch_tanh"), ref.linear_gated(x, wgu, "gelu_pytorch_tanh"), torch.bfloat16, what="gated")
+    assert_close(ops.linear(x, w[:n2]), ref.linear(x, w[:n2]), torch.bfloat16, what="plain")
+
+
 @pytest.mark.parametrize("m", [128, 129, 200, 2048])
 @pytest.mark.parametrize("n,k", [(256, 64), (384, 96), (131, 80), (2304, 2048), (520, 1160)])
 def test_tcgen05_gemm(m, n, k):
