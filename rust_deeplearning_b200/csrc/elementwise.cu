@@ -103,7 +103,7 @@ __global__ void norm_residual_norm_kernel(NormArgs a) {
 
 // The same operation with the row held in registers: every load of a row is issued before the
 // first reduction, so the kernel's critical path is one trip to memory and two block sums.  Used
-// when hidden is a multiple of 4 and at most 256 * 4 * ITER.
+// when hidden is a multiple of 4 and at most THREADS * 4 * ITER (ITER <= 8).
 __device__ __forceinline__ float4 load4(const void* p, long long i, int dtype) {
     if (dtype == RDL_BF16) {
         const uint2 raw = *reinterpret_cast<const uint2*>((const __nv_bfloat16*)p + i);
@@ -125,8 +125,8 @@ __device__ __forceinline__ void store4(void* p, long long i, int dtype, float4 v
     }
 }
 
-template <int ITER>
-__global__ void __launch_bounds__(256) norm_residual_norm_vec_kernel(NormArgs a) {
+template <int ITER, int THREADS>
+__global__ void __launch_bounds__(THREADS) norm_residual_norm_vec_kernel(NormArgs a) {
     __shared__ float scratch[33];
     rdl_grid_wait();
     rdl_grid_launch_dependents();
@@ -138,7 +138,7 @@ __global__ void __launch_bounds__(256) norm_residual_norm_vec_kernel(NormArgs a)
     const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int i = 0; i < ITER; ++i) {
-        const int j = (i * 256 + threadIdx.x) * 4;
+        const int j = (i * THREADS + threadIdx.x) * 4;
         const bool on = j < H;
         xv[i] = on ? load4(a.x, xin + j, a.x_dtype) : zero;
         rv[i] = (on && a.res) ? *reinterpret_cast<const float4*>(a.res + out + j) : zero;
@@ -162,7 +162,7 @@ __global__ void __launch_bounds__(256) norm_residual_norm_vec_kernel(NormArgs a)
     if (a.res) {
 #pragma unroll
         for (int i = 0; i < ITER; ++i) {
-            const int j = (i * 256 + threadIdx.x) * 4;
+            const int j = (i * THREADS + threadIdx.x) * 4;
             xv[i].x += rv[i].x; xv[i].y += rv[i].y; xv[i].z += rv[i].z; xv[i].w += rv[i].w;
             if (j < H) *reinterpret_cast<float4*>(a.res + out + j) = xv[i];
         }
@@ -178,7 +178,7 @@ __global__ void __launch_bounds__(256) norm_residual_norm_vec_kernel(NormArgs a)
     }
 #pragma unroll
     for (int i = 0; i < ITER; ++i) {
-        const int j = (i * 256 + threadIdx.x) * 4;
+        const int j = (i * THREADS + threadIdx.x) * 4;
         if (j >= H) continue;
         float4 v = xv[i];
         if (a.w2) {
@@ -204,10 +204,27 @@ extern "C" int rdl_norm_residual_norm(const void* x, int x_dtype, const int* row
         NormArgs a{x, x_dtype, row_index, w1, w1_dtype, eps1, off1, (float*)res_f32, w2, w2_dtype, eps2, off2, y, y_dtype, hidden};
         cudaStream_t st = (cudaStream_t)stream;
         cudaError_t e;
-        if (hidden <= 1024) e = rdl_launch(norm_residual_norm_vec_kernel<1>, dim3(n_rows), dim3(256), 0, st, a);
-        else if (hidden <= 2048) e = rdl_launch(norm_residual_norm_vec_kernel<2>, dim3(n_rows), dim3(256), 0, st, a);
-        else if (hidden <= 4096) e = rdl_launch(norm_residual_norm_vec_kernel<4>, dim3(n_rows), dim3(256), 0, st, a);
-        else e = rdl_launch(norm_residual_norm_vec_kernel<8>, dim3(n_rows), dim3(256), 0, st, a);
+        // Threads per row: few rows (decode) want the row spread over many threads; many rows (prefill) want
+        // every thread busy and more rows in flight per multiprocessor, so the block is the smallest of
+        // 128, 192 or 256 threads that covers the row with the fewest idle lanes.
+        const int quads = hidden / 4;
+        int threads = 256;
+        if (n_rows >= 256) {
+            int best_waste = 1 << 30;
+            for (int t = 128; t <= 256; t += 64) {
+                const int iter = (quads + t - 1) / t;
+                if (iter > 8) continue;
+                const int waste = iter * t - quads;
+                if (waste < best_waste) { best_waste = waste; threads = t; }
+            }
+        }
+        const int iter = (quads + threads - 1) / threads;
+#define RDL_NORM_CASE(I, T) if (iter == I && threads == T) e = rdl_launch(norm_residual_norm_vec_kernel<I, T>, dim3(n_rows), dim3(T), 0, st, a); else
+#define RDL_NORM_ITERS(T) RDL_NORM_CASE(1, T) RDL_NORM_CASE(2, T) RDL_NORM_CASE(3, T) RDL_NORM_CASE(4, T) RDL_NORM_CASE(5, T) RDL_NORM_CASE(6, T) RDL_NORM_CASE(7, T) RDL_NORM_CASE(8, T)
+        RDL_NORM_ITERS(128) RDL_NORM_ITERS(192) RDL_NORM_ITERS(256)
+        e = cudaErrorInvalidConfiguration;
+#undef RDL_NORM_ITERS
+#undef RDL_NORM_CASE
         RDL_CHECK_EX(e, "norm_residual_norm");
         return 0;
     }
