@@ -112,12 +112,30 @@ __global__ void __launch_bounds__(256) rope_cache_vec_kernel(T* __restrict__ qkv
         r = pos - logical * page_size;
         page_base = (long long)tables[(long long)seq * table_width + logical % ring_pages] * n_kv_heads;
     }
-    const int first_head = do_rope ? 0 : n_heads;     // without rotation the query heads need nothing
-    for (int item = first_head * chunks + threadIdx.x; item < total_heads * chunks; item += blockDim.x) {
-        const int head = item / chunks, c = item - head * chunks;
+    // Work items, one 16-byte chunk of output pair or chunk each, so that no thread idles: first the rotated
+    // pairs (chunk c with chunk c + half) of the query and key heads, then the chunks that are only copied
+    // to the cache: the unrotated tail of the key heads and the value heads.
+    const int n_pairs = (n_heads + n_kv_heads) * half_chunks;
+    const int k_tail = chunks - 2 * half_chunks;                  // unrotated chunks of a key head
+    const int n_copy = write ? n_kv_heads * (k_tail + chunks) : 0;
+    for (int item = threadIdx.x; item < n_pairs + n_copy; item += blockDim.x) {
+        int head, c;
+        bool rotated = item < n_pairs;
+        if (rotated) {
+            head = item / half_chunks;
+            c = item - head * half_chunks;
+        } else {
+            const int rest = item - n_pairs;
+            if (rest < n_kv_heads * k_tail) {
+                head = n_heads + rest / k_tail;
+                c = 2 * half_chunks + rest % k_tail;
+            } else {
+                const int v = rest - n_kv_heads * k_tail;
+                head = n_heads + n_kv_heads + v / chunks;
+                c = v % chunks;
+            }
+        }
         const bool is_q = head < n_heads, is_v = head >= n_heads + n_kv_heads;
-        const bool rotated = !is_v && c < 2 * half_chunks;
-        if (rotated && c >= half_chunks) continue;    // done together with its partner chunk
         T* row = base + (long long)head * head_dim;
         T* dst = nullptr;
         if (write && !is_q) {
@@ -127,10 +145,16 @@ __global__ void __launch_bounds__(256) rope_cache_vec_kernel(T* __restrict__ qkv
         float a[N];
         Chunk<T>::load(row + c * N, a);
         if (rotated) {
-            float b[N];
+            float b[N], cs[N], sn[N];
             Chunk<T>::load(row + (c + half_chunks) * N, b);
-            const float* cs = cos_t + (long long)pos * half + c * N;
-            const float* sn = sin_t + (long long)pos * half + c * N;
+            const float4* cp = reinterpret_cast<const float4*>(cos_t + (long long)pos * half + c * N);
+            const float4* sp = reinterpret_cast<const float4*>(sin_t + (long long)pos * half + c * N);
+#pragma unroll
+            for (int i = 0; i < N / 4; ++i) {
+                const float4 cv = __ldg(cp + i), sv = __ldg(sp + i);
+                cs[4 * i] = cv.x; cs[4 * i + 1] = cv.y; cs[4 * i + 2] = cv.z; cs[4 * i + 3] = cv.w;
+                sn[4 * i] = sv.x; sn[4 * i + 1] = sv.y; sn[4 * i + 2] = sv.z; sn[4 * i + 3] = sv.w;
+            }
             float lo[N], hi[N];
 #pragma unroll
             for (int i = 0; i < N; ++i) {
@@ -170,10 +194,14 @@ extern "C" int rdl_rope_cache(void* qkv, int dtype, int n_tokens, int n_heads, i
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
     const int per_chunk = dtype == RDL_BF16 ? 8 : 4;
-    const bool aligned = ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0;
+    const bool aligned = ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0 &&
+                         ((uintptr_t)cos_table & 15) == 0 && ((uintptr_t)sin_table & 15) == 0;
     if (aligned && head_dim % per_chunk == 0 && (!do_rope || (rotary_dim / 2) % per_chunk == 0)) {
-        const int items = total_heads * (head_dim / per_chunk);
-        const int vthreads = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
+        // two work items a thread where there are many (the kernel's comment says what an item is)
+        const int chunks = head_dim / per_chunk, half_chunks = do_rope ? rotary_dim / 2 / per_chunk : 0;
+        const int items = (n_heads + n_kv_heads) * half_chunks + n_kv_heads * (2 * chunks - 2 * half_chunks);
+        int vthreads = ((items + 1) / 2 + 31) / 32 * 32;
+        vthreads = vthreads < 64 ? 64 : (vthreads > 256 ? 256 : vthreads);
         if (dtype == RDL_BF16)
             e = rdl_launch(rope_cache_vec_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(vthreads), 0, st, (__nv_bfloat16*)qkv, n_heads,
                            n_kv_heads, head_dim, rotary_dim, cos_table, sin_table, tok_seq, tok_pos, do_rope, do_write,
