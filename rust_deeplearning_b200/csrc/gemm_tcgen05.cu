@@ -300,33 +300,40 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {        // arriv
 
 constexpr int PAIR_BN = 256, PAIR_THREADS = 320;
 
-template <bool GATED>
+__device__ __forceinline__ void mbar_arrive_at(uint32_t cluster_addr) {      // a barrier in any block of the cluster
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// The pair is persistent: it takes tiles pair, pair + pairs, ... of the grouped order.  The loaders run
+// ahead into the next tile while the current one is still being multiplied or stored, so a tile's
+// first operands are there when its products start.  Without the gate the accumulator takes half of
+// tensor memory and there are two: the products of a tile run while the tile before it is stored.
+template <bool GATED, int NACC>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, TcArgs a) {
     constexpr int NB = GATED ? 2 : 1;
     constexpr int HALF = PAIR_BN / 2;                                  // weight rows a block holds
     constexpr int A_BYTES = BM * BK * 2, B_BYTES = HALF * BK * 2, STAGE_BYTES = A_BYTES + NB * B_BYTES;
     constexpr int STAGES = GATED ? 4 : 6;
-    constexpr int TMEM_COLS = NB * PAIR_BN;
+    constexpr int TMEM_COLS = NACC * NB * PAIR_BN;                     // NACC accumulators of NB * 256 columns
+    static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "tensor memory has 512 columns");
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], done_bar;
+    __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], acc_full[NACC], acc_empty[NACC];
     __shared__ uint32_t tmem_slot;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
-    int m0, n0;                                                         // of the pair's tile
-    {
-        const int tiles_m = (a.M + 2 * BM - 1) / (2 * BM), tiles_n = (a.N + PAIR_BN - 1) / PAIR_BN;
-        const int pair = blockIdx.x >> 1;
+    const int tiles_m = (a.M + 2 * BM - 1) / (2 * BM), tiles_n = (a.N + PAIR_BN - 1) / PAIR_BN;
+    const int n_tiles = tiles_m * tiles_n, pairs = gridDim.x >> 1, first_tile = blockIdx.x >> 1;
+    auto tile_origin = [&](int tile, int& m0, int& n0) {
         const int per_group = RASTER_GROUP * tiles_n;
-        const int group = pair / per_group, in_group = pair - group * per_group;
+        const int group = tile / per_group, in_group = tile - group * per_group;
         const int first_m = group * RASTER_GROUP;
         const int gm = tiles_m - first_m < RASTER_GROUP ? tiles_m - first_m : RASTER_GROUP;
         m0 = (first_m + in_group % gm) * (2 * BM);
         n0 = (in_group / gm) * PAIR_BN;
-    }
-    const int my_m0 = m0 + (int)rank * BM;
+    };
     const int kblocks = (a.K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -334,7 +341,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             mbar_init(smem_u32(&full_bar[s]), 1);
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
-        mbar_init(smem_u32(&done_bar), 1);
+        for (int b = 0; b < NACC; ++b) {
+            mbar_init(smem_u32(&acc_full[b]), 1);
+            mbar_init(smem_u32(&acc_empty[b]), 16);        // the eight epilogue warps of both blocks (used in block 0)
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {       // the same warp of both blocks: the allocation is made for the pair
@@ -351,16 +361,20 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     if (warp == 0) {
         if (lane == 0) {
             // ---- loader (in both blocks): own half of each operand; every transfer reports to block 0 ----
-            for (int kb = 0; kb < kblocks; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t parity = ((kb / STAGES) & 1) ^ 1;
-                if (!mbar_wait_bounded(smem_u32(&empty_bar[s]), parity)) { ok = false; break; }
-                const uint32_t full = map_to_block(smem_u32(&full_bar[s]), 0);
-                unsigned char* stage = smem + (size_t)s * STAGE_BYTES;
-                if (rank == 0) mbar_expect_tx(smem_u32(&full_bar[s]), 2 * STAGE_BYTES);
-                tma_load_2d_pair(smem_u32(stage), &map_x, kb * BK, my_m0, full);
-                tma_load_2d_pair(smem_u32(stage + A_BYTES), &map_w, kb * BK, n0 + (int)rank * HALF, full);
-                if (GATED) tma_load_2d_pair(smem_u32(stage + A_BYTES + B_BYTES), &map_w, kb * BK, a.N + n0 + (int)rank * HALF, full);
+            int it = 0;                                     // k-blocks loaded so far, over all tiles
+            for (int tile = first_tile; tile < n_tiles && ok; tile += pairs) {
+                int m0, n0;
+                tile_origin(tile, m0, n0);
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait_bounded(smem_u32(&empty_bar[s]), ((it / STAGES) & 1) ^ 1)) { ok = false; break; }
+                    const uint32_t full = map_to_block(smem_u32(&full_bar[s]), 0);
+                    unsigned char* stage = smem + (size_t)s * STAGE_BYTES;
+                    if (rank == 0) mbar_expect_tx(smem_u32(&full_bar[s]), 2 * STAGE_BYTES);
+                    tma_load_2d_pair(smem_u32(stage), &map_x, kb * BK, m0 + (int)rank * BM, full);
+                    tma_load_2d_pair(smem_u32(stage + A_BYTES), &map_w, kb * BK, n0 + (int)rank * HALF, full);
+                    if (GATED) tma_load_2d_pair(smem_u32(stage + A_BYTES + B_BYTES), &map_w, kb * BK, a.N + n0 + (int)rank * HALF, full);
+                }
             }
         }
     } else if (warp == 1) {
@@ -368,48 +382,68 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             // ---- product issuer: one thread for the pair ----
             constexpr uint32_t idesc = umma_idesc(2 * BM, PAIR_BN);
             const uint64_t desc0 = umma_desc(smem_u32(smem));
-            for (int kb = 0; kb < kblocks && ok; ++kb) {
-                const int s = kb % STAGES;
-                if (!mbar_wait_bounded(smem_u32(&full_bar[s]), (kb / STAGES) & 1)) { ok = false; break; }
+            int it = 0, lt = 0;
+            for (int tile = first_tile; tile < n_tiles && ok; tile += pairs, ++lt) {
+                const int buf = lt % NACC;
+                // the accumulator must have been read out by the epilogue of the tile that used it last
+                if (!mbar_wait_bounded(smem_u32(&acc_empty[buf]), ((lt / NACC) & 1) ^ 1)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t adesc = desc0 + (uint32_t)((s * STAGE_BYTES) >> 4);
+                const uint32_t acc_addr = tmem_base + (uint32_t)(buf * NB * PAIR_BN);
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait_bounded(smem_u32(&full_bar[s]), (it / STAGES) & 1)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t adesc = desc0 + (uint32_t)((s * STAGE_BYTES) >> 4);
 #pragma unroll
-                for (int k = 0; k < BK / 16; ++k) {
-                    const uint32_t acc = (kb | k) != 0;
-                    umma_pair(tmem_base, adesc + (uint32_t)(k * 2), adesc + (uint32_t)((A_BYTES >> 4) + k * 2), idesc, acc);
-                    if (GATED) umma_pair(tmem_base + PAIR_BN, adesc + (uint32_t)(k * 2), adesc + (uint32_t)(((A_BYTES + B_BYTES) >> 4) + k * 2), idesc, acc);
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint32_t acc = (kb | k) != 0;
+                        umma_pair(acc_addr, adesc + (uint32_t)(k * 2), adesc + (uint32_t)((A_BYTES >> 4) + k * 2), idesc, acc);
+                        if (GATED) umma_pair(acc_addr + PAIR_BN, adesc + (uint32_t)(k * 2), adesc + (uint32_t)(((A_BYTES + B_BYTES) >> 4) + k * 2), idesc, acc);
+                    }
+                    umma_commit_pair(smem_u32(&empty_bar[s]));
                 }
-                umma_commit_pair(smem_u32(&empty_bar[s]));
+                if (ok) umma_commit_pair(smem_u32(&acc_full[buf]));
             }
-            umma_commit_pair(smem_u32(&done_bar));
         }
     } else {
-        // ---- epilogue: each block stores its own 128 rows ----
+        // ---- epilogue: each block stores its own 128 rows of every tile of the pair ----
         const int q = warp & 3;
         const int col_half = (warp - 2) >> 2;
-        if (!mbar_wait_bounded(smem_u32(&done_bar), 0)) ok = false;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const bool vec = (a.N % 8) == 0;
-        const int row = my_m0 + q * 32 + lane;
-        const uint32_t tcol = tmem_base + ((uint32_t)(q * 32) << 16);
-        if (ok && my_m0 < a.M) {
+        const uint32_t acc_empty_at_leader0 = map_to_block(smem_u32(&acc_empty[0]), 0);
+        int lt = 0;
+        for (int tile = first_tile; tile < n_tiles && ok; tile += pairs, ++lt) {
+            const int buf = lt % NACC;
+            int m0, n0;
+            tile_origin(tile, m0, n0);
+            const int my_m0 = m0 + (int)rank * BM;
+            if (!mbar_wait_bounded(smem_u32(&acc_full[buf]), (lt / NACC) & 1)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = my_m0 + q * 32 + lane;
+            const uint32_t tcol = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * NB * PAIR_BN);
+            if (my_m0 < a.M) {
 #pragma unroll 1
-            for (int c0 = col_half * (PAIR_BN / 2); c0 < (col_half + 1) * (PAIR_BN / 2); c0 += 32) {
-                if (n0 + c0 >= a.N) break;
-                float v[32];
-                tmem_ld32(tcol + c0, v);
-                if (GATED) {
-                    float u[32];
-                    tmem_ld32(tcol + PAIR_BN + c0, u);
+                for (int c0 = col_half * (PAIR_BN / 2); c0 < (col_half + 1) * (PAIR_BN / 2); c0 += 32) {
+                    if (n0 + c0 >= a.N) break;
+                    float v[32];
+                    tmem_ld32(tcol + c0, v);
+                    if (GATED) {
+                        float u[32];
+                        tmem_ld32(tcol + PAIR_BN + c0, u);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = (a.activation == RDL_ACT_GELU_TANH ? gelu_tanh(v[i]) : silu(v[i])) * u[i];
-                }
-                if (a.softcap > 0.f) {
+                        for (int i = 0; i < 32; ++i) v[i] = (a.activation == RDL_ACT_GELU_TANH ? gelu_tanh(v[i]) : silu(v[i])) * u[i];
+                    }
+                    if (a.softcap > 0.f) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = a.softcap * tanhf(v[i] / a.softcap);
+                        for (int i = 0; i < 32; ++i) v[i] = a.softcap * tanhf(v[i] / a.softcap);
+                    }
+                    if (row < a.M) store_row_piece(a, (long long)row * a.N + n0 + c0, n0 + c0, vec, v);
                 }
-                if (row < a.M) store_row_piece(a, (long long)row * a.N + n0 + c0, n0 + c0, vec, v);
             }
+            // this warp has read its part of the accumulator: tell the issuer in block 0
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_at(acc_empty_at_leader0 + (uint32_t)(buf * 8));
         }
     }
     if (!ok && a.status) atomicExch(a.status, 4);
@@ -468,19 +502,27 @@ int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs& a, cud
     return 0;
 }
 
-template <bool GATED>
+template <bool GATED, int NACC>
 int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs& a, cudaStream_t st) {
     constexpr int NB = GATED ? 2 : 1;
     constexpr int STAGES = GATED ? 4 : 6;
     const int smem = STAGES * (BM * BK * 2 + NB * (PAIR_BN / 2) * BK * 2) + 1024;
     static bool opted = false;
     if (!opted) {
-        RDL_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "gemm_tc");
+        RDL_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel<GATED, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "gemm_tc");
         opted = true;
     }
     const long long tiles = (long long)((a.N + PAIR_BN - 1) / PAIR_BN) * ((a.M + 2 * BM - 1) / (2 * BM));
-    RDL_REQUIRE(2 * tiles <= 0x7fffffffLL, "gemm_tc: %lld tiles exceed the grid limit", tiles);
-    gemm_tc_pair_kernel<GATED><<<dim3((unsigned)(2 * tiles)), PAIR_THREADS, smem, st>>>(mx, mw, a);
+    RDL_REQUIRE(tiles <= 0x3fffffffLL, "gemm_tc: %lld tiles are too many", tiles);
+    static int pairs_that_fit = 0;             // one block per multiprocessor: half as many pairs
+    if (!pairs_that_fit) {
+        int dev = 0, sms = 0;
+        RDL_CUDA(cudaGetDevice(&dev), "gemm_tc");
+        RDL_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "gemm_tc");
+        pairs_that_fit = sms / 2 > 0 ? sms / 2 : 1;
+    }
+    const int pairs = tiles < pairs_that_fit ? (int)tiles : pairs_that_fit;
+    gemm_tc_pair_kernel<GATED, NACC><<<dim3((unsigned)(2 * pairs)), PAIR_THREADS, smem, st>>>(mx, mw, a);
     RDL_CHECK_LAUNCH("gemm_tc");
     return 0;
 }
@@ -498,10 +540,12 @@ extern "C" int rdl_gemm_tc(void* out, int out_dtype, const void* x, const void* 
     RDL_REQUIRE(softcap >= 0.f, "gemm_tc: soft-cap must not be negative");
     if (m == 0) return 0;
     // Pairs of multiprocessors on 256 x 256 tiles where a tile's products are many (the gated form, or a long
-    // sum): measured 5 to 10 % faster there; with a short sum the pair's longer set-up and drain cost more than
-    // they bring.  RDL_GEMM_PAIR=0 / 1 forces single blocks / pairs, for comparison.
+    // sum) or where every pair gets several tiles (its second accumulator then hides the stores): measured 5 to
+    // 25 % faster there; with a short sum and few tiles the pair's longer set-up and drain cost more than they
+    // bring.  RDL_GEMM_PAIR=0 / 1 forces single blocks / pairs, for comparison.
     static const int pair_mode = getenv("RDL_GEMM_PAIR") ? atoi(getenv("RDL_GEMM_PAIR")) : -1;
-    const bool pair = m > BM && (pair_mode == 1 || (pair_mode != 0 && (gated || k >= 4096)));
+    const long long tiles_of_pairs = (long long)((n + 255) / 256) * ((m + 2 * BM - 1) / (2 * BM));
+    const bool pair = m > BM && (pair_mode == 1 || (pair_mode != 0 && (gated || k >= 4096 || tiles_of_pairs >= 4 * 74)));
     const int bn = pair ? PAIR_BN / 2 : (gated ? 128 : 256);      // weight rows per TMA box
     // two row tiles a block when that still fills most of the 148 multiprocessors
     const long long tiles2 = (long long)((n + bn - 1) / bn) * ((m + 2 * BM - 1) / (2 * BM));
@@ -521,7 +565,13 @@ extern "C" int rdl_gemm_tc(void* out, int out_dtype, const void* x, const void* 
     }
     TcArgs a{out, m, n, k, out_dtype, activation, softcap, status};
     cudaStream_t st = (cudaStream_t)stream;
-    if (pair) return gated ? launch_pair<true>(mx, mw, a, st) : launch_pair<false>(mx, mw, a, st);
+    if (pair) {
+        // a second accumulator (the products of a tile run while the tile before it is stored) where a pair
+        // gets more than one tile and tensor memory has room for it
+        const long long pair_tiles = (long long)((n + PAIR_BN - 1) / PAIR_BN) * ((m + 2 * BM - 1) / (2 * BM));
+        if (gated) return launch_pair<true, 1>(mx, mw, a, st);
+        return pair_tiles > 74 ? launch_pair<false, 2>(mx, mw, a, st) : launch_pair<false, 1>(mx, mw, a, st);
+    }
     if (mt == 2) return gated ? launch_tc<128, true, 2>(mx, mw, a, st) : launch_tc<256, false, 2>(mx, mw, a, st);
     return gated ? launch_tc<128, true, 1>(mx, mw, a, st) : launch_tc<256, false, 1>(mx, mw, a, st);
 }
