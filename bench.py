@@ -173,7 +173,7 @@ def main():
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "the reference is a Rust workspace (no Python package, no GPU code); no cargo/rustc in this image, "
-                          "pip install of /root/reference fails: neither setup.py nor pyproject.toml"}))
+                          "pip install of the reference tree fails: neither setup.py nor pyproject.toml"}))
         return 0
     if args.gpus != 1:
         print(f"bench.py measures one GPU: this library is single-GPU by design (got --gpus {args.gpus})")
