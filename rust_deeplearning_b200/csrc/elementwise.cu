@@ -125,8 +125,18 @@ __device__ __forceinline__ void store4(void* p, long long i, int dtype, float4 v
     }
 }
 
-template <int ITER, int THREADS>
-__global__ void __launch_bounds__(THREADS) norm_residual_norm_vec_kernel(NormArgs a) {
+// LATE (many rows): the weights are fetched where they are used (they come from the cache by then) instead of
+// being held in registers from the start, and the register count is bounded so that more rows are in
+// flight per multiprocessor: with many rows the kernel is bound by the bytes it has in flight.  With few
+// rows (decode) everything is requested at once: there the one row's latency is what counts.
+constexpr int norm_min_blocks(int iter, int threads, bool late) {
+    if (!late) return 1;
+    const int by_registers = 65536 / (threads * (8 * iter + (iter >= 4 ? 24 : 16))), by_threads = 2048 / threads;
+    const int n = by_registers < by_threads ? by_registers : by_threads;
+    return n < 1 ? 1 : n;
+}
+template <int ITER, int THREADS, bool LATE>
+__global__ void __launch_bounds__(THREADS, norm_min_blocks(ITER, THREADS, LATE)) norm_residual_norm_vec_kernel(NormArgs a) {
     __shared__ float scratch[33];
     rdl_grid_wait();
     rdl_grid_launch_dependents();
@@ -142,8 +152,10 @@ __global__ void __launch_bounds__(THREADS) norm_residual_norm_vec_kernel(NormArg
         const bool on = j < H;
         xv[i] = on ? load4(a.x, xin + j, a.x_dtype) : zero;
         rv[i] = (on && a.res) ? *reinterpret_cast<const float4*>(a.res + out + j) : zero;
-        w1v[i] = (on && a.w1) ? load4(a.w1, j, a.w1_dtype) : zero;
-        w2v[i] = (on && a.w2 && a.y) ? load4(a.w2, j, a.w2_dtype) : zero;
+        if (!LATE) {
+            w1v[i] = (on && a.w1) ? load4(a.w1, j, a.w1_dtype) : zero;
+            w2v[i] = (on && a.w2 && a.y) ? load4(a.w2, j, a.w2_dtype) : zero;
+        }
     }
     if (a.w1) {
         float ss = 0.f;
@@ -153,6 +165,10 @@ __global__ void __launch_bounds__(THREADS) norm_residual_norm_vec_kernel(NormArg
         const float inv = 1.0f / sqrtf(ss / (float)H + a.eps1);
 #pragma unroll
         for (int i = 0; i < ITER; ++i) {
+            if (LATE) {
+                const int j = (i * THREADS + threadIdx.x) * 4;
+                w1v[i] = j < H ? load4(a.w1, j, a.w1_dtype) : zero;
+            }
             xv[i].x = xv[i].x * inv * (w1v[i].x + a.off1);
             xv[i].y = xv[i].y * inv * (w1v[i].y + a.off1);
             xv[i].z = xv[i].z * inv * (w1v[i].z + a.off1);
@@ -182,6 +198,7 @@ __global__ void __launch_bounds__(THREADS) norm_residual_norm_vec_kernel(NormArg
         if (j >= H) continue;
         float4 v = xv[i];
         if (a.w2) {
+            if (LATE) w2v[i] = load4(a.w2, j, a.w2_dtype);
             v.x = v.x * inv2 * (w2v[i].x + a.off2);
             v.y = v.y * inv2 * (w2v[i].y + a.off2);
             v.z = v.z * inv2 * (w2v[i].z + a.off2);
@@ -219,9 +236,10 @@ extern "C" int rdl_norm_residual_norm(const void* x, int x_dtype, const int* row
             }
         }
         const int iter = (quads + threads - 1) / threads;
-#define RDL_NORM_CASE(I, T) if (iter == I && threads == T) e = rdl_launch(norm_residual_norm_vec_kernel<I, T>, dim3(n_rows), dim3(T), 0, st, a); else
-#define RDL_NORM_ITERS(T) RDL_NORM_CASE(1, T) RDL_NORM_CASE(2, T) RDL_NORM_CASE(3, T) RDL_NORM_CASE(4, T) RDL_NORM_CASE(5, T) RDL_NORM_CASE(6, T) RDL_NORM_CASE(7, T) RDL_NORM_CASE(8, T)
-        RDL_NORM_ITERS(128) RDL_NORM_ITERS(192) RDL_NORM_ITERS(256)
+        const bool late = n_rows >= 256;
+#define RDL_NORM_CASE(I, T, L) if (iter == I && threads == T && late == L) e = rdl_launch(norm_residual_norm_vec_kernel<I, T, L>, dim3(n_rows), dim3(T), 0, st, a); else
+#define RDL_NORM_ITERS(T, L) RDL_NORM_CASE(1, T, L) RDL_NORM_CASE(2, T, L) RDL_NORM_CASE(3, T, L) RDL_NORM_CASE(4, T, L) RDL_NORM_CASE(5, T, L) RDL_NORM_CASE(6, T, L) RDL_NORM_CASE(7, T, L) RDL_NORM_CASE(8, T, L)
+        RDL_NORM_ITERS(128, true) RDL_NORM_ITERS(192, true) RDL_NORM_ITERS(256, true) RDL_NORM_ITERS(256, false)
         e = cudaErrorInvalidConfiguration;
 #undef RDL_NORM_ITERS
 #undef RDL_NORM_CASE

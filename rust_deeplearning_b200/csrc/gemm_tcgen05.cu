@@ -96,7 +96,7 @@ __device__ __forceinline__ float gelu_tanh(float x) {
     asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * (x + 0.044715f * x * x * x)));
     return 0.5f * x * (1.0f + t);
 }
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.0f + __expf(fminf(-x, 80.0f))); }   // the divisor stays below 2^126
 
 struct TcArgs {
     void* out;
@@ -130,6 +130,84 @@ __device__ __forceinline__ void store_row_piece(const TcArgs& a, long long base,
     } else {
         for (int i = 0; i < 32; ++i)
             if (col + i < a.N) rdl_store(a.out, base + i, a.out_dtype, v[i]);
+    }
+}
+
+// ---- the epilogue of a warp: its 32 rows (tensor-memory lanes) of columns [c_begin, c_end) of the tile ----
+//
+// A thread reads consecutive columns of its own row, so a direct store instruction writes 16 bytes of 32
+// different rows: 32 partial lines.  For bfloat16 results the warp therefore passes 32 rows x 64 columns
+// (128 bytes a row) through 4 KB of shared memory of its own and writes them out with each instruction
+// covering four whole lines.  The 16-byte chunk c of row r lies at chunk c ^ (r & 7), which keeps both
+// the writes (a thread a row) and the reads (eight threads a row) free of bank conflicts.
+constexpr int EPI_STAGE_BYTES = 32 * 128;                  // a warp's staging area
+constexpr int EPI_WARPS = 8;
+
+template <bool GATED>
+__device__ __forceinline__ void epilogue_piece(const TcArgs& a, uint32_t taddr, uint32_t up_offset, float (&v)[32]) {
+    tmem_ld32(taddr, v);
+    if (GATED) {
+        float u[32];
+        tmem_ld32(taddr + up_offset, u);
+        // the choice is made once a piece, not once a value: otherwise both activations are computed for each
+        if (a.activation == RDL_ACT_GELU_TANH) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]) * u[i];
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = silu(v[i]) * u[i];
+        }
+    }
+    if (a.softcap > 0.f) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = a.softcap * tanhf(v[i] / a.softcap);
+    }
+}
+
+// tcol: tensor-memory address of the warp's lanes at column 0 of the tile; row0: the row of lane 0
+template <bool GATED>
+__device__ __forceinline__ void epilogue_columns(const TcArgs& a, uint32_t tcol, uint32_t up_offset, int c_begin, int c_end,
+                                                 int n0, int row0, int lane, unsigned char* stage) {
+    const bool vec = (a.N % 8) == 0;
+    const bool through_smem = vec && a.out_dtype == RDL_BF16;
+#pragma unroll 1
+    for (int c0 = c_begin; c0 < c_end; c0 += 64) {
+        if (n0 + c0 >= a.N) break;                         // uniform over the warp
+        if (through_smem && n0 + c0 + 64 <= a.N) {
+#pragma unroll
+            for (int p = 0; p < 2; ++p) {
+                float v[32];
+                epilogue_piece<GATED>(a, tcol + c0 + p * 32, up_offset, v);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    uint4 raw;
+                    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+                    h[0] = __floats2bfloat162_rn(v[8 * i], v[8 * i + 1]);
+                    h[1] = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]);
+                    h[2] = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]);
+                    h[3] = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
+                    *reinterpret_cast<uint4*>(stage + lane * 128 + (((p * 4 + i) ^ (lane & 7)) << 4)) = raw;
+                }
+            }
+            __syncwarp();
+            const int c = lane & 7;
+            __nv_bfloat16* o = (__nv_bfloat16*)a.out + (long long)row0 * a.N + n0 + c0 + c * 8;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int r = j * 4 + (lane >> 3);
+                const uint4 raw = *reinterpret_cast<const uint4*>(stage + r * 128 + ((c ^ (r & 7)) << 4));
+                if (row0 + r < a.M) *reinterpret_cast<uint4*>(o + (long long)r * a.N) = raw;
+            }
+            __syncwarp();                                  // the staging area is free for the next columns
+        } else {
+#pragma unroll 1
+            for (int p = 0; p < 2; ++p) {
+                if (n0 + c0 + p * 32 >= a.N) break;
+                float v[32];
+                epilogue_piece<GATED>(a, tcol + c0 + p * 32, up_offset, v);
+                if (row0 + lane < a.M) store_row_piece(a, (long long)(row0 + lane) * a.N + n0 + c0 + p * 32, n0 + c0 + p * 32, vec, v);
+            }
+        }
     }
 }
 
@@ -228,29 +306,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
         const int col_half = (warp - 2) >> 2;              // two warps share a quarter: each takes half of the columns
         if (!mbar_wait_bounded(smem_u32(&done_bar), 0)) ok = false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const bool vec = (a.N % 8) == 0;
+        unsigned char* stage = smem + (size_t)STAGES * STAGE_BYTES + (size_t)(warp - 2) * EPI_STAGE_BYTES;
 #pragma unroll 1
         for (int h = 0; h < MT && ok; ++h) {
-            const int row = m0 + h * BM + q * 32 + lane;
             if (m0 + h * BM >= a.M) break;                 // uniform over the block
             const uint32_t tcol = tmem_base + ((uint32_t)(q * 32) << 16) + h * NB * BN;
-#pragma unroll 1
-            for (int c0 = col_half * (BN / 2); c0 < (col_half + 1) * (BN / 2); c0 += 32) {
-                if (n0 + c0 >= a.N) break;                 // uniform over the warp
-                float v[32];
-                tmem_ld32(tcol + c0, v);
-                if (GATED) {
-                    float u[32];
-                    tmem_ld32(tcol + BN + c0, u);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = (a.activation == RDL_ACT_GELU_TANH ? gelu_tanh(v[i]) : silu(v[i])) * u[i];
-                }
-                if (a.softcap > 0.f) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = a.softcap * tanhf(v[i] / a.softcap);
-                }
-                if (row < a.M) store_row_piece(a, (long long)row * a.N + n0 + c0, n0 + c0, vec, v);
-            }
+            epilogue_columns<GATED>(a, tcol, BN, col_half * (BN / 2), (col_half + 1) * (BN / 2), n0, m0 + h * BM + q * 32, lane, stage);
         }
     }
     if (!ok && a.status) atomicExch(a.status, 4);
@@ -409,7 +470,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         // ---- epilogue: each block stores its own 128 rows of every tile of the pair ----
         const int q = warp & 3;
         const int col_half = (warp - 2) >> 2;
-        const bool vec = (a.N % 8) == 0;
+        unsigned char* stage = smem + (size_t)STAGES * STAGE_BYTES + (size_t)(warp - 2) * EPI_STAGE_BYTES;
         const uint32_t acc_empty_at_leader0 = map_to_block(smem_u32(&acc_empty[0]), 0);
         int lt = 0;
         for (int tile = first_tile; tile < n_tiles && ok; tile += pairs, ++lt) {
@@ -419,27 +480,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             const int my_m0 = m0 + (int)rank * BM;
             if (!mbar_wait_bounded(smem_u32(&acc_full[buf]), (lt / NACC) & 1)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int row = my_m0 + q * 32 + lane;
             const uint32_t tcol = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * NB * PAIR_BN);
-            if (my_m0 < a.M) {
-#pragma unroll 1
-                for (int c0 = col_half * (PAIR_BN / 2); c0 < (col_half + 1) * (PAIR_BN / 2); c0 += 32) {
-                    if (n0 + c0 >= a.N) break;
-                    float v[32];
-                    tmem_ld32(tcol + c0, v);
-                    if (GATED) {
-                        float u[32];
-                        tmem_ld32(tcol + PAIR_BN + c0, u);
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = (a.activation == RDL_ACT_GELU_TANH ? gelu_tanh(v[i]) : silu(v[i])) * u[i];
-                    }
-                    if (a.softcap > 0.f) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = a.softcap * tanhf(v[i] / a.softcap);
-                    }
-                    if (row < a.M) store_row_piece(a, (long long)row * a.N + n0 + c0, n0 + c0, vec, v);
-                }
-            }
+            if (my_m0 < a.M)
+                epilogue_columns<GATED>(a, tcol, PAIR_BN, col_half * (PAIR_BN / 2), (col_half + 1) * (PAIR_BN / 2), n0, my_m0 + q * 32, lane, stage);
             // this warp has read its part of the accumulator: tell the issuer in block 0
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -488,7 +531,7 @@ template <int BN, bool GATED, int MT>
 int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs& a, cudaStream_t st) {
     constexpr int NB = GATED ? 2 : 1;
     constexpr int STAGES = MT == 2 ? 3 : 4;
-    const int smem = STAGES * (MT * BM * BK * 2 + NB * BN * BK * 2) + 1024;
+    const int smem = STAGES * (MT * BM * BK * 2 + NB * BN * BK * 2) + EPI_WARPS * EPI_STAGE_BYTES + 1024;
     static bool opted = false;
     if (!opted) {
         RDL_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, GATED, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "gemm_tc");
@@ -506,7 +549,7 @@ template <bool GATED, int NACC>
 int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs& a, cudaStream_t st) {
     constexpr int NB = GATED ? 2 : 1;
     constexpr int STAGES = GATED ? 4 : 6;
-    const int smem = STAGES * (BM * BK * 2 + NB * (PAIR_BN / 2) * BK * 2) + 1024;
+    const int smem = STAGES * (BM * BK * 2 + NB * (PAIR_BN / 2) * BK * 2) + EPI_WARPS * EPI_STAGE_BYTES + 1024;
     static bool opted = false;
     if (!opted) {
         RDL_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel<GATED, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "gemm_tc");
