@@ -359,7 +359,7 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {        // arriv
                  ::"r"(bar), "h"((unsigned short)3) : "memory");
 }
 
-constexpr int PAIR_BN = 256, PAIR_THREADS = 320;
+constexpr int PAIR_BN = 256, PAIR_THREADS = 320, PAIR_STAGES = 6;
 
 __device__ __forceinline__ void mbar_arrive_at(uint32_t cluster_addr) {      // a barrier in any block of the cluster
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
@@ -367,16 +367,23 @@ __device__ __forceinline__ void mbar_arrive_at(uint32_t cluster_addr) {      // 
 
 // The pair is persistent: it takes tiles pair, pair + pairs, ... of the grouped order.  The loaders run
 // ahead into the next tile while the current one is still being multiplied or stored, so a tile's
-// first operands are there when its products start.  Without the gate the accumulator takes half of
-// tensor memory and there are two: the products of a tile run while the tile before it is stored.
+// first operands are there when its products start.  The accumulator takes half of tensor memory, so
+// there can be two: the products of a tile run while the tile before it is stored.  In the main loop a
+// block fetches 32 KB of operands for 512 cycles of products; at full rate that is more than the L2 cache
+// was seen to deliver to 148 multiprocessors (about 11.6 TB/s), so long sums run at about 80 % of the
+// tensor cores' rate.
+//
+// The gated form is the same product with other weight rows: block 0 of the pair loads 128 gate rows
+// and block 1 the 128 up rows of the same outputs, so the accumulator's columns [0, 128) are the gate and
+// [128, 256) the up values of a 256 x 128 tile of the result, and the epilogue multiplies them.
 template <bool GATED, int NACC>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, TcArgs a) {
-    constexpr int NB = GATED ? 2 : 1;
     constexpr int HALF = PAIR_BN / 2;                                  // weight rows a block holds
-    constexpr int A_BYTES = BM * BK * 2, B_BYTES = HALF * BK * 2, STAGE_BYTES = A_BYTES + NB * B_BYTES;
-    constexpr int STAGES = GATED ? 4 : 6;
-    constexpr int TMEM_COLS = NACC * NB * PAIR_BN;                     // NACC accumulators of NB * 256 columns
+    constexpr int OUT_BN = GATED ? HALF : PAIR_BN;                     // columns of the result a tile covers
+    constexpr int A_BYTES = BM * BK * 2, B_BYTES = HALF * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int STAGES = PAIR_STAGES;
+    constexpr int TMEM_COLS = NACC * PAIR_BN;                          // NACC accumulators of 256 columns
     static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "tensor memory has 512 columns");
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -385,7 +392,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
-    const int tiles_m = (a.M + 2 * BM - 1) / (2 * BM), tiles_n = (a.N + PAIR_BN - 1) / PAIR_BN;
+    const int tiles_m = (a.M + 2 * BM - 1) / (2 * BM), tiles_n = (a.N + OUT_BN - 1) / OUT_BN;
     const int n_tiles = tiles_m * tiles_n, pairs = gridDim.x >> 1, first_tile = blockIdx.x >> 1;
     auto tile_origin = [&](int tile, int& m0, int& n0) {
         const int per_group = RASTER_GROUP * tiles_n;
@@ -393,7 +400,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         const int first_m = group * RASTER_GROUP;
         const int gm = tiles_m - first_m < RASTER_GROUP ? tiles_m - first_m : RASTER_GROUP;
         m0 = (first_m + in_group % gm) * (2 * BM);
-        n0 = (in_group / gm) * PAIR_BN;
+        n0 = (in_group / gm) * OUT_BN;
     };
     const int kblocks = (a.K + BK - 1) / BK;
 
@@ -433,8 +440,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     unsigned char* stage = smem + (size_t)s * STAGE_BYTES;
                     if (rank == 0) mbar_expect_tx(smem_u32(&full_bar[s]), 2 * STAGE_BYTES);
                     tma_load_2d_pair(smem_u32(stage), &map_x, kb * BK, m0 + (int)rank * BM, full);
-                    tma_load_2d_pair(smem_u32(stage + A_BYTES), &map_w, kb * BK, n0 + (int)rank * HALF, full);
-                    if (GATED) tma_load_2d_pair(smem_u32(stage + A_BYTES + B_BYTES), &map_w, kb * BK, a.N + n0 + (int)rank * HALF, full);
+                    tma_load_2d_pair(smem_u32(stage + A_BYTES), &map_w, kb * BK, GATED ? n0 + (int)rank * a.N : n0 + (int)rank * HALF, full);
                 }
             }
         }
@@ -449,7 +455,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 // the accumulator must have been read out by the epilogue of the tile that used it last
                 if (!mbar_wait_bounded(smem_u32(&acc_empty[buf]), ((lt / NACC) & 1) ^ 1)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t acc_addr = tmem_base + (uint32_t)(buf * NB * PAIR_BN);
+                const uint32_t acc_addr = tmem_base + (uint32_t)(buf * PAIR_BN);
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (!mbar_wait_bounded(smem_u32(&full_bar[s]), (it / STAGES) & 1)) { ok = false; break; }
@@ -459,7 +465,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     for (int k = 0; k < BK / 16; ++k) {
                         const uint32_t acc = (kb | k) != 0;
                         umma_pair(acc_addr, adesc + (uint32_t)(k * 2), adesc + (uint32_t)((A_BYTES >> 4) + k * 2), idesc, acc);
-                        if (GATED) umma_pair(acc_addr + PAIR_BN, adesc + (uint32_t)(k * 2), adesc + (uint32_t)(((A_BYTES + B_BYTES) >> 4) + k * 2), idesc, acc);
                     }
                     umma_commit_pair(smem_u32(&empty_bar[s]));
                 }
@@ -480,9 +485,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             const int my_m0 = m0 + (int)rank * BM;
             if (!mbar_wait_bounded(smem_u32(&acc_full[buf]), (lt / NACC) & 1)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t tcol = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * NB * PAIR_BN);
+            const uint32_t tcol = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * PAIR_BN);
             if (my_m0 < a.M)
-                epilogue_columns<GATED>(a, tcol, PAIR_BN, col_half * (PAIR_BN / 2), (col_half + 1) * (PAIR_BN / 2), n0, my_m0 + q * 32, lane, stage);
+                epilogue_columns<GATED>(a, tcol, HALF, col_half * (OUT_BN / 2), (col_half + 1) * (OUT_BN / 2), n0, my_m0 + q * 32, lane, stage);
             // this warp has read its part of the accumulator: tell the issuer in block 0
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -547,15 +552,14 @@ int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs& a, cud
 
 template <bool GATED, int NACC>
 int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs& a, cudaStream_t st) {
-    constexpr int NB = GATED ? 2 : 1;
-    constexpr int STAGES = GATED ? 4 : 6;
-    const int smem = STAGES * (BM * BK * 2 + NB * (PAIR_BN / 2) * BK * 2) + EPI_WARPS * EPI_STAGE_BYTES + 1024;
+    constexpr int OUT_BN = GATED ? PAIR_BN / 2 : PAIR_BN;
+    const int smem = PAIR_STAGES * (BM * BK * 2 + (PAIR_BN / 2) * BK * 2) + EPI_WARPS * EPI_STAGE_BYTES + 1024;
     static bool opted = false;
     if (!opted) {
         RDL_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel<GATED, NACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "gemm_tc");
         opted = true;
     }
-    const long long tiles = (long long)((a.N + PAIR_BN - 1) / PAIR_BN) * ((a.M + 2 * BM - 1) / (2 * BM));
+    const long long tiles = (long long)((a.N + OUT_BN - 1) / OUT_BN) * ((a.M + 2 * BM - 1) / (2 * BM));
     RDL_REQUIRE(tiles <= 0x3fffffffLL, "gemm_tc: %lld tiles are too many", tiles);
     static int pairs_that_fit = 0;             // one block per multiprocessor: half as many pairs
     if (!pairs_that_fit) {
@@ -611,8 +615,9 @@ extern "C" int rdl_gemm_tc(void* out, int out_dtype, const void* x, const void* 
     if (pair) {
         // a second accumulator (the products of a tile run while the tile before it is stored) where a pair
         // gets more than one tile and tensor memory has room for it
-        const long long pair_tiles = (long long)((n + PAIR_BN - 1) / PAIR_BN) * ((m + 2 * BM - 1) / (2 * BM));
-        if (gated) return launch_pair<true, 1>(mx, mw, a, st);
+        const int out_bn = gated ? PAIR_BN / 2 : PAIR_BN;
+        const long long pair_tiles = (long long)((n + out_bn - 1) / out_bn) * ((m + 2 * BM - 1) / (2 * BM));
+        if (gated) return pair_tiles > 74 ? launch_pair<true, 2>(mx, mw, a, st) : launch_pair<true, 1>(mx, mw, a, st);
         return pair_tiles > 74 ? launch_pair<false, 2>(mx, mw, a, st) : launch_pair<false, 1>(mx, mw, a, st);
     }
     if (mt == 2) return gated ? launch_tc<128, true, 2>(mx, mw, a, st) : launch_tc<256, false, 2>(mx, mw, a, st);
