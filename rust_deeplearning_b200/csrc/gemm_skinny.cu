@@ -70,7 +70,7 @@ struct SkinnyArgs {
 // registers of mode 1 and twice as many, smaller blocks).
 // PERSIST: a block goes on to further units (when there are more units than blocks fit the GPU at once).
 template <int NT, int WARPS, int GMODE, int DEPTH, bool PERSIST>
-__global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(SkinnyArgs a) {
+__global__ void __launch_bounds__(WARPS * 32, (NT == 1 && WARPS == 8 && DEPTH == 2 && GMODE != 1) ? 2 : 0) gemm_skinny_kernel(SkinnyArgs a) {
     constexpr bool GATED = GMODE != 0;
     constexpr int NS = GMODE == 1 ? 2 : 1;
     constexpr int OUT_ROWS = GMODE == 2 ? 8 : ROWS;          // outputs per activation row and block
@@ -116,6 +116,15 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(SkinnyArgs a) {
             }
         }
     };
+    auto load_x = [&](int kc, uint4 (&xb)[NT][4]) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int k = kc + u * 32 + t * 8;
+#pragma unroll
+            for (int i = 0; i < NT; ++i)
+                xb[i][u] = (k < K && x_ok[i]) ? __ldg(reinterpret_cast<const uint4*>(xrow[i] + k)) : zero4;
+        }
+    };
     // The weights are constants: the first chunks are requested before waiting for the kernel that
     // produces x, and every later chunk while the chunks before it are being multiplied.
     uint4 wbuf[DEPTH][NS][4][2];
@@ -135,20 +144,25 @@ __global__ void __launch_bounds__(WARPS * 32) gemm_skinny_kernel(SkinnyArgs a) {
 #pragma unroll
             for (int i = 0; i < NT; ++i) acc[s][i][0] = acc[s][i][1] = acc[s][i][2] = acc[s][i][3] = 0.f;
         int kc = warp * KCHUNK;
+        // With eight warps a block (not for 16 activation rows at depth 2: measured slower) the activations of a chunk are requested one
+        // chunk ahead, so that their way through L1 is not waited for; the four-warp form has no registers to
+        // spare for that without giving up a resident block.
+        constexpr bool X_AHEAD = WARPS == 8 && (NT == 1 || DEPTH >= 3);
+        uint4 xbuf[X_AHEAD ? DEPTH : 1][NT][4];
+        if (X_AHEAD) load_x(kc, xbuf[0]);
         while (kc < K) {
 #pragma unroll
             for (int d = 0; d < DEPTH; ++d) {          // buffer indices are compile-time: the ring lives in registers
                 if (kc < K) {
                     const int kn = kc + (DEPTH - 1) * STEP;
                     if (kn < K) load_weights(kn, wbuf[(d + DEPTH - 1) % DEPTH]);
-                    uint4 xb[NT][4];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const int k = kc + u * 32 + t * 8;
-#pragma unroll
-                        for (int i = 0; i < NT; ++i)
-                            xb[i][u] = (k < K && x_ok[i]) ? __ldg(reinterpret_cast<const uint4*>(xrow[i] + k)) : zero4;
+                    uint4 xnow[NT][4];
+                    if (X_AHEAD) {
+                        if (kc + STEP < K) load_x(kc + STEP, xbuf[X_AHEAD ? (d + 1) % DEPTH : 0]);
+                    } else {
+                        load_x(kc, xnow);
                     }
+                    const uint4 (&xb)[NT][4] = X_AHEAD ? xbuf[X_AHEAD ? d : 0] : xnow;
                     const uint4 (&wcur)[NS][4][2] = wbuf[d];
 #pragma unroll
                     for (int u = 0; u < 4; ++u)
