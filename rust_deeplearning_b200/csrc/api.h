@@ -10,7 +10,7 @@ extern "C" {
 #define RDL_ACT_GELU_TANH 0
 #define RDL_ACT_SILU 1
 
-#define RDL_ABI_VERSION 7
+#define RDL_ABI_VERSION 8
 
 const char* rdl_last_error(void);
 int rdl_abi_version(void);
@@ -81,9 +81,10 @@ int rdl_gemm_f32(void* out, const void* x, const void* w, int m, int n, int k, v
 
 // out[m, n] = epilogue(sum_k x[m, k] * w[n, k]) for m <= 16, bfloat16 operands, float accumulation.
 // gated: w is [2 n, k] (gate rows, then up rows) and the result is act(gate) * up.
-// softcap > 0: cap * tanh(v / cap).  out_dtype: RDL_F32 or RDL_BF16.
+// softcap > 0: cap * tanh(v / cap).  out_dtype: RDL_F32 or RDL_BF16.  status (optional) is set non-zero
+// when a block gives up a bounded wait for a copy.
 int rdl_gemm_skinny(void* out, int out_dtype, const void* x, const void* w, int m, int n, int k,
-                    int gated, int activation, float softcap, void* stream);
+                    int gated, int activation, float softcap, int* status, void* stream);
 
 // The same product and epilogues for any number of rows on tcgen05 tensor cores (TMA-fed, accumulators in
 // tensor memory).  n must be a positive number, k a multiple of 8; status (optional) is set non-zero

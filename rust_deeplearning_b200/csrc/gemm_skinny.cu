@@ -222,6 +222,230 @@ __global__ void __launch_bounds__(WARPS * 32, (NT == 1 && WARPS == 8 && DEPTH ==
 
 thread_local cudaError_t g_launch_error = cudaSuccess;
 
+// ---------------------------------------------------------------------------------------------
+// The same product with the weights brought into shared memory by bulk copies (TMA)
+// ---------------------------------------------------------------------------------------------
+//
+// Eight warps multiply and a ninth issues the copies: a tile is the unit's 16 weight rows x 1024 k (each row
+// one cp.async.bulk of 2 KB into a ring of three tiles), every multiplying warp takes 128 k of it.  The
+// copying warp needs nothing an earlier kernel of the step writes, so it never waits for that kernel: with
+// programmatic dependent launch a block's first three tiles (96 KB) are on their way while the kernel before
+// it is still running, and as the block goes from unit to unit the ring never drains.  What is in flight
+// does not live in registers, so a block needs few of them and about 100 KB of shared memory: a block of
+// this kernel and a block of the next one fit a multiprocessor together.
+constexpr int ST_WARPS = 8;                      // multiplying warps
+constexpr int ST_THREADS = (ST_WARPS + 1) * 32;
+constexpr int ST_KT = ST_WARPS * KCHUNK;         // k per tile
+// Rows of a tile lie 2 KB + 64 bytes apart: a quarter warp's eight 16-byte reads (rows g and g + 1, four
+// chunks each) then fall into eight different groups of four banks.
+constexpr int ST_PITCH = ST_KT * 2 + 64;
+constexpr int ST_TILE_BYTES = ROWS * ST_PITCH;
+constexpr int ST_MAX_STAGES = 6;                 // tiles in the ring: 3 (two blocks a multiprocessor) or 6 (one)
+constexpr long long ST_WAIT_CYCLES = 2000000000LL;
+
+__device__ __forceinline__ void st_mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void st_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void st_mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void st_bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ bool st_mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// false if the barrier's phase did not complete within about a second, or if another warp of the block has
+// already given up (the block then runs to its end without waiting; its status word says that the result is void)
+__device__ __forceinline__ bool st_wait(uint32_t bar, uint32_t parity, volatile int* gave_up) {
+    if (st_mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!st_mbar_try_wait(bar, parity)) {
+        if (*gave_up) return false;
+        if (clock64() - t0 > ST_WAIT_CYCLES) { *gave_up = 1; return false; }
+    }
+    return true;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+template <int NT, bool GATED>
+__global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(SkinnyArgs a, int stages, int* status) {
+    extern __shared__ __align__(128) unsigned char st_tiles[];
+    __shared__ __align__(8) unsigned long long full_bar[ST_MAX_STAGES], empty_bar[ST_MAX_STAGES];
+    __shared__ float partial[ST_WARPS][NT][ROWS * 8];
+    __shared__ int gave_up;
+    constexpr int OUT_ROWS = GATED ? 8 : ROWS;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int K = a.K;
+    const int n_units = (a.N + OUT_ROWS - 1) / OUT_ROWS;
+    const int tiles_per_unit = (K + ST_KT - 1) / ST_KT;
+    const uint32_t tiles_s = (uint32_t)__cvta_generic_to_shared(st_tiles);
+    const uint32_t full_s = (uint32_t)__cvta_generic_to_shared(full_bar), empty_s = (uint32_t)__cvta_generic_to_shared(empty_bar);
+    if (threadIdx.x == 0) {
+        gave_up = 0;
+        for (int s = 0; s < stages; ++s) {
+            st_mbar_init(full_s + 8 * s, 1);
+            st_mbar_init(empty_s + 8 * s, ST_WARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    volatile int* gave_up_v = &gave_up;
+
+    if (warp == ST_WARPS) {
+        // ---- the copying warp: lane r brings row r of every tile ----
+        if (lane < ROWS) {
+            int s = 0;                                   // place in the ring, and how often it has been gone round
+            uint32_t round = 0;
+            for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x) {
+                long long row;
+                bool row_ok;
+                if (GATED) {                             // rows 0-7: gate rows of 8 outputs; rows 8-15: their up rows
+                    const int o = unit * 8 + (lane & 7);
+                    row_ok = o < a.N;
+                    row = (long long)(lane < 8 ? 0 : a.N) + o;
+                } else {
+                    row = (long long)unit * ROWS + lane;
+                    row_ok = row < a.N;
+                }
+                const int n_ok = __popc(__ballot_sync(0xffffu, row_ok));
+                for (int tk = 0; tk < tiles_per_unit; ++tk) {
+                    // the tile that lay here must have been read by all eight warps
+                    if (round > 0 && !st_wait(empty_s + 8 * s, (round & 1) ^ 1, gave_up_v)) break;
+                    const int k0 = tk * ST_KT;
+                    const uint32_t bytes = (uint32_t)((K - k0 < ST_KT ? K - k0 : ST_KT) * 2);
+                    if (lane == 0) {
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        st_mbar_expect_tx(full_s + 8 * s, bytes * (uint32_t)n_ok);
+                    }
+                    __syncwarp(0xffffu);
+                    if (row_ok) st_bulk_load(tiles_s + (uint32_t)(s * ST_TILE_BYTES + lane * ST_PITCH), a.w + row * K + k0, bytes, full_s + 8 * s);
+                    if (++s == stages) { s = 0; ++round; }
+                }
+                if (*gave_up_v) break;
+            }
+        }
+    } else {
+        // ---- the multiplying warps ----
+        const int g = lane >> 2, t = lane & 3;
+        const __nv_bfloat16* xrow[NT];
+        bool x_ok[NT];
+#pragma unroll
+        for (int i = 0; i < NT; ++i) {
+            x_ok[i] = i * 8 + g < a.M;
+            xrow[i] = a.x + (long long)(i * 8 + g) * K;
+        }
+        const uint4 zero4 = make_uint4(0, 0, 0, 0);
+        const int kw = warp * KCHUNK;                    // this warp's k inside a tile
+        auto load_x = [&](int kc, uint4 (&xb)[NT][4]) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int k = kc + u * 32 + t * 8;
+#pragma unroll
+                for (int i = 0; i < NT; ++i)
+                    xb[i][u] = (k < K && x_ok[i]) ? __ldg(reinterpret_cast<const uint4*>(xrow[i] + k)) : zero4;
+            }
+        };
+        rdl_grid_wait();
+        rdl_grid_launch_dependents();
+        uint4 xcur[NT][4], xnext[NT][4];
+        load_x(kw, xcur);
+        const uint32_t frag = tiles_s + (uint32_t)(g * ST_PITCH + (kw + t * 8) * 2);
+        int s = 0;
+        uint32_t round = 0;
+        for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x) {
+            float acc[NT][4];
+#pragma unroll
+            for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+            for (int tk = 0; tk < tiles_per_unit; ++tk) {
+                // the activations of the tile after this one (the next unit starts again at k = 0)
+                load_x((tk + 1 < tiles_per_unit ? (tk + 1) * ST_KT : 0) + kw, xnext);
+                st_wait(full_s + 8 * s, round & 1, gave_up_v);
+                const int kb = tk * ST_KT + kw;
+                if (kb < K) {
+                    const uint32_t base = frag + (uint32_t)(s * ST_TILE_BYTES);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const bool in = kb + u * 32 + t * 8 < K;      // what lies beyond K in the tile is stale
+                        const uint4 w0 = in ? lds128(base + u * 64) : zero4;
+                        const uint4 w1 = in ? lds128(base + u * 64 + 8 * ST_PITCH) : zero4;
+#pragma unroll
+                        for (int i = 0; i < NT; ++i) {
+                            mma_bf16(acc[i], w0.x, w1.x, w0.y, w1.y, xcur[i][u].x, xcur[i][u].y);
+                            mma_bf16(acc[i], w0.z, w1.z, w0.w, w1.w, xcur[i][u].z, xcur[i][u].w);
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) st_mbar_arrive(empty_s + 8 * s);
+                if (++s == stages) { s = 0; ++round; }
+#pragma unroll
+                for (int i = 0; i < NT; ++i)
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) xcur[i][u] = xnext[i][u];
+            }
+            // accumulator element e of a lane: weight row g + 8 * (e >> 1), activation row 2 t + (e & 1)
+#pragma unroll
+            for (int i = 0; i < NT; ++i)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) partial[warp][i][(2 * t + (e & 1)) * ROWS + g + 8 * (e >> 1)] = acc[i][e];
+            asm volatile("bar.sync 1, %0;" ::"n"(ST_WARPS * 32) : "memory");
+            const int n0 = unit * OUT_ROWS;
+            for (int idx = threadIdx.x; idx < NT * 8 * OUT_ROWS; idx += ST_WARPS * 32) {
+                const int m = idx / OUT_ROWS, r = idx - m * OUT_ROWS;
+                const int n = n0 + r;
+                if (m >= a.M || n >= a.N) continue;
+                const int i = m >> 3, slot = (m & 7) * ROWS + r;
+                float v0 = 0.f, v1 = 0.f;
+#pragma unroll
+                for (int w = 0; w < ST_WARPS; ++w) {
+                    v0 += partial[w][i][slot];
+                    if (GATED) v1 += partial[w][i][slot + 8];
+                }
+                float y = v0;
+                if (GATED) y = (a.activation == RDL_ACT_GELU_TANH ? gelu_tanh(v0) : silu(v0)) * v1;
+                if (a.softcap > 0.f) y = a.softcap * tanhf(y / a.softcap);
+                rdl_store(a.out, (long long)m * a.N + n, a.out_dtype, y);
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(ST_WARPS * 32) : "memory");      // the partial sums are free again
+        }
+    }
+    if (*gave_up_v && status && lane == 0) atomicExch(status, 5);
+}
+
+template <int NT, bool GATED>
+void launch_stream(const SkinnyArgs& a, int* status, cudaStream_t st) {
+    constexpr int smem_max = ST_MAX_STAGES * ST_TILE_BYTES;
+    static bool opted = false;
+    static int sms = 0;
+    if (!opted) {
+        g_launch_error = cudaFuncSetAttribute(gemm_stream_kernel<NT, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
+        if (g_launch_error != cudaSuccess) return;
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 148;
+        opted = true;
+    }
+    // What counts is the bytes a multiprocessor has in flight: two blocks with three tiles each, or, where
+    // the output is so narrow that there is at most one block a multiprocessor, one block with six.
+    const int units = (a.N + (GATED ? 8 : ROWS) - 1) / (GATED ? 8 : ROWS);
+    const int stages = units <= sms ? ST_MAX_STAGES : ST_MAX_STAGES / 2;
+    const int fit = units <= sms ? sms : 2 * sms;
+    g_launch_error = rdl_launch(gemm_stream_kernel<NT, GATED>, dim3(units < fit ? units : fit), dim3(ST_THREADS), (size_t)stages * ST_TILE_BYTES, st, a, stages, status);
+}
+
+
+
 // blocks that fit the GPU at once for a kernel (asked of the runtime once per kernel)
 template <typename Kernel>
 int resident_blocks(Kernel kernel, int threads) {
@@ -253,7 +477,7 @@ void launch(const SkinnyArgs& a, cudaStream_t st) {
 }  // namespace
 
 extern "C" int rdl_gemm_skinny(void* out, int out_dtype, const void* x, const void* w, int m, int n, int k,
-                               int gated, int activation, float softcap, void* stream) {
+                               int gated, int activation, float softcap, int* status, void* stream) {
     RDL_REQUIRE(out && x && w, "gemm_skinny: missing operand");
     RDL_REQUIRE(rdl_valid_dtype(out_dtype), "gemm_skinny: bad output dtype %d", out_dtype);
     RDL_REQUIRE(m >= 0 && m <= 16, "gemm_skinny: %d rows, at most 16 are supported", m);
@@ -265,6 +489,16 @@ extern "C" int rdl_gemm_skinny(void* out, int out_dtype, const void* x, const vo
     static const int gmode_env = getenv("RDL_SKINNY_GATED") ? atoi(getenv("RDL_SKINNY_GATED")) : 2;
     SkinnyArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, out, m, n, k, out_dtype, gated ? gmode_env : 0, activation, softcap};
     cudaStream_t st = (cudaStream_t)stream;
+    static const int stream_mode = getenv("RDL_SKINNY_STREAM") ? atoi(getenv("RDL_SKINNY_STREAM")) : 1;
+    // up to 8 rows: the kernel that brings the weights into shared memory by bulk copies; 9 to 16 rows were
+    // measured faster with the weights in registers (RDL_SKINNY_STREAM=0 / 2: never / always the former)
+    if (stream_mode == 2 || (stream_mode == 1 && m <= 8)) {
+        g_launch_error = cudaSuccess;
+        if (m <= 8) { if (gated) launch_stream<1, true>(a, status, st); else launch_stream<1, false>(a, status, st); }
+        else { if (gated) launch_stream<2, true>(a, status, st); else launch_stream<2, false>(a, status, st); }
+        RDL_CHECK_EX(g_launch_error, "gemm_skinny");
+        return 0;
+    }
     // few blocks (a narrow output): more warps per block keep enough loads in flight
     const int blocks = (n + ROWS - 1) / ROWS;
     const bool wide = blocks >= 2 * 148 || k < 8 * KCHUNK;

@@ -184,7 +184,7 @@ def _gemm_bf16(x, weight, n_out, out_dtype, gated, activation, softcap, status):
     lib = library.load()
     if x.shape[0] <= SKINNY_MAX_ROWS:
         library.check(lib.rdl_gemm_skinny(_ptr(out), _dtype_code(out), _ptr(x), _ptr(weight), x.shape[0], n_out, x.shape[1],
-                                          int(gated), activation, float(softcap or 0.0), _stream(x)))
+                                          int(gated), activation, float(softcap or 0.0), _ptr(status), _stream(x)))
     else:
         library.check(lib.rdl_gemm_tc(_ptr(out), _dtype_code(out), _ptr(x), _ptr(weight), x.shape[0], n_out, x.shape[1],
                                       int(gated), activation, float(softcap or 0.0), _ptr(status), _stream(x)))
