@@ -235,12 +235,15 @@ thread_local cudaError_t g_launch_error = cudaSuccess;
 // this kernel and a block of the next one fit a multiprocessor together.
 constexpr int ST_WARPS = 8;                      // multiplying warps
 constexpr int ST_THREADS = (ST_WARPS + 1) * 32;
-constexpr int ST_KT = ST_WARPS * KCHUNK;         // k per tile
-// Rows of a tile lie 2 KB + 64 bytes apart: a quarter warp's eight 16-byte reads (rows g and g + 1, four
-// chunks each) then fall into eight different groups of four banks.
-constexpr int ST_PITCH = ST_KT * 2 + 64;
-constexpr int ST_TILE_BYTES = ROWS * ST_PITCH;
-constexpr int ST_MAX_STAGES = 6;                 // tiles in the ring: 3 (two blocks a multiprocessor) or 6 (one)
+// KU: steps of 32 k a multiplying warp takes of a tile (4: tiles of 1024 k, 3: of 768 k; the host takes
+// the one that leaves less of the last tile of a row empty).
+// Rows of a tile lie their length + 64 bytes apart: a quarter warp's eight 16-byte reads (rows g and g + 1,
+// four chunks each) then fall into eight different groups of four banks.
+__host__ __device__ constexpr int st_kt(int ku) { return ST_WARPS * 32 * ku; }
+__host__ __device__ constexpr int st_pitch(int ku) { return st_kt(ku) * 2 + 64; }
+__host__ __device__ constexpr int st_tile_bytes(int ku) { return ROWS * st_pitch(ku); }
+__host__ __device__ constexpr int st_stages(int ku) { return ku == 4 ? 3 : 4; }      // about 100 KB a block; twice that where one block has a multiprocessor to itself
+constexpr int ST_MAX_STAGES = 8;
 constexpr long long ST_WAIT_CYCLES = 2000000000LL;
 
 __device__ __forceinline__ void st_mbar_init(uint32_t bar, int count) {
@@ -279,8 +282,9 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     return v;
 }
 
-template <int NT, bool GATED>
+template <int NT, bool GATED, int KU>
 __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(SkinnyArgs a, int stages, int* status) {
+    constexpr int ST_KT = st_kt(KU), ST_PITCH = st_pitch(KU), ST_TILE_BYTES = st_tile_bytes(KU), KW = 32 * KU;
     extern __shared__ __align__(128) unsigned char st_tiles[];
     __shared__ __align__(8) unsigned long long full_bar[ST_MAX_STAGES], empty_bar[ST_MAX_STAGES];
     __shared__ float partial[ST_WARPS][NT][ROWS * 8];
@@ -347,10 +351,10 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(SkinnyArgs a
             xrow[i] = a.x + (long long)(i * 8 + g) * K;
         }
         const uint4 zero4 = make_uint4(0, 0, 0, 0);
-        const int kw = warp * KCHUNK;                    // this warp's k inside a tile
-        auto load_x = [&](int kc, uint4 (&xb)[NT][4]) {
+        const int kw = warp * KW;                        // this warp's k inside a tile
+        auto load_x = [&](int kc, uint4 (&xb)[NT][KU]) {
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < KU; ++u) {
                 const int k = kc + u * 32 + t * 8;
 #pragma unroll
                 for (int i = 0; i < NT; ++i)
@@ -359,7 +363,7 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(SkinnyArgs a
         };
         rdl_grid_wait();
         rdl_grid_launch_dependents();
-        uint4 xcur[NT][4], xnext[NT][4];
+        uint4 xcur[NT][KU], xnext[NT][KU];
         load_x(kw, xcur);
         const uint32_t frag = tiles_s + (uint32_t)(g * ST_PITCH + (kw + t * 8) * 2);
         int s = 0;
@@ -376,7 +380,7 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(SkinnyArgs a
                 if (kb < K) {
                     const uint32_t base = frag + (uint32_t)(s * ST_TILE_BYTES);
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
+                    for (int u = 0; u < KU; ++u) {
                         const bool in = kb + u * 32 + t * 8 < K;      // what lies beyond K in the tile is stale
                         const uint4 w0 = in ? lds128(base + u * 64) : zero4;
                         const uint4 w1 = in ? lds128(base + u * 64 + 8 * ST_PITCH) : zero4;
@@ -393,7 +397,7 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(SkinnyArgs a
 #pragma unroll
                 for (int i = 0; i < NT; ++i)
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) xcur[i][u] = xnext[i][u];
+                    for (int u = 0; u < KU; ++u) xcur[i][u] = xnext[i][u];
             }
             // accumulator element e of a lane: weight row g + 8 * (e >> 1), activation row 2 t + (e & 1)
 #pragma unroll
@@ -424,24 +428,36 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(SkinnyArgs a
     if (*gave_up_v && status && lane == 0) atomicExch(status, 5);
 }
 
-template <int NT, bool GATED>
-void launch_stream(const SkinnyArgs& a, int* status, cudaStream_t st) {
-    constexpr int smem_max = ST_MAX_STAGES * ST_TILE_BYTES;
+template <int NT, bool GATED, int KU>
+void launch_stream_ku(const SkinnyArgs& a, int* status, cudaStream_t st) {
+    constexpr int smem_max = 2 * st_stages(KU) * st_tile_bytes(KU);
+    static_assert(2 * st_stages(KU) <= ST_MAX_STAGES, "the ring's barriers");
     static bool opted = false;
     static int sms = 0;
     if (!opted) {
-        g_launch_error = cudaFuncSetAttribute(gemm_stream_kernel<NT, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
+        g_launch_error = cudaFuncSetAttribute(gemm_stream_kernel<NT, GATED, KU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
         if (g_launch_error != cudaSuccess) return;
         int dev = 0;
         if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 148;
         opted = true;
     }
     // What counts is the bytes a multiprocessor has in flight: two blocks with three tiles each, or, where
-    // the output is so narrow that there is at most one block a multiprocessor, one block with six.
+    // the output is so narrow that there is at most one block a multiprocessor, one block with twice as many.
     const int units = (a.N + (GATED ? 8 : ROWS) - 1) / (GATED ? 8 : ROWS);
-    const int stages = units <= sms ? ST_MAX_STAGES : ST_MAX_STAGES / 2;
+    const int stages = units <= sms ? 2 * st_stages(KU) : st_stages(KU);
     const int fit = units <= sms ? sms : 2 * sms;
-    g_launch_error = rdl_launch(gemm_stream_kernel<NT, GATED>, dim3(units < fit ? units : fit), dim3(ST_THREADS), (size_t)stages * ST_TILE_BYTES, st, a, stages, status);
+    g_launch_error = rdl_launch(gemm_stream_kernel<NT, GATED, KU>, dim3(units < fit ? units : fit), dim3(ST_THREADS), (size_t)stages * st_tile_bytes(KU), st, a, stages, status);
+}
+
+template <int NT, bool GATED>
+void launch_stream(const SkinnyArgs& a, int* status, cudaStream_t st) {
+    static const int ku_env = getenv("RDL_STREAM_KU") ? atoi(getenv("RDL_STREAM_KU")) : 0;
+    const int waste4 = (a.K + st_kt(4) - 1) / st_kt(4) * st_kt(4) - a.K, waste3 = (a.K + st_kt(3) - 1) / st_kt(3) * st_kt(3) - a.K;
+    // Tiles of 768 k where they divide the row better, unless the output is very wide: there the kernel runs in
+    // its steady state, where the larger copies of 1024 k were measured faster (the output head: 162 against 174 us).
+    const int units = (a.N + (GATED ? 8 : ROWS) - 1) / (GATED ? 8 : ROWS);
+    if (ku_env == 3 || (ku_env != 4 && waste3 < waste4 && units <= 4096)) launch_stream_ku<NT, GATED, 3>(a, status, st);
+    else launch_stream_ku<NT, GATED, 4>(a, status, st);
 }
 
 
