@@ -1,17 +1,18 @@
-// Matrix product for few rows (decode): out[m, n] = sum_k x[m, k] * w[n, k] with m <= 16.
-// The weight matrix is streamed from HBM exactly once with 16-byte loads straight into
-// tensor-core fragments; the few activation rows come through L1/L2.  bfloat16 operands, float
-// accumulation (mma.sync m16n8k16: 16 weight rows x 8 activation rows per instruction).
+// Matrix products for few rows (decode): out[m, n] = sum_k x[m, k] * w[n, k] with m <= 16.
+// The weight matrix is streamed from HBM exactly once; the few activation rows come through L1/L2.
+// bfloat16 operands, float accumulation (mma.sync m16n8k16: 16 weight rows x 8 activation rows per
+// instruction).  A unit of work is 16 weight rows (for the gated form: 8 gate rows and the 8 up rows
+// of the same outputs, which are the two halves of one 16-row fragment); the warps of a block split K
+// between them and their partial sums are added in warp order through shared memory.
 //
-// A unit of work is 16 weight rows (for the gated form: 8 gate rows and the 8 up rows of the same
-// outputs, which are the two halves of one 16-row fragment).  The warps of a block split K between
-// them in interleaved chunks of 128 and their partial sums are added in warp order through shared
-// memory.  A warp keeps a ring of chunks in registers (one being multiplied, the others on their way
-// from HBM; deeper where the output is so narrow that one block runs per multiprocessor).  When
-// there are more units than blocks fit the GPU at once, the grid is that many blocks and each goes
-// on to further units, requesting the next unit's first weights before it adds up the current one.
-// Under programmatic dependent launch the first weights are requested before the wait for the
-// kernel that produces the activations.
+// Two kernels.  gemm_stream_kernel (up to 8 rows; further down) brings the weights into a ring of
+// shared-memory tiles by bulk copies that a warp of their own issues.  gemm_skinny_kernel (9 to 16
+// rows) loads them with 16-byte loads straight into fragments: a warp keeps a ring of chunks in
+// registers (one being multiplied, the others on their way from HBM; deeper where the output is so
+// narrow that one block runs per multiprocessor), in interleaved chunks of 128 k.  When there are
+// more units than blocks fit the GPU at once, the grid is that many blocks and each goes on to
+// further units.  Under programmatic dependent launch both request their first weights before the
+// wait for the kernel that produces the activations.
 //
 // Epilogues: plain store (bfloat16 or float), cap * tanh(v / cap) (the output head), and
 // act(gate) * up for a row-concatenated [gate; up] matrix (the feed-forward), all in float.

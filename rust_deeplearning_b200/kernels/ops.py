@@ -196,10 +196,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     """x [rows, in] times weight [out, in] transposed; optionally cap * tanh(. / cap) on the result.
 
     float32: the library's own FMA kernel (no tensor cores, no reduced-precision mode).
-    bfloat16: up to 16 rows (decode) the weight-streaming tensor-core kernel, above that the TMA +
-    tcgen05 kernel, both with float accumulation and the soft-cap in their epilogue.  Operands that do
-    not meet their alignment rules go to a library product (cuBLAS through torch), which is what the
-    reference's engine uses for all its products."""
+    bfloat16: up to 16 rows (decode) the weight-streaming tensor-core kernels, from 128 rows the TMA +
+    tcgen05 kernels, all with float accumulation and the soft-cap in their epilogue.  17 to 127 rows, and
+    operands that do not meet the alignment rules, go to a library product (cuBLAS through torch), which
+    is what the reference's engine uses for all its products."""
     _need(x.dim() == 2 and weight.dim() == 2 and x.shape[1] == weight.shape[1],
           f"linear: shapes {tuple(x.shape)} and {tuple(weight.shape)} do not fit")
     _need(x.dtype is weight.dtype, f"linear: input is {x.dtype}, weight is {weight.dtype}")
