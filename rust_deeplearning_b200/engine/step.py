@@ -18,7 +18,7 @@ from typing import Tuple, Dict, List, Optional, Sequence, Union
 import numpy as np
 import torch
 
-from ..cache.cache import Cache, CacheError
+from ..cache.cache import Cache
 from ..kernels import library
 from .batch import BatchLayout, StepBatch, batch_from_buffer, count_tiles, fill_batch
 

@@ -21,7 +21,6 @@ import json
 import os
 import sys
 
-import numpy as np
 
 
 def run(argv=None, stdin=None, stdout=None) -> int:

@@ -23,7 +23,7 @@ from ..cache.cache import RunNeeds
 from ..kernels import ops
 from .norm import ResidualStream
 from .registry import BuildContext, build_part, register_part
-from .spec import LayerSpec, ModelSpec, PartSpec
+from .spec import LayerSpec, ModelSpec
 
 
 class ScaledEmbedding:

@@ -14,7 +14,6 @@ Interface of a norm: `apply(x [rows, hidden], out_dtype) -> [rows, hidden]`.
 """
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 

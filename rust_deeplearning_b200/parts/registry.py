@@ -8,7 +8,7 @@ library: a test, or a user, can add a mixer of their own and name it in a ModelS
 """
 from __future__ import annotations
 
-from typing import Any, Callable, Dict, Optional
+from typing import Any, Callable, Dict
 
 import torch
 

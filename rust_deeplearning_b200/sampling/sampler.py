@@ -11,7 +11,7 @@ unseeded thread-local generator (`generator.rs:199`).
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import List, Optional, Sequence
+from typing import Optional, Sequence
 
 import numpy as np
 import torch

@@ -3,7 +3,6 @@ and whole, the last 32 tokens one by one, batches of unequal lengths with slot r
 first tokens, greedy generation through the entry point."""
 import numpy as np
 import pytest
-import torch
 
 import model_helpers as mh
 import plain_gemma2 as plain

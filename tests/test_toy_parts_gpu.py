@@ -3,7 +3,6 @@ to the package: a mixer with per-sequence state of fixed size, a feed-forward wi
 position encoding, a norm of another kind; and a schedule that names a layer twice and lets a run
 read another run's keys and values.  The toy model is compared with a plain whole-sequence
 restatement written below; it is nobody's architecture."""
-import math
 
 import numpy as np
 import pytest
