@@ -125,6 +125,23 @@ def test_skinny_gemm(m, n, k):
                  torch.bfloat16, what="gated, library product")
 
 
+@pytest.mark.parametrize("m,n,k", [(8, 2304, 9216), (5, 100, 7000), (1, 16, 6152), (7, 2368, 3080)])
+def test_skinny_gemm_long_rows(m, n, k):
+    """Rows of many tiles: a narrow output has one block a multiprocessor with the longer ring, which goes
+    round more than once within a unit (9216 = 9 tiles of 1024 through 6 places); 7000 and 6152 end in a
+    short tile; 2368 outputs are 148 units, the most that still get the longer ring."""
+    x, w = rnd((m, k), torch.bfloat16, 43), rnd((n, k), torch.bfloat16, 44, 0.2)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    assert ops._skinny_ok(x, w)
+    assert_close(ops.linear(x, w, status=status), ref.linear(x, w), torch.bfloat16, what="plain")
+    assert_close(ops.linear(x, w, out_dtype=torch.float32, status=status), ref.linear(x, w, torch.float32), torch.float32,
+                 what="float32 out", f32_tol=k * 2.0 ** -24)
+    if n % 2 == 0:
+        assert_close(ops.linear_gated(x, w, "gelu_pytorch_tanh", status=status), ref.linear_gated(x, w, "gelu_pytorch_tanh"),
+                     torch.bfloat16, what="gated")
+    assert status.item() == 0
+
+
 @pytest.mark.parametrize("m", [2, 8, 13])
 def test_skinny_gemm_with_more_units_than_blocks_fit(m):
     """A wide output has more 16-row units than blocks fit the GPU at once: blocks then go on to further
