@@ -1,18 +1,19 @@
-// Matrix products for few rows (decode): out[m, n] = sum_k x[m, k] * w[n, k] with m <= 16.
+// Matrix product for few rows (decode): out[m, n] = sum_k x[m, k] * w[n, k] with m <= 16.
 // The weight matrix is streamed from HBM exactly once; the few activation rows come through L1/L2.
 // bfloat16 operands, float accumulation (mma.sync m16n8k16: 16 weight rows x 8 activation rows per
 // instruction).  A unit of work is 16 weight rows (for the gated form: 8 gate rows and the 8 up rows
-// of the same outputs, which are the two halves of one 16-row fragment); the warps of a block split K
-// between them and their partial sums are added in warp order through shared memory.
+// of the same outputs, which are the two halves of one 16-row fragment).
 //
-// Two kernels.  gemm_stream_kernel (up to 8 rows; further down) brings the weights into a ring of
-// shared-memory tiles by bulk copies that a warp of their own issues.  gemm_skinny_kernel (9 to 16
-// rows) loads them with 16-byte loads straight into fragments: a warp keeps a ring of chunks in
-// registers (one being multiplied, the others on their way from HBM; deeper where the output is so
-// narrow that one block runs per multiprocessor), in interleaved chunks of 128 k.  When there are
-// more units than blocks fit the GPU at once, the grid is that many blocks and each goes on to
-// further units.  Under programmatic dependent launch both request their first weights before the
-// wait for the kernel that produces the activations.
+// Eight warps multiply and a ninth issues the copies: a tile is the unit's 16 weight rows x 768 or 1024 k
+// (each row one cp.async.bulk of 1.5 or 2 KB) in a ring of shared-memory tiles, and every multiplying warp
+// takes an eighth of its k; the warps' partial sums are added in warp order through shared memory.  The
+// copying warp needs nothing an earlier kernel of the step writes, so it never waits for that kernel:
+// with programmatic dependent launch a block's ring (about 100 KB) is on its way while the kernel before
+// it is still running.  Blocks are persistent (at most two a multiprocessor) and the ring runs on from
+// unit to unit, so it never drains.  What is in flight does not live in registers: a multiprocessor has
+// about 200 KB on their way, which is what it takes to keep HBM busy when a copy needs about 3 us to
+// arrive (with the weights in a ring of registers, 64 KB a multiprocessor, the same products were 15-30 %
+// slower).  Every wait is bounded; a block that gives up sets `status`.
 //
 // Epilogues: plain store (bfloat16 or float), cap * tanh(v / cap) (the output head), and
 // act(gate) * up for a row-concatenated [gate; up] matrix (the feed-forward), all in float.
@@ -29,22 +30,13 @@
 
 namespace {
 
-constexpr int ROWS = 16;        // weight rows per block
-constexpr int KCHUNK = 128;     // k per warp iteration: 4 steps of 32
+constexpr int ROWS = 16;        // weight rows per unit
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// streaming load: weights are read once, keep them out of L1
-__device__ __forceinline__ uint4 ld_stream(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
 }
 
 __device__ __forceinline__ float gelu_tanh(float x) {
@@ -58,182 +50,12 @@ struct SkinnyArgs {
     void* out;                  // [M, N]
     int M, N, K;
     int out_dtype;              // RDL_F32 / RDL_BF16
-    int gated;                  // 0: plain, 1: act(gate) * up
-    int activation;
+    int activation;             // of the gated form
     float softcap;              // > 0: cap * tanh(v / cap)
 };
 
-// NT: activation row tiles of 8 (M <= 8 * NT).  WARPS: warps that split K.
-// DEPTH: chunks of weights a warp has in registers, one being multiplied and DEPTH - 1 on their way; a
-// narrow output has one block per multiprocessor and needs the deeper queue to keep HBM busy.
-// GMODE: 0 plain; 1 gated, 16 outputs a block from two streams of 16 weight rows; 2 gated, 8 outputs a
-// block from one stream whose 16 rows are 8 gate rows and the 8 up rows of the same outputs (half the
-// registers of mode 1 and twice as many, smaller blocks).
-// PERSIST: a block goes on to further units (when there are more units than blocks fit the GPU at once).
-template <int NT, int WARPS, int GMODE, int DEPTH, bool PERSIST>
-__global__ void __launch_bounds__(WARPS * 32, (NT == 1 && WARPS == 8 && DEPTH == 2 && GMODE != 1) ? 2 : 0) gemm_skinny_kernel(SkinnyArgs a) {
-    constexpr bool GATED = GMODE != 0;
-    constexpr int NS = GMODE == 1 ? 2 : 1;
-    constexpr int OUT_ROWS = GMODE == 2 ? 8 : ROWS;          // outputs per activation row and block
-    __shared__ float partial[WARPS][NS][NT][ROWS * 8];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int g = lane >> 2, t = lane & 3;
-    const int K = a.K;
-    const int n_units = (a.N + OUT_ROWS - 1) / OUT_ROWS;       // a unit: OUT_ROWS outputs for every activation row
-    // A block takes units blockIdx.x, blockIdx.x + gridDim.x, ...: the first weights of its next unit are
-    // requested before the sums of the current one are added up and stored.
-    int n0 = blockIdx.x * OUT_ROWS;
-    bool row0_ok, row1_ok;
-    const __nv_bfloat16* wrow[NS][2];
-    auto set_unit = [&](int first_row) {
-        row0_ok = first_row + g < a.N;
-        row1_ok = GMODE == 2 ? row0_ok : first_row + g + 8 < a.N;
-#pragma unroll
-        for (int s = 0; s < NS; ++s) {
-            const long long base = (long long)(s * a.N + first_row + g) * K;
-            wrow[s][0] = a.w + base;
-            wrow[s][1] = a.w + base + (GMODE == 2 ? (long long)a.N : 8LL) * K;
-        }
-    };
-    set_unit(n0);
-    const __nv_bfloat16* xrow[NT];
-    bool x_ok[NT];
-#pragma unroll
-    for (int i = 0; i < NT; ++i) {
-        x_ok[i] = i * 8 + g < a.M;
-        xrow[i] = a.x + (long long)(i * 8 + g) * K;
-    }
-    const uint4 zero4 = make_uint4(0, 0, 0, 0);
-    // one chunk of this warp's weights: 4 steps of 32 k, two rows per lane and stream
-    auto load_weights = [&](int kc, uint4 (&wa)[NS][4][2]) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int k = kc + u * 32 + t * 8;
-            const bool k_ok = k < K;      // K is a multiple of 8: a 16-byte load is whole or absent
-#pragma unroll
-            for (int s = 0; s < NS; ++s) {
-                wa[s][u][0] = (k_ok && row0_ok) ? ld_stream(wrow[s][0] + k) : zero4;
-                wa[s][u][1] = (k_ok && row1_ok) ? ld_stream(wrow[s][1] + k) : zero4;
-            }
-        }
-    };
-    auto load_x = [&](int kc, uint4 (&xb)[NT][4]) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int k = kc + u * 32 + t * 8;
-#pragma unroll
-            for (int i = 0; i < NT; ++i)
-                xb[i][u] = (k < K && x_ok[i]) ? __ldg(reinterpret_cast<const uint4*>(xrow[i] + k)) : zero4;
-        }
-    };
-    // The weights are constants: the first chunks are requested before waiting for the kernel that
-    // produces x, and every later chunk while the chunks before it are being multiplied.
-    uint4 wbuf[DEPTH][NS][4][2];
-    constexpr int STEP = WARPS * KCHUNK;
-    auto request_first_chunks = [&]() {
-#pragma unroll
-        for (int d = 0; d < DEPTH - 1; ++d)
-            if (warp * KCHUNK + d * STEP < K) load_weights(warp * KCHUNK + d * STEP, wbuf[d]);
-    };
-    request_first_chunks();
-    rdl_grid_wait();
-    rdl_grid_launch_dependents();
-    for (int unit = blockIdx.x;;) {
-        float acc[NS][NT][4];
-#pragma unroll
-        for (int s = 0; s < NS; ++s)
-#pragma unroll
-            for (int i = 0; i < NT; ++i) acc[s][i][0] = acc[s][i][1] = acc[s][i][2] = acc[s][i][3] = 0.f;
-        int kc = warp * KCHUNK;
-        // With eight warps a block (not for 16 activation rows at depth 2: measured slower) the activations of a chunk are requested one
-        // chunk ahead, so that their way through L1 is not waited for; the four-warp form has no registers to
-        // spare for that without giving up a resident block.
-        constexpr bool X_AHEAD = WARPS == 8 && (NT == 1 || DEPTH >= 3);
-        uint4 xbuf[X_AHEAD ? DEPTH : 1][NT][4];
-        if (X_AHEAD) load_x(kc, xbuf[0]);
-        while (kc < K) {
-#pragma unroll
-            for (int d = 0; d < DEPTH; ++d) {          // buffer indices are compile-time: the ring lives in registers
-                if (kc < K) {
-                    const int kn = kc + (DEPTH - 1) * STEP;
-                    if (kn < K) load_weights(kn, wbuf[(d + DEPTH - 1) % DEPTH]);
-                    uint4 xnow[NT][4];
-                    if (X_AHEAD) {
-                        if (kc + STEP < K) load_x(kc + STEP, xbuf[X_AHEAD ? (d + 1) % DEPTH : 0]);
-                    } else {
-                        load_x(kc, xnow);
-                    }
-                    const uint4 (&xb)[NT][4] = X_AHEAD ? xbuf[X_AHEAD ? d : 0] : xnow;
-                    const uint4 (&wcur)[NS][4][2] = wbuf[d];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u)
-#pragma unroll
-                        for (int s = 0; s < NS; ++s)
-#pragma unroll
-                            for (int i = 0; i < NT; ++i) {
-                                mma_bf16(acc[s][i], wcur[s][u][0].x, wcur[s][u][1].x, wcur[s][u][0].y, wcur[s][u][1].y, xb[i][u].x, xb[i][u].y);
-                                mma_bf16(acc[s][i], wcur[s][u][0].z, wcur[s][u][1].z, wcur[s][u][0].w, wcur[s][u][1].w, xb[i][u].z, xb[i][u].w);
-                            }
-                    kc += STEP;
-                }
-            }
-        }
-        // accumulator element e of a lane: weight row g + 8 * (e >> 1), activation row 2 t + (e & 1)
-#pragma unroll
-        for (int s = 0; s < NS; ++s)
-#pragma unroll
-            for (int i = 0; i < NT; ++i)
-#pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    partial[warp][s][i][(2 * t + (e & 1)) * ROWS + g + 8 * (e >> 1)] = acc[s][i][e];
-        const int next = unit + (int)gridDim.x;
-        const bool more = PERSIST && next < n_units;
-        if (more) {                       // the ring is empty now: the next unit's first weights set out
-            set_unit(next * OUT_ROWS);
-            request_first_chunks();
-        }
-        __syncthreads();
-        // thread -> (activation row, weight row): consecutive threads write consecutive outputs
-        for (int idx = threadIdx.x; idx < NT * 8 * OUT_ROWS; idx += WARPS * 32) {
-            const int m = idx / OUT_ROWS, r = idx - m * OUT_ROWS;
-            const int n = n0 + r;
-            if (m >= a.M || n >= a.N) continue;
-            const int i = m >> 3, slot = (m & 7) * ROWS + r;
-            float v[2];
-#pragma unroll
-            for (int s = 0; s < 2; ++s) {
-                float sum = 0.f;
-                if (s == 0 || GATED) {
-#pragma unroll
-                    for (int w = 0; w < WARPS; ++w) sum += GMODE == 2 ? partial[w][0][i][slot + 8 * s] : partial[w][s < NS ? s : 0][i][slot];
-                }
-                v[s] = sum;
-            }
-            float y = v[0];
-            if (GATED) y = (a.activation == RDL_ACT_GELU_TANH ? gelu_tanh(v[0]) : silu(v[0])) * v[1];
-            if (a.softcap > 0.f) y = a.softcap * tanhf(y / a.softcap);
-            rdl_store(a.out, (long long)m * a.N + n, a.out_dtype, y);
-        }
-        if (!more) break;
-        __syncthreads();                  // the partial sums are free again
-        unit = next;
-        n0 = unit * OUT_ROWS;
-    }
-}
-
 thread_local cudaError_t g_launch_error = cudaSuccess;
 
-// ---------------------------------------------------------------------------------------------
-// The same product with the weights brought into shared memory by bulk copies (TMA)
-// ---------------------------------------------------------------------------------------------
-//
-// Eight warps multiply and a ninth issues the copies: a tile is the unit's 16 weight rows x 1024 k (each row
-// one cp.async.bulk of 2 KB into a ring of three tiles), every multiplying warp takes 128 k of it.  The
-// copying warp needs nothing an earlier kernel of the step writes, so it never waits for that kernel: with
-// programmatic dependent launch a block's first three tiles (96 KB) are on their way while the kernel before
-// it is still running, and as the block goes from unit to unit the ring never drains.  What is in flight
-// does not live in registers, so a block needs few of them and about 100 KB of shared memory: a block of
-// this kernel and a block of the next one fit a multiprocessor together.
 constexpr int ST_WARPS = 8;                      // multiplying warps
 constexpr int ST_THREADS = (ST_WARPS + 1) * 32;
 // KU: steps of 32 k a multiplying warp takes of a tile (4: tiles of 1024 k, 3: of 768 k; the host takes
@@ -364,8 +186,11 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(SkinnyArgs a
         };
         rdl_grid_wait();
         rdl_grid_launch_dependents();
-        uint4 xcur[NT][KU], xnext[NT][KU];
-        load_x(kw, xcur);
+        // up to 8 rows: the activations of a tile are requested one tile ahead; with 16 rows the registers for
+        // that would cost the second block of a multiprocessor
+        constexpr bool X_AHEAD = NT == 1;
+        uint4 xcur[NT][KU], xnext[X_AHEAD ? NT : 1][KU];
+        if (X_AHEAD) load_x(kw, xcur);
         const uint32_t frag = tiles_s + (uint32_t)(g * ST_PITCH + (kw + t * 8) * 2);
         int s = 0;
         uint32_t round = 0;
@@ -375,7 +200,8 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(SkinnyArgs a
             for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
             for (int tk = 0; tk < tiles_per_unit; ++tk) {
                 // the activations of the tile after this one (the next unit starts again at k = 0)
-                load_x((tk + 1 < tiles_per_unit ? (tk + 1) * ST_KT : 0) + kw, xnext);
+                if (X_AHEAD) load_x((tk + 1 < tiles_per_unit ? (tk + 1) * ST_KT : 0) + kw, reinterpret_cast<uint4 (&)[NT][KU]>(xnext));
+                else load_x(tk * ST_KT + kw, xcur);
                 st_wait(full_s + 8 * s, round & 1, gave_up_v);
                 const int kb = tk * ST_KT + kw;
                 if (kb < K) {
@@ -395,10 +221,12 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(SkinnyArgs a
                 __syncwarp();
                 if (lane == 0) st_mbar_arrive(empty_s + 8 * s);
                 if (++s == stages) { s = 0; ++round; }
+                if (X_AHEAD) {
 #pragma unroll
-                for (int i = 0; i < NT; ++i)
+                    for (int i = 0; i < NT; ++i)
 #pragma unroll
-                    for (int u = 0; u < KU; ++u) xcur[i][u] = xnext[i][u];
+                        for (int u = 0; u < KU; ++u) xcur[i][u] = xnext[X_AHEAD ? i : 0][u];
+                }
             }
             // accumulator element e of a lane: weight row g + 8 * (e >> 1), activation row 2 t + (e & 1)
 #pragma unroll
@@ -452,43 +280,12 @@ void launch_stream_ku(const SkinnyArgs& a, int* status, cudaStream_t st) {
 
 template <int NT, bool GATED>
 void launch_stream(const SkinnyArgs& a, int* status, cudaStream_t st) {
-    static const int ku_env = getenv("RDL_STREAM_KU") ? atoi(getenv("RDL_STREAM_KU")) : 0;
     const int waste4 = (a.K + st_kt(4) - 1) / st_kt(4) * st_kt(4) - a.K, waste3 = (a.K + st_kt(3) - 1) / st_kt(3) * st_kt(3) - a.K;
     // Tiles of 768 k where they divide the row better, unless the output is very wide: there the kernel runs in
     // its steady state, where the larger copies of 1024 k were measured faster (the output head: 162 against 174 us).
     const int units = (a.N + (GATED ? 8 : ROWS) - 1) / (GATED ? 8 : ROWS);
-    if (ku_env == 3 || (ku_env != 4 && waste3 < waste4 && units <= 4096)) launch_stream_ku<NT, GATED, 3>(a, status, st);
+    if (waste3 < waste4 && units <= 4096) launch_stream_ku<NT, GATED, 3>(a, status, st);
     else launch_stream_ku<NT, GATED, 4>(a, status, st);
-}
-
-
-
-// blocks that fit the GPU at once for a kernel (asked of the runtime once per kernel)
-template <typename Kernel>
-int resident_blocks(Kernel kernel, int threads) {
-    int per_sm = 0, sms = 0, dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) != cudaSuccess || per_sm < 1 || sms < 1)
-        return 1 << 30;                   // unknown: one block per unit
-    return per_sm * sms;
-}
-
-template <int NT, int WARPS, int GMODE, int DEPTH>
-void launch_units(const SkinnyArgs& a, cudaStream_t st) {
-    static const int fit = resident_blocks(gemm_skinny_kernel<NT, WARPS, GMODE, DEPTH, true>, WARPS * 32);
-    static const bool persistent = !(getenv("RDL_SKINNY_PERSISTENT") && atoi(getenv("RDL_SKINNY_PERSISTENT")) == 0);
-    const int units = (a.N + (GMODE == 2 ? 8 : ROWS) - 1) / (GMODE == 2 ? 8 : ROWS);
-    if (persistent && units > fit)
-        g_launch_error = rdl_launch(gemm_skinny_kernel<NT, WARPS, GMODE, DEPTH, true>, dim3(fit), dim3(WARPS * 32), 0, st, a);
-    else
-        g_launch_error = rdl_launch(gemm_skinny_kernel<NT, WARPS, GMODE, DEPTH, false>, dim3(units), dim3(WARPS * 32), 0, st, a);
-}
-
-template <int NT, int WARPS, int DEPTH>
-void launch(const SkinnyArgs& a, cudaStream_t st) {
-    if (a.gated == 2) launch_units<NT, 8, 2, 2>(a, st);
-    else if (a.gated) launch_units<NT, WARPS, 1, 2>(a, st);
-    else launch_units<NT, WARPS, 0, DEPTH>(a, st);
 }
 
 }  // namespace
@@ -503,35 +300,15 @@ extern "C" int rdl_gemm_skinny(void* out, int out_dtype, const void* x, const vo
     RDL_REQUIRE(!gated || activation == RDL_ACT_GELU_TANH || activation == RDL_ACT_SILU, "gemm_skinny: unknown activation %d", activation);
     RDL_REQUIRE(softcap >= 0.f, "gemm_skinny: soft-cap must not be negative");
     if (m == 0) return 0;
-    static const int gmode_env = getenv("RDL_SKINNY_GATED") ? atoi(getenv("RDL_SKINNY_GATED")) : 2;
-    SkinnyArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, out, m, n, k, out_dtype, gated ? gmode_env : 0, activation, softcap};
+    SkinnyArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, out, m, n, k, out_dtype, activation, softcap};
     cudaStream_t st = (cudaStream_t)stream;
-    static const int stream_mode = getenv("RDL_SKINNY_STREAM") ? atoi(getenv("RDL_SKINNY_STREAM")) : 1;
-    // up to 8 rows: the kernel that brings the weights into shared memory by bulk copies; 9 to 16 rows were
-    // measured faster with the weights in registers (RDL_SKINNY_STREAM=0 / 2: never / always the former)
-    if (stream_mode == 2 || (stream_mode == 1 && m <= 8)) {
-        g_launch_error = cudaSuccess;
-        if (m <= 8) { if (gated) launch_stream<1, true>(a, status, st); else launch_stream<1, false>(a, status, st); }
-        else { if (gated) launch_stream<2, true>(a, status, st); else launch_stream<2, false>(a, status, st); }
-        RDL_CHECK_EX(g_launch_error, "gemm_skinny");
-        return 0;
-    }
-    // few blocks (a narrow output): more warps per block keep enough loads in flight
-    const int blocks = (n + ROWS - 1) / ROWS;
-    const bool wide = blocks >= 2 * 148 || k < 8 * KCHUNK;
-    static const int depth_env = getenv("RDL_SKINNY_DEPTH") ? atoi(getenv("RDL_SKINNY_DEPTH")) : 0;
-    // at most one block per multiprocessor: four chunks in registers (measured: the 2304 x 9216 product 13.5 ->
-    // 11.2 us); otherwise two (three was slower than either)
-    const int depth = depth_env ? depth_env : (!wide && blocks <= 148 ? 4 : 2);
+    g_launch_error = cudaSuccess;
     if (m <= 8) {
-        if (wide) launch<1, 4, 2>(a, st);
-        else if (depth >= 4) launch<1, 8, 4>(a, st);
-        else if (depth == 3) launch<1, 8, 3>(a, st);
-        else launch<1, 8, 2>(a, st);
+        if (gated) launch_stream<1, true>(a, status, st);
+        else launch_stream<1, false>(a, status, st);
     } else {
-        if (wide) launch<2, 4, 2>(a, st);
-        else if (depth >= 3) launch<2, 8, 3>(a, st);
-        else launch<2, 8, 2>(a, st);
+        if (gated) launch_stream<2, true>(a, status, st);
+        else launch_stream<2, false>(a, status, st);
     }
     RDL_CHECK_EX(g_launch_error, "gemm_skinny");
     return 0;
