@@ -106,6 +106,14 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
     const int t = blockIdx.z, g = blockIdx.y, sp = blockIdx.x;
     const int hd = EXACT ? HD : a.head_dim, ps = a.page_size;
     const int G = a.n_heads / a.n_kv_heads;
+    // The page list can only be read once the token's sequence and position are known: two trips to memory one
+    // after the other, at a time when the kernel before this one keeps the memory system busy.  In a decode
+    // step token t usually is sequence t and a run that does not start inside a window begins at page
+    // sp * pages-per-run: ask for that line of the page list now (a hint only; the reads below decide).
+    if (threadIdx.x == 0) {
+        const int guess = (sp * (a.keys_per_split / ps)) % a.ring_pages;
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(a.tables + (long long)t * a.table_width + guess));
+    }
     const int seq = a.tok_seq[t], p = a.tok_pos[t];
     if (p < 0) return;  // a padding row of a fixed-size batch
     const int lo = first_key(p, a.window);
@@ -456,9 +464,9 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
     float* w_s = sm_o;                            // [G][n_splits] weights of the runs
     float* inv_s = sm_o + G * n_splits;           // [G] 1 / normaliser
     const long long run0 = ((long long)t * a.n_heads + g * G) * a.max_splits;
-    // The first eight runs' sums of this thread's first outputs are requested before the weights are
-    // known: the two trips to L2 overlap.
-    constexpr int AHEAD = 8;
+    // The first sixteen runs' sums of this thread's first outputs are requested before the weights are
+    // known: the two trips to L2 overlap (with eight, a context of nine runs cost a third trip).
+    constexpr int AHEAD = 16;
     float4 ahead[AHEAD];
     {
         const int h = (tid * 4) / hd, d = tid * 4 - h * hd;
