@@ -31,6 +31,9 @@ import numpy as np
 import torch
 
 
+DEFAULT_PAGE_SIZE = 64   # positions a page holds unless an engine is built with another size
+
+
 class CacheError(RuntimeError):
     """A request the cache cannot serve: no free slot, no free pages, a bad or freed slot."""
 
@@ -168,7 +171,7 @@ class Cache:
     alive at once (default: max_tokens / page_size).  max_context: the longest sequence."""
 
     def __init__(self, needs: Sequence[RunNeeds], *, max_tokens: int, max_seqs: Optional[int] = None,
-                 max_context: Optional[int] = None, page_size: int = 64, dtype: torch.dtype = torch.bfloat16,
+                 max_context: Optional[int] = None, page_size: int = DEFAULT_PAGE_SIZE, dtype: torch.dtype = torch.bfloat16,
                  device="cuda", allocate: bool = True):
         if page_size < 1 or max_tokens < 1:
             raise CacheError("page_size and max_tokens must be positive")

@@ -159,7 +159,9 @@ def build_spec(cfg: Gemma2Config) -> ModelSpec:
         max_positions=cfg.max_position_embeddings, embedding=embedding, layers=tuple(layers),
         schedule=tuple(ScheduleEntry(i) for i in range(cfg.num_hidden_layers)),
         final_norm=norm("model.norm.weight"), head=head,
-        stop_token_ids=cfg.eos_token_id, bos_token_id=cfg.bos_token_id)
+        stop_token_ids=cfg.eos_token_id, bos_token_id=cfg.bos_token_id,
+        # buffers some exporters write, and the head's copy of the tied table (model.rs:829-834 ties them)
+        ignored_tensors=("*.rotary_emb.inv_freq",) + (("lm_head.weight",) if cfg.tie_word_embeddings else ()))
     spec.validate()
     return spec
 

@@ -10,13 +10,29 @@ extern "C" {
 #define RDL_ACT_GELU_TANH 0
 #define RDL_ACT_SILU 1
 
-#define RDL_ABI_VERSION 8
+#define RDL_ABI_VERSION 9
 
 const char* rdl_last_error(void);
 int rdl_abi_version(void);
 // 1 (the default): the decode-path kernels are launched with programmatic dependent launch, so that a
 // kernel's start-up overlaps the end of the kernel before it; 0: ordinary launches.
 void rdl_set_programmatic_launch(int on);
+
+// Codes a kernel leaves in the step's status word (an int the host reads after the step).  Each
+// kernel that can give up a bounded wait has its own.
+#define RDL_FAULT_TOKEN_ID 1           // embed_rows: a token id outside the table (its row is NaN)
+#define RDL_FAULT_ATTENTION_DECODE 3   // attention_decode: a page copy did not complete
+#define RDL_FAULT_GEMM_TC 4            // gemm_tc, one block a tile: a stage or an accumulator was not handed over
+#define RDL_FAULT_ATTENTION_TC 5       // attention_prefill_tc: a tile copy or a product did not complete
+#define RDL_FAULT_GEMM_TC_PAIR 6       // gemm_tc, pairs of blocks: as 4
+#define RDL_FAULT_GEMM_STREAM 7        // gemm_skinny: a weight copy did not complete
+
+// For tests of the bounded waits: the kernel whose fault code is `code` gives up a wait after `cycles`
+// clock cycles instead of about a second, and announces `extra_tx_bytes` more bytes to the barrier of
+// its first copy than that copy delivers, so that this one wait cannot complete.  The block then
+// records its code and returns normally.  code 0 switches the test off.  Kernels with the codes
+// RDL_FAULT_ATTENTION_DECODE and RDL_FAULT_GEMM_STREAM honour it.
+void rdl_set_wait_test(int code, long long cycles, int extra_tx_bytes);
 
 // One attention call over a batch of sequences: the new tokens of this step are the queries,
 // keys and values come from a paged cache and from the step's own packed rows.
@@ -47,6 +63,8 @@ typedef struct {
     // them, one token per sequence; the kernel rotates the query and key heads itself (float tables
     // [position][rotary_dim / 2]; rotary_dim 0: no rotation) and writes the new key and value rows to the cache
     const float* rope_cos; const float* rope_sin; int rotary_dim; int new_rows;
+    // filled in by the launcher: clock cycles after which a wait is given up, and the test's extra bytes
+    long long wait_cycles; int test_extra_tx;
 } AttentionArgs;
 
 int rdl_attention_plain(const AttentionArgs* a, void* stream);

@@ -28,7 +28,8 @@
 // shared memory; one launch less per layer of a decode step.
 //
 // Every wait on a copy is bounded: after about a second without completion the block records
-// an error in `status` and leaves.
+// RDL_FAULT_ATTENTION_DECODE in `status`, stops waiting and issuing, and runs on to its end, so
+// that the run counters are left as the next launch needs them; its output is void.
 #include "api.h"
 #include "common.cuh"
 #include "launch.cuh"
@@ -38,7 +39,6 @@ namespace {
 constexpr int DEC_THREADS = 128;
 constexpr int DEC_WARPS = DEC_THREADS / 32;
 constexpr int QROWS = 8;                          // most query heads per kv head: the columns of one score product
-constexpr long long WAIT_CYCLES = 2000000000LL;
 
 __device__ __forceinline__ float tanh_fast(float x) {
     float y;
@@ -82,12 +82,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// false if the copy did not complete within the limit
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+// false if the copy did not complete within the limit, or if the block has given up already
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, long long limit, volatile int* gave_up) {
+    if (*gave_up) return false;
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity))
-        if (clock64() - t0 > WAIT_CYCLES) return false;
+    while (!mbar_try_wait(bar, parity)) {
+        if (*gave_up) return false;
+        if (clock64() - t0 > limit) { *gave_up = 1; return false; }
+    }
     return true;
 }
 
@@ -100,6 +103,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
     __shared__ __align__(8) unsigned long long bar_storage[3];     // one per tile of the ring
     __shared__ float sm_m[DEC_WARPS][QROWS], sm_l[DEC_WARPS][QROWS];
     __shared__ int s_flag;
+    __shared__ int s_gave_up;      // a wait ran out: the block no longer waits or issues, and its result is void
     // new_rows: the rotated query heads of the group, then the new key row and the new value row
     __shared__ __align__(16) __nv_bfloat16 new_s[(QROWS + 2) * 256];
 
@@ -148,23 +152,28 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
         asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(vcache + off), "r"(ps * row_bytes) : "memory");
     }
     if (tid == 0) {
+        s_gave_up = 0;
         mbar_init(bars, 1);
         mbar_init(bars + 8, 1);
         mbar_init(bars + 16, 1);
     }
     __syncthreads();   // nobody waits on the barrier before it is initialised
+    volatile int* gave_up = &s_gave_up;
+    int issued = 0;    // thread 0: tiles asked for so far
     // A page's keys and its values are each one contiguous block: one bulk copy each (issued by thread 0).
     // Tile i of the run is the keys (i even) or the values (i odd) of page page_first + i / 2.
     const int n_tiles = 2 * (page_last - page_first + 1);
     auto issue = [&](int i) {
+        if (*gave_up) return;
+        issued = i + 1;
         const int page = table[(page_first + (i >> 1)) % a.ring_pages];
         const long long off = ((long long)page * a.n_kv_heads + g) * ps * hd;
         const uint32_t place = (uint32_t)(i % 3);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_expect_tx(bars + 8 * place, tile_bytes);
+        mbar_expect_tx(bars + 8 * place, tile_bytes + (i == 0 ? (uint32_t)a.test_extra_tx : 0u));
         bulk_load(tiles_s + place * tile_bytes, ((i & 1) ? vcache : kcache) + off, tile_bytes, bars + 8 * place);
     };
-    auto wait_tile = [&](int i) { return mbar_wait_bounded(bars + 8 * (uint32_t)(i % 3), (uint32_t)((i / 3) & 1)); };
+    auto wait_tile = [&](int i) { return mbar_wait_bounded(bars + 8 * (uint32_t)(i % 3), (uint32_t)((i / 3) & 1), a.wait_cycles, gave_up); };
     // The kernel before this one writes the step's new rows: positions from seq_past on.  A first page
     // that lies wholly below seq_past does not change any more and is fetched before that kernel has
     // finished.  (In a ring a new row of a later token of the same sequence could land in this page's
@@ -287,10 +296,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
     }
     for (int lp = page_first; lp <= page_last; ++lp) {
         const int ti = 2 * (lp - page_first);              // the tile of this page's keys; its values: ti + 1
-        if (!wait_tile(ti)) {
-            if (a.status) atomicExch(a.status, 3);
-            return;
-        }
+        wait_tile(ti);
         unsigned char* k_tile = smem + (size_t)(ti % 3) * tile_bytes;
         unsigned char* v_tile = smem + (size_t)((ti + 1) % 3) * tile_bytes;
 #pragma unroll
@@ -362,10 +368,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
         }
         __syncthreads();                                   // every warp is done with the key tile: its place takes tile ti + 3
         if (ti + 3 < n_tiles && tid == 0) issue(ti + 3);
-        if (!wait_tile(ti + 1)) {
-            if (a.status) atomicExch(a.status, 3);
-            return;
-        }
+        wait_tile(ti + 1);
         if (has_new && lp == page_last) {
             const int r = p - lp * ps;
             if (tid < chunks)
@@ -398,6 +401,21 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
         if (ti + 4 < n_tiles && tid == 0) issue(ti + 4);
     }
 
+    if (*gave_up) {
+        // No copy may still be on its way into this block's shared memory when the block ends: wait once more,
+        // again with the limit, for the last tile asked of each place of the ring.
+        if (tid == 0) {
+            for (int pl = 0; pl < 3; ++pl) {
+                int last = -1;
+                for (int i = pl; i < issued; i += 3) last = i;
+                if (last < 0) continue;
+                const long long t0 = clock64();
+                while (!mbar_try_wait(bars + 8 * (uint32_t)pl, (uint32_t)((last / 3) & 1)) && clock64() - t0 <= a.wait_cycles) {}
+            }
+            if (a.status) atomicExch(a.status, RDL_FAULT_ATTENTION_DECODE);
+        }
+        __syncthreads();
+    }
     // ---- merge the four warps through shared memory, in warp order ----
     float* sm_o = reinterpret_cast<float*>(smem);    // [warp][head][HD]; the tiles are no longer needed
     if (quad == 0) {
@@ -550,7 +568,10 @@ int launch_decode(const AttentionArgs* a, cudaStream_t st) {
         granted = smem;
     }
     dim3 grid(a->max_splits, a->n_kv_heads, a->n_tokens);
-    RDL_CHECK_EX(rdl_launch(attention_decode_kernel<HD, EXACT>, grid, dim3(DEC_THREADS), (size_t)smem, st, *a), "attention_decode");
+    AttentionArgs b = *a;
+    b.wait_cycles = rdl_wait_cycles_for(RDL_FAULT_ATTENTION_DECODE);
+    b.test_extra_tx = rdl_test_extra_tx_for(RDL_FAULT_ATTENTION_DECODE);
+    RDL_CHECK_EX(rdl_launch(attention_decode_kernel<HD, EXACT>, grid, dim3(DEC_THREADS), (size_t)smem, st, b), "attention_decode");
     return 0;
 }
 

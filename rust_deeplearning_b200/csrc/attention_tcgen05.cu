@@ -22,7 +22,7 @@
 namespace {
 
 constexpr int QM = 128, KN = 64, ATC_THREADS = 192;
-constexpr long long WAIT_CYCLES = 2000000000LL;
+constexpr long long WAIT_CYCLES = RDL_WAIT_CYCLES;
 constexpr float RESCALE_STEP = 8.0f;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -384,7 +384,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
             }
         }
     }
-    if (!ok && a.status) atomicExch(a.status, 5);
+    if (!ok && a.status) atomicExch(a.status, RDL_FAULT_ATTENTION_TC);
     // ---- tear-down, reached by every thread ----
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();

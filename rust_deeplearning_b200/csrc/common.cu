@@ -9,6 +9,17 @@ int g_rdl_programmatic_launch = 1;
 
 extern "C" void rdl_set_programmatic_launch(int on) { g_rdl_programmatic_launch = on ? 1 : 0; }
 
+// rdl_set_wait_test: which kernel (by fault code) runs with a short wait limit, the limit, the extra bytes
+int g_rdl_wait_test_code = 0;
+long long g_rdl_wait_test_cycles = 0;
+int g_rdl_wait_test_extra = 0;
+
+extern "C" void rdl_set_wait_test(int code, long long cycles, int extra_tx_bytes) {
+    g_rdl_wait_test_code = code;
+    g_rdl_wait_test_cycles = code ? cycles : 0;
+    g_rdl_wait_test_extra = code ? extra_tx_bytes : 0;
+}
+
 static thread_local char g_error[512] = "";
 
 void rdl_set_error(const char* fmt, ...) {

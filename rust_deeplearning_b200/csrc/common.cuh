@@ -41,6 +41,17 @@ void rdl_set_error(const char* fmt, ...);
         }                                                                   \
     } while (0)
 
+// About a second of clock cycles: the default limit of a wait inside a kernel.
+#define RDL_WAIT_CYCLES 2000000000LL
+extern int g_rdl_wait_test_code;
+extern long long g_rdl_wait_test_cycles;
+extern int g_rdl_wait_test_extra;
+// The wait limit of the kernel with fault code `code`, and the extra bytes its first copy announces (0 outside tests).
+static inline long long rdl_wait_cycles_for(int code) {
+    return (g_rdl_wait_test_code == code && g_rdl_wait_test_cycles > 0) ? g_rdl_wait_test_cycles : RDL_WAIT_CYCLES;
+}
+static inline int rdl_test_extra_tx_for(int code) { return g_rdl_wait_test_code == code ? g_rdl_wait_test_extra : 0; }
+
 static inline bool rdl_valid_dtype(int d) { return d == RDL_F32 || d == RDL_BF16; }
 static inline size_t rdl_dtype_size(int d) { return d == RDL_BF16 ? 2 : 4; }
 

@@ -24,7 +24,7 @@ __global__ void embed_rows_kernel(float* __restrict__ out, const void* __restric
     if (id < 0 || id >= vocab) {
         // never a wrong result: the row is poisoned and the step reports the fault
         for (int j = threadIdx.x; j < hidden; j += blockDim.x) o[j] = __int_as_float(0x7fc00000);
-        if (threadIdx.x == 0 && status) atomicExch(status, 1);
+        if (threadIdx.x == 0 && status) atomicExch(status, RDL_FAULT_TOKEN_ID);
         return;
     }
     const long long base = (long long)id * hidden;
@@ -223,10 +223,15 @@ extern "C" int rdl_norm_residual_norm(const void* x, int x_dtype, const int* row
         cudaError_t e;
         // Threads per row: few rows (decode) want the row spread over many threads; many rows (prefill) want
         // every thread busy and more rows in flight per multiprocessor, so the block is the smallest of
-        // 128, 192 or 256 threads that covers the row with the fewest idle lanes.
+        // 128, 192 or 256 threads that covers the row with the fewest idle lanes.  The block size fixes the
+        // order in which a row's squares are summed, so the 32-bit path (float results) always takes the one
+        // shape that depends on `hidden` alone: a row's result then does not depend on how many rows the
+        // step has.  The bfloat16 path rounds its results to 8 bits anyway and keeps the faster choice.
+        const bool float_path = y ? y_dtype == RDL_F32 : x_dtype == RDL_F32;
+        const bool many_rows = n_rows >= 256 && !float_path;
         const int quads = hidden / 4;
         int threads = 256;
-        if (n_rows >= 256) {
+        if (many_rows) {
             int best_waste = 1 << 30;
             for (int t = 128; t <= 256; t += 64) {
                 const int iter = (quads + t - 1) / t;
@@ -236,7 +241,7 @@ extern "C" int rdl_norm_residual_norm(const void* x, int x_dtype, const int* row
             }
         }
         const int iter = (quads + threads - 1) / threads;
-        const bool late = n_rows >= 256;
+        const bool late = many_rows;
 #define RDL_NORM_CASE(I, T, L) if (iter == I && threads == T && late == L) e = rdl_launch(norm_residual_norm_vec_kernel<I, T, L>, dim3(n_rows), dim3(T), 0, st, a); else
 #define RDL_NORM_ITERS(T, L) RDL_NORM_CASE(1, T, L) RDL_NORM_CASE(2, T, L) RDL_NORM_CASE(3, T, L) RDL_NORM_CASE(4, T, L) RDL_NORM_CASE(5, T, L) RDL_NORM_CASE(6, T, L) RDL_NORM_CASE(7, T, L) RDL_NORM_CASE(8, T, L)
         RDL_NORM_ITERS(128, true) RDL_NORM_ITERS(192, true) RDL_NORM_ITERS(256, true) RDL_NORM_ITERS(256, false)

@@ -52,6 +52,8 @@ struct SkinnyArgs {
     int out_dtype;              // RDL_F32 / RDL_BF16
     int activation;             // of the gated form
     float softcap;              // > 0: cap * tanh(v / cap)
+    long long wait_cycles;      // clock cycles after which a wait is given up
+    int test_extra_tx;          // tests only: bytes announced beyond what the block's first copy delivers
 };
 
 thread_local cudaError_t g_launch_error = cudaSuccess;
@@ -67,7 +69,6 @@ __host__ __device__ constexpr int st_pitch(int ku) { return st_kt(ku) * 2 + 64; 
 __host__ __device__ constexpr int st_tile_bytes(int ku) { return ROWS * st_pitch(ku); }
 __host__ __device__ constexpr int st_stages(int ku) { return ku == 4 ? 3 : 4; }      // about 100 KB a block; twice that where one block has a multiprocessor to itself
 constexpr int ST_MAX_STAGES = 8;
-constexpr long long ST_WAIT_CYCLES = 2000000000LL;
 
 __device__ __forceinline__ void st_mbar_init(uint32_t bar, int count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
@@ -90,12 +91,13 @@ __device__ __forceinline__ bool st_mbar_try_wait(uint32_t bar, uint32_t parity) 
 }
 // false if the barrier's phase did not complete within about a second, or if another warp of the block has
 // already given up (the block then runs to its end without waiting; its status word says that the result is void)
-__device__ __forceinline__ bool st_wait(uint32_t bar, uint32_t parity, volatile int* gave_up) {
+__device__ __forceinline__ bool st_wait(uint32_t bar, uint32_t parity, long long limit, volatile int* gave_up) {
+    if (*gave_up) return false;
     if (st_mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (!st_mbar_try_wait(bar, parity)) {
         if (*gave_up) return false;
-        if (clock64() - t0 > ST_WAIT_CYCLES) { *gave_up = 1; return false; }
+        if (clock64() - t0 > limit) { *gave_up = 1; return false; }
     }
     return true;
 }
@@ -135,6 +137,7 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(SkinnyArgs a
         if (lane < ROWS) {
             int s = 0;                                   // place in the ring, and how often it has been gone round
             uint32_t round = 0;
+            bool first_copy = true;
             for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x) {
                 long long row;
                 bool row_ok;
@@ -149,15 +152,16 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(SkinnyArgs a
                 const int n_ok = __popc(__ballot_sync(0xffffu, row_ok));
                 for (int tk = 0; tk < tiles_per_unit; ++tk) {
                     // the tile that lay here must have been read by all eight warps
-                    if (round > 0 && !st_wait(empty_s + 8 * s, (round & 1) ^ 1, gave_up_v)) break;
+                    if (round > 0 && !st_wait(empty_s + 8 * s, (round & 1) ^ 1, a.wait_cycles, gave_up_v)) break;
                     const int k0 = tk * ST_KT;
                     const uint32_t bytes = (uint32_t)((K - k0 < ST_KT ? K - k0 : ST_KT) * 2);
                     if (lane == 0) {
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                        st_mbar_expect_tx(full_s + 8 * s, bytes * (uint32_t)n_ok);
+                        st_mbar_expect_tx(full_s + 8 * s, bytes * (uint32_t)n_ok + (first_copy ? (uint32_t)a.test_extra_tx : 0u));
                     }
                     __syncwarp(0xffffu);
                     if (row_ok) st_bulk_load(tiles_s + (uint32_t)(s * ST_TILE_BYTES + lane * ST_PITCH), a.w + row * K + k0, bytes, full_s + 8 * s);
+                    first_copy = false;
                     if (++s == stages) { s = 0; ++round; }
                 }
                 if (*gave_up_v) break;
@@ -202,7 +206,7 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(SkinnyArgs a
                 // the activations of the tile after this one (the next unit starts again at k = 0)
                 if (X_AHEAD) load_x((tk + 1 < tiles_per_unit ? (tk + 1) * ST_KT : 0) + kw, reinterpret_cast<uint4 (&)[NT][KU]>(xnext));
                 else load_x(tk * ST_KT + kw, xcur);
-                st_wait(full_s + 8 * s, round & 1, gave_up_v);
+                st_wait(full_s + 8 * s, round & 1, a.wait_cycles, gave_up_v);
                 const int kb = tk * ST_KT + kw;
                 if (kb < K) {
                     const uint32_t base = frag + (uint32_t)(s * ST_TILE_BYTES);
@@ -254,7 +258,7 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(SkinnyArgs a
             asm volatile("bar.sync 1, %0;" ::"n"(ST_WARPS * 32) : "memory");      // the partial sums are free again
         }
     }
-    if (*gave_up_v && status && lane == 0) atomicExch(status, 5);
+    if (*gave_up_v && status && lane == 0) atomicExch(status, RDL_FAULT_GEMM_STREAM);
 }
 
 template <int NT, bool GATED, int KU>
@@ -300,7 +304,8 @@ extern "C" int rdl_gemm_skinny(void* out, int out_dtype, const void* x, const vo
     RDL_REQUIRE(!gated || activation == RDL_ACT_GELU_TANH || activation == RDL_ACT_SILU, "gemm_skinny: unknown activation %d", activation);
     RDL_REQUIRE(softcap >= 0.f, "gemm_skinny: soft-cap must not be negative");
     if (m == 0) return 0;
-    SkinnyArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, out, m, n, k, out_dtype, activation, softcap};
+    SkinnyArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, out, m, n, k, out_dtype, activation, softcap,
+                 rdl_wait_cycles_for(RDL_FAULT_GEMM_STREAM), rdl_test_extra_tx_for(RDL_FAULT_GEMM_STREAM)};
     cudaStream_t st = (cudaStream_t)stream;
     g_launch_error = cudaSuccess;
     if (m <= 8) {

@@ -33,7 +33,7 @@
 namespace {
 
 constexpr int BM = 128, BK = 64, TC_THREADS = 320;
-constexpr long long WAIT_CYCLES = 2000000000LL;
+constexpr long long WAIT_CYCLES = RDL_WAIT_CYCLES;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -314,7 +314,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
             epilogue_columns<GATED>(a, tcol, BN, col_half * (BN / 2), (col_half + 1) * (BN / 2), n0, m0 + h * BM + q * 32, lane, stage);
         }
     }
-    if (!ok && a.status) atomicExch(a.status, 4);
+    if (!ok && a.status) atomicExch(a.status, RDL_FAULT_GEMM_TC);
     // ---- tear-down, reached by every thread ----
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -494,7 +494,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             if (lane == 0) mbar_arrive_at(acc_empty_at_leader0 + (uint32_t)(buf * 8));
         }
     }
-    if (!ok && a.status) atomicExch(a.status, 4);
+    if (!ok && a.status) atomicExch(a.status, RDL_FAULT_GEMM_TC_PAIR);
     // ---- tear-down, reached by every thread of both blocks ----
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();

@@ -14,7 +14,7 @@ from ..parts.model import Model
 from ..sampling.sampler import SamplingParams
 from ..weights.loader import load_weights, random_weights
 from ..weights.random_init import parse_dtype
-from .generate import GenerationResult, generate
+from .generate import GenerationResult, GenerationStats, generate
 from .step import Engine
 
 
@@ -27,16 +27,17 @@ def _require_cuda(device):
     return dev
 
 
-def load_model(folder: str, dtype: Union[str, torch.dtype] = "bfloat16", device="cuda:0") -> Model:
+def load_model(folder: str, dtype: Union[str, torch.dtype] = "bfloat16", device="cuda:0", strict: bool = True) -> Model:
     """A model folder (config.json + model.safetensors) -> a model on the device.  The model class
     is chosen by config.json.  dtype "bfloat16": the serving kernels; "float32": everything in
-    true 32-bit."""
+    true 32-bit.  strict False: tensors the model does not read are skipped with a warning instead
+    of being an error."""
     dev = _require_cuda(device)
     dtype = parse_dtype(dtype)
     raw = read_config_json(folder)
     arch = architecture_for(raw)
     spec = arch.build_spec(arch.parse_config(raw))
-    weights = load_weights(spec, folder, dtype, dev)
+    weights = load_weights(spec, folder, dtype, dev, strict)
     return Model(spec, weights, dtype, dev)
 
 
@@ -54,13 +55,13 @@ class Generator:
     """Model + cache + sampler.  Options are set with `with_*` calls that return the generator."""
 
     def __init__(self, model: Model, *, max_cache_tokens: Optional[int] = None, max_batch: int = 64,
-                 max_context: Optional[int] = None, use_graphs: bool = True):
+                 max_context: Optional[int] = None, use_graphs: bool = True, time_steps: bool = False):
         max_context = min(max_context or model.max_positions, model.max_positions)
         if max_cache_tokens is None:
             max_cache_tokens = max_batch * max_context
         self.model = model
         self.engine = Engine(model, max_tokens=max_cache_tokens, max_seqs=max_batch, max_context=max_context,
-                             use_graphs=use_graphs)
+                             use_graphs=use_graphs, time_steps=time_steps)
         self._temperature = 0.8
         self._top_k: Optional[int] = None
         self._top_p: Optional[float] = None
@@ -116,9 +117,10 @@ class Generator:
 
     # ---- generation ----
     def generate_batch_results(self, prompts: Sequence[Sequence[int]], max_tokens: int = 256,
-                               stream: Optional[Callable[[int, int], Optional[bool]]] = None) -> List[GenerationResult]:
+                               stream: Optional[Callable[[int, int], Optional[bool]]] = None,
+                               stats: Optional[GenerationStats] = None) -> List[GenerationResult]:
         return generate(self.engine, self._prompts(prompts), max_new_tokens=max_tokens, sampling=self._params(),
-                        stop_token_ids=self._stop, include_stop=self._include_stop, stream=stream)
+                        stop_token_ids=self._stop, include_stop=self._include_stop, stream=stream, stats=stats)
 
     def generate(self, prompt: Sequence[int], max_tokens: int = 256) -> List[int]:
         """Prompt plus generated tokens, as the reference returns prompt plus completion (generator.rs:272)."""

@@ -20,6 +20,7 @@ the loop waits for each step.
 """
 from __future__ import annotations
 
+import time
 from dataclasses import dataclass, field
 from typing import Callable, Iterable, List, Optional, Sequence
 
@@ -32,6 +33,23 @@ from ..sampling.sampler import Sampler, SamplingParams
 class GenerationResult:
     tokens: List[int]          # the new tokens (a stop token is left out unless asked for)
     finish_reason: str         # "stop" | "length" | "context"
+
+
+@dataclass
+class GenerationStats:
+    """Host wall-clock of a `generate` call, as the reference prints it for its own loop
+    (`rustml/nlp/examples/gemma3_gguf.rs:29-75`): the prompts' step up to the first sampled tokens,
+    then all single-token steps."""
+    prefill_tokens: int = 0
+    prefill_seconds: float = 0.0
+    decode_tokens: int = 0
+    decode_seconds: float = 0.0
+
+    def prefill_rate(self) -> float:
+        return self.prefill_tokens / self.prefill_seconds if self.prefill_seconds > 0 else 0.0
+
+    def decode_rate(self) -> float:
+        return self.decode_tokens / self.decode_seconds if self.decode_seconds > 0 else 0.0
 
 
 @dataclass
@@ -128,13 +146,15 @@ class _Readback:
 def generate(engine, prompts: Sequence[Sequence[int]], *, max_new_tokens: int = 256,
              sampling: Optional[SamplingParams] = None, stop_token_ids: Optional[Iterable[int]] = None,
              include_stop: bool = False, stream: Optional[Callable[[int, int], Optional[bool]]] = None,
-             max_batch: Optional[int] = None, run_ahead: bool = True) -> List[GenerationResult]:
+             max_batch: Optional[int] = None, run_ahead: bool = True,
+             stats: Optional[GenerationStats] = None) -> List[GenerationResult]:
     """Generate for every prompt (lists of token ids).
 
     stop_token_ids: default, the model's end-of-sequence ids.  stream(request index, token) is
     called for every kept token; returning False ends that request (as the reference's streaming
     callback does, generator.rs:277-318).  run_ahead False waits for every step's tokens before the
-    next step is queued (the results are the same)."""
+    next step is queued (the results are the same).  stats, if given, receives the call's token counts
+    and host times (prompts up to their first sampled tokens; then the single-token steps)."""
     sampling = sampling or SamplingParams()
     model, cache = engine.model, engine.cache
     stops = frozenset(model.spec.stop_token_ids if stop_token_ids is None else stop_token_ids)
@@ -168,8 +188,10 @@ def generate(engine, prompts: Sequence[Sequence[int]], *, max_new_tokens: int = 
                 return _Readback(toks, pinned[flip[0]] if pinned is not None else None)
 
             rows = list(range(len(seqs)))       # the sequences whose tokens `sampled` holds, row by row
+            t_start = time.perf_counter()
             sampled = sample(rows, engine.step([slots[j] for j in rows], [s.prompt for s in seqs], "last"))
             ahead = run_ahead and not need_history
+            first = True
             while rows:
                 nxt_rows, nxt = [], None
                 if ahead:
@@ -182,6 +204,13 @@ def generate(engine, prompts: Sequence[Sequence[int]], *, max_new_tokens: int = 
                         nxt = sample(nxt_rows, logits)
                 tokens = sampled.tokens()
                 engine.check_status()
+                if first and stats is not None:
+                    # the first tokens are on the host: the prompts' step is over
+                    now = time.perf_counter()
+                    stats.prefill_tokens += sum(len(s.prompt) for s in seqs)
+                    stats.prefill_seconds += now - t_start
+                    t_start = now
+                first = False
                 go_on = []
                 for j, tok in zip(rows, tokens):
                     s = seqs[j]
@@ -208,6 +237,9 @@ def generate(engine, prompts: Sequence[Sequence[int]], *, max_new_tokens: int = 
             for sl in slots:
                 if sl is not None:
                     engine.release(sl)
+        if stats is not None:
+            stats.decode_tokens += sum(max(s.sampled - 1, 0) for s in seqs)
+            stats.decode_seconds += time.perf_counter() - t_start
         for s in seqs:
             results[s.request] = GenerationResult(s.new_tokens, s.finish_reason)
     return results

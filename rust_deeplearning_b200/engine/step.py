@@ -18,8 +18,8 @@ from typing import Tuple, Dict, List, Optional, Sequence, Union
 import numpy as np
 import torch
 
-from ..cache.cache import Cache
-from ..kernels import library
+from ..cache.cache import DEFAULT_PAGE_SIZE, Cache
+from ..kernels import library, ops
 from .batch import BatchLayout, StepBatch, batch_from_buffer, count_tiles, fill_batch
 
 
@@ -47,7 +47,8 @@ class Engine:
     """A model, its cache and the step function."""
 
     def __init__(self, model, *, max_tokens: int, max_seqs: Optional[int] = None, max_context: Optional[int] = None,
-                 page_size: int = 64, use_graphs: bool = True, allocate: bool = True):
+                 page_size: int = DEFAULT_PAGE_SIZE, use_graphs: bool = True, allocate: bool = True,
+                 time_steps: bool = False):
         self.model = model
         self.device = model.device
         max_context = min(max_context or model.max_positions, model.max_positions)
@@ -61,6 +62,9 @@ class Engine:
         self._scratch: Dict[str, torch.Tensor] = {}
         self.graph_replays = 0
         self.eager_steps = 0
+        # time_steps: every step is bracketed by CUDA events on its stream; `step_timings()` reads them
+        self.time_steps = time_steps and self.device.type == "cuda"
+        self._timed: List[tuple] = []
         # kernels set this word when they give up a bounded wait; pinned host memory, so the host
         # reads it without a device call (after any synchronising read of a step's result)
         self.status = torch.zeros(1, dtype=torch.int32)
@@ -82,7 +86,8 @@ class Engine:
         code = int(self.status[0])
         if code:
             self.status[0] = 0
-            raise RuntimeError(f"a kernel reported fault {code} (1: token outside the vocabulary, 3: a copy did not complete)")
+            raise RuntimeError(f"a kernel reported fault {code}: {library.FAULTS.get(code, 'unknown code')}; "
+                               f"the results of that step are void")
 
     # ---- the step ----
     def step(self, slots: Sequence[int], tokens: Optional[Sequence[Sequence[int]]],
@@ -128,6 +133,9 @@ class Engine:
         if max(totals) > self.model.max_positions:
             raise StepError(f"a sequence would reach {max(totals)} positions, the model allows {self.model.max_positions}")
         self.cache.reserve(slots, lens)
+        if self.time_steps:
+            t0 = torch.cuda.Event(enable_timing=True)
+            t0.record()
         tables = [g.table_rows(slots) for g in self.cache.kv_groups]
         widths = [g.table_width for g in self.cache.kv_groups]
         is_decode = max(lens) == 1
@@ -149,12 +157,31 @@ class Engine:
                                       is_decode=is_decode, max_total_len=max(totals), scratch=self._scratch)
             batch.status = self.status
             batch.has_past = max(past) > 0
-            logits = self.model.forward(batch, self.cache)
+            logits = self._forward(batch)
             self.eager_steps += 1
         self.cache.advance(slots, lens)
+        if self.time_steps:
+            t1 = torch.cuda.Event(enable_timing=True)
+            t1.record()
+            self._timed.append(("decode" if is_decode else "prompt", n, sum(lens), t0, t1))
         return logits
 
+    def step_timings(self) -> List[dict]:
+        """Device time of every step since the last call (needs time_steps=True): kind, sequences,
+        tokens, milliseconds between CUDA events recorded before and after the step's work."""
+        out = []
+        for kind, n_seqs, n_tokens, t0, t1 in self._timed:
+            t1.synchronize()
+            out.append({"kind": kind, "sequences": n_seqs, "tokens": n_tokens, "ms": t0.elapsed_time(t1)})
+        self._timed = []
+        return out
+
     # ---- helpers ----
+    def _forward(self, batch: StepBatch) -> torch.Tensor:
+        """The model on the batch; every kernel it launches reports faults to the engine's status word."""
+        with ops.step_status(self.status if self.device.type == "cuda" else None):
+            return self.model.forward(batch, self.cache)
+
     def _host_buffer(self, size: int) -> torch.Tensor:
         self._flip ^= 1
         i = self._flip
@@ -205,7 +232,7 @@ class Engine:
             graph = torch.cuda.CUDAGraph()
             before = library.launch_count
             with torch.cuda.graph(graph):
-                g.logits = self.model.forward(g.batch, self.cache)
+                g.logits = self._forward(g.batch)
             g.kernels = library.launch_count - before     # captured, not run
             library.launch_count = before
             g.graph = graph
@@ -215,7 +242,7 @@ class Engine:
             self.graph_replays += 1
             logits = g.logits
         else:
-            logits = self.model.forward(g.batch, self.cache)
+            logits = self._forward(g.batch)
             self.eager_steps += 1
         for i, w in enumerate(want):
             if any(x != 0 for x in w):

@@ -30,17 +30,18 @@ def run(argv=None, stdin=None, stdout=None) -> int:
                     help="bfloat16: the serving kernels; float32: everything in true 32-bit")
     ap.add_argument("--out", required=True, help="folder that receives <step>.f32")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time, each rounded up to a multiple of 64")
+                    help="most tokens live requests hold at any time, each rounded up to a multiple of the page size (64)")
     args = ap.parse_args(argv)
     stdin = stdin or sys.stdin
     stdout = stdout or sys.stdout
 
+    from ..cache.cache import DEFAULT_PAGE_SIZE
     from .api import load_model
     from .step import Engine
 
     os.makedirs(args.out, exist_ok=True)
     model = load_model(args.model, args.dtype)
-    page = 64
+    page = DEFAULT_PAGE_SIZE     # the unit requests' token counts are rounded up to
     max_tokens = max(page, -(-args.max_tokens // page) * page)
     engine = Engine(model, max_tokens=max_tokens, max_seqs=max_tokens // page,
                     max_context=min(model.max_positions, max_tokens), page_size=page)

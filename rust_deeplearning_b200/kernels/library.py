@@ -23,7 +23,7 @@ from concurrent.futures import ThreadPoolExecutor
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(_PKG, "csrc")
 LIB_NAME = "librdl_b200_kernels.so"
-ABI_VERSION = 8
+ABI_VERSION = 9
 
 # fast math is never enabled: the 32-bit path relies on exact tanhf/expf/sqrtf and plain FMA
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -156,7 +156,19 @@ class AttentionArgs(ctypes.Structure):
         ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_longlong),
         ("counter_bytes", ctypes.c_longlong), ("status", ctypes.c_void_p),
         ("rope_cos", ctypes.c_void_p), ("rope_sin", ctypes.c_void_p), ("rotary_dim", ctypes.c_int), ("new_rows", ctypes.c_int),
+        ("wait_cycles", ctypes.c_longlong), ("test_extra_tx", ctypes.c_int),     # filled in by the launcher
     ]
+
+
+# What a kernel leaves in a step's status word when it gives up (`csrc/api.h`, RDL_FAULT_*).
+FAULTS = {
+    1: "embed_rows: a token id outside the vocabulary (its row is NaN)",
+    3: "attention_decode: a page copy did not complete",
+    4: "gemm_tc: a stage or an accumulator was not handed over",
+    5: "attention_prefill_tc: a tile copy or a product did not complete",
+    6: "gemm_tc (pairs of blocks): a stage or an accumulator was not handed over",
+    7: "gemm_skinny: a weight copy did not complete",
+}
 
 
 class SamplingArgs(ctypes.Structure):
@@ -180,6 +192,7 @@ _SIGNATURES = {
     "rdl_gemm_f32": [_P, _P, _P, _I, _I, _I, _P],
     "rdl_gemm_skinny": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
     "rdl_gemm_tc": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
+    "rdl_random_normal": [_P, _I, _LL, ctypes.c_ulonglong, ctypes.c_double, _P],
     "rdl_sample": [_P, _P, _I, _I, ctypes.POINTER(SamplingArgs), _P, _P, _P, _P, _P, _P],
 }
 
@@ -216,6 +229,8 @@ def load():
         lib.rdl_sampling_uniform.restype = ctypes.c_float
         lib.rdl_set_programmatic_launch.argtypes = [ctypes.c_int]
         lib.rdl_set_programmatic_launch.restype = None
+        lib.rdl_set_wait_test.argtypes = [ctypes.c_int, ctypes.c_longlong, ctypes.c_int]
+        lib.rdl_set_wait_test.restype = None
         if os.environ.get("RDL_PROGRAMMATIC_LAUNCH") == "0":   # ordinary launches, for comparison
             lib.rdl_set_programmatic_launch(0)
         _lib = lib

@@ -18,6 +18,33 @@ from .library import AttentionArgs, KernelError, SamplingArgs
 
 ACTIVATIONS = {"gelu_pytorch_tanh": 0, "gelu_tanh": 0, "silu": 1}
 
+# The status word of the step that is running: every kernel that can report a fault (a token id
+# outside the table, a bounded wait that ran out) gets it unless the caller passes one of its own.
+# The engine sets it around a step; parts need not know about it.
+_step_status: Optional[torch.Tensor] = None
+
+
+class step_status:
+    """`with ops.step_status(word): ...` - kernels launched inside report their faults to `word` (int32[1])."""
+
+    def __init__(self, word: Optional[torch.Tensor]):
+        self.word = word
+
+    def __enter__(self):
+        global _step_status
+        self.before, _step_status = _step_status, self.word
+        return self.word
+
+    def __exit__(self, *exc):
+        global _step_status
+        _step_status = self.before
+        return False
+
+
+def _status(status: Optional[torch.Tensor]):
+    status = status if status is not None else _step_status
+    return ctypes.c_void_p(status.data_ptr()) if status is not None else None
+
 
 def _dtype_code(t: torch.Tensor) -> int:
     if t.dtype is torch.float32:
@@ -67,7 +94,7 @@ def embed_rows(table: torch.Tensor, ids: torch.Tensor, scale: float, status: Opt
     T = ids.numel()
     out = torch.empty((T, H), dtype=torch.float32, device=table.device)
     library.check(library.load().rdl_embed_rows(_ptr(out), _ptr(table), _dtype_code(table), _ptr(ids), float(scale),
-                                                T, H, V, _ptr(status), _stream(table)))
+                                                T, H, V, _status(status), _stream(table)))
     return out
 
 
@@ -184,10 +211,10 @@ def _gemm_bf16(x, weight, n_out, out_dtype, gated, activation, softcap, status):
     lib = library.load()
     if x.shape[0] <= SKINNY_MAX_ROWS:
         library.check(lib.rdl_gemm_skinny(_ptr(out), _dtype_code(out), _ptr(x), _ptr(weight), x.shape[0], n_out, x.shape[1],
-                                          int(gated), activation, float(softcap or 0.0), _ptr(status), _stream(x)))
+                                          int(gated), activation, float(softcap or 0.0), _status(status), _stream(x)))
     else:
         library.check(lib.rdl_gemm_tc(_ptr(out), _dtype_code(out), _ptr(x), _ptr(weight), x.shape[0], n_out, x.shape[1],
-                                      int(gated), activation, float(softcap or 0.0), _ptr(status), _stream(x)))
+                                      int(gated), activation, float(softcap or 0.0), _status(status), _stream(x)))
     return out
 
 
@@ -374,7 +401,7 @@ def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n
         if kind == "prefill_tc":
             # sequences that start at position 0, packed q/k/v rows, head_dim a multiple of 64
             _need(new_kv is not None and new_kv[0] is q, "attention: the tcgen05 prefill kernel reads packed q/k/v rows")
-            a.status = status.data_ptr() if status is not None else None
+            a.status = _status(status)
             library.check(lib.rdl_attention_prefill_tc(ctypes.byref(a), q.stride(0), _stream(q)))
         else:
             library.check(lib.rdl_attention_prefill(ctypes.byref(a), _stream(q)))
@@ -390,7 +417,7 @@ def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n
         _need(buf.dtype is torch.float32 and buf.numel() * 4 >= need, "attention: decode scratch too small")
         a.scratch, a.scratch_bytes = buf.data_ptr(), buf.numel() * 4
         a.counter_bytes = lib.rdl_attention_decode_counter_bytes(b.n_tokens, n_kv_heads)
-        a.status = status.data_ptr() if status is not None else None
+        a.status = _status(status)
         if rotate_and_write is not None:
             cos, sin, rotary_dim = rotate_and_write
             _need(new_kv is not None, "attention: rotate_and_write needs the step's key and value rows")
@@ -402,6 +429,19 @@ def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n
         library.check(lib.rdl_attention_decode(ctypes.byref(a), _stream(q)))
     else:
         raise KernelError(f"attention: unknown kind '{kind}'")
+    return out
+
+
+# ------------------------------------------------------------------------------------------
+# random weights
+# ------------------------------------------------------------------------------------------
+
+def random_normal(shape, key: int, std: float, dtype: torch.dtype, device) -> torch.Tensor:
+    """N(0, std) values of the tensor with 64-bit `key`, made on the device: element j depends only on
+    (key, j) and equals, bit for bit in float32, what `weights.counter_random.normal` makes on the host."""
+    out = torch.empty(shape, dtype=dtype, device=device)
+    library.check(library.load().rdl_random_normal(_ptr(out), _dtype_code(out), out.numel(), int(key) & (2**64 - 1),
+                                                   float(std), _stream(out)))
     return out
 
 

@@ -117,11 +117,11 @@ class Model:
             out.append(RunNeeds(kv, state, s.reads_cache_of))
         return out
 
-    def forward(self, batch, cache, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, batch, cache) -> torch.Tensor:
         """Runs the batch's tokens through the schedule; float32 logits [wanted rows, vocab]."""
         batch.cache_owner_of, batch.shared_runs = self.cache_owner_of, self.shared_runs
         batch.new_kv.clear()
-        stream = ResidualStream(self.embedding.forward(batch.tokens, status))
+        stream = ResidualStream(self.embedding.forward(batch.tokens))
         for run, entry in enumerate(self.schedule):
             self.layers[entry.layer].forward(stream, batch, cache.run_cache(run), run)
         batch.new_kv.clear()

@@ -68,6 +68,9 @@ class ModelSpec:
     head: PartSpec
     stop_token_ids: Tuple[int, ...] = ()
     bos_token_id: Optional[int] = None
+    # tensors a checkpoint of this architecture may carry that the model does not read (buffers such as
+    # rotary frequencies, a copy of tied weights): names or shell-style patterns; they are skipped silently
+    ignored_tensors: Tuple[str, ...] = ()
 
     def part_specs(self):
         yield self.embedding

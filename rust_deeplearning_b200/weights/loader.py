@@ -9,12 +9,14 @@ wrong shapes and unusable dtypes.
 """
 from __future__ import annotations
 
-import zlib
+import fnmatch
+import warnings
 from typing import Dict, Optional
 
 import torch
 
 from ..parts.spec import ModelSpec, TensorSpec
+from . import counter_random
 from .safetensors_io import WeightFiles
 
 _FLOAT_FILE_DTYPES = ("F32", "BF16", "F16", "F64")
@@ -51,11 +53,19 @@ def stored_dtype(spec: TensorSpec, file_dtype: str, compute_dtype: torch.dtype) 
     return compute_dtype
 
 
-def check_weights(spec: ModelSpec, files, where: str) -> None:
+def check_weights(spec: ModelSpec, files, where: str, strict: bool = True) -> None:
+    """Compare the files with the model's description; one WeightError lists everything that is wrong.
+    Tensors the model does not read are an error too, unless the architecture declares them
+    (`ModelSpec.ignored_tensors`) or `strict` is False, in which case they are listed in a warning
+    and skipped, as the reference does (`rustml/nlp/main/src/core/weight_map.rs:360-362`)."""
     wanted = spec.tensor_specs()
     have = set(files.names())
     missing = sorted(n for n in wanted if n not in have)
-    unexpected = sorted(n for n in have if n not in wanted)
+    unexpected = sorted(n for n in have if n not in wanted
+                        and not any(fnmatch.fnmatchcase(n, pat) for pat in spec.ignored_tensors))
+    if unexpected and not strict:
+        warnings.warn(f"{where}: {len(unexpected)} tensors the model does not read are skipped: " + ", ".join(unexpected))
+        unexpected = []
     wrong_shape, wrong_dtype = [], []
     for name, t in wanted.items():
         if name not in have:
@@ -70,10 +80,10 @@ def check_weights(spec: ModelSpec, files, where: str) -> None:
         raise WeightError(where, missing, unexpected, wrong_shape, wrong_dtype)
 
 
-def load_weights(spec: ModelSpec, folder: str, compute_dtype: torch.dtype, device) -> Dict[str, torch.Tensor]:
+def load_weights(spec: ModelSpec, folder: str, compute_dtype: torch.dtype, device, strict: bool = True) -> Dict[str, torch.Tensor]:
     """Every tensor the model names, on `device`, in the dtype it is kept in."""
     files = WeightFiles(folder)
-    check_weights(spec, files, folder)
+    check_weights(spec, files, folder, strict)
     out = {}
     for name, t in spec.tensor_specs().items():
         file_dtype, _ = files.info(name)
@@ -82,20 +92,21 @@ def load_weights(spec: ModelSpec, folder: str, compute_dtype: torch.dtype, devic
     return out
 
 
-def _tensor_seed(seed: int, name: str) -> int:
-    return (int(seed) * 0x9E3779B1 + zlib.crc32(name.encode())) & 0x7FFFFFFFFFFFFFFF
-
-
 def random_tensor(t: TensorSpec, seed: int, dtype: torch.dtype, device="cpu") -> torch.Tensor:
-    """N(0, init_std) from a generator seeded by (seed, tensor name), so a tensor's values
-    do not depend on which other tensors the model has.  The reference's random models are
-    unseeded (`rustml/core/main/src/core/tensor/tensor.rs:217-238`)."""
+    """N(0, init_std) values that depend only on (seed, tensor name, element index): the same
+    float32 numbers, bit for bit, whether they are made on the host or on a CUDA device
+    (`weights/counter_random.py`, `csrc/random_init.cu`), rounded to `dtype` to nearest even.
+    The reference's random models are unseeded (`rustml/core/main/src/core/tensor/tensor.rs:217-238`)."""
     if t.kind == "int":
         raise ValueError(f"no random initialisation for integer table '{t.name}'")
-    g = torch.Generator(device=device)
-    g.manual_seed(_tensor_seed(seed, t.name))
-    x = torch.empty(t.shape, dtype=torch.float32, device=device)
-    x.normal_(0.0, t.init_std, generator=g)
+    key = counter_random.tensor_key(seed, t.name)
+    n = 1
+    for d in t.shape:
+        n *= int(d)
+    if torch.device(device).type == "cuda":
+        from ..kernels import ops
+        return ops.random_normal(tuple(t.shape), key, t.init_std, dtype, device)
+    x = torch.from_numpy(counter_random.normal(n, key, t.init_std)).reshape(tuple(t.shape))
     return x.to(dtype)
 
 

@@ -33,9 +33,12 @@ def parse_dtype(name: Union[str, torch.dtype]) -> torch.dtype:
 
 
 def write_random_model(folder: str, config: Dict[str, Any], seed: int,
-                       dtype: Union[str, torch.dtype] = "bfloat16") -> str:
+                       dtype: Union[str, torch.dtype] = "bfloat16", device="cpu") -> str:
     """Create `folder` with config.json and model.safetensors holding N(0, 0.02) tensors
-    (every tensor, norm weights too) in `dtype`, reproducibly from `seed`."""
+    (every tensor, norm weights too) in `dtype`, reproducibly from `seed`.  The values depend only
+    on (seed, tensor name, element index); `device` only says where they are made (a CUDA device
+    makes large models quickly and gives the same file), and `random_model` with the same
+    configuration and seed holds the same weights."""
     dtype = parse_dtype(dtype)
     arch = architecture_for(config)
     typed = arch.parse_config(config)
@@ -47,7 +50,7 @@ def write_random_model(folder: str, config: Dict[str, Any], seed: int,
     out["torch_dtype"] = "float32" if dtype is torch.float32 else "bfloat16"
     with open(os.path.join(folder, "config.json"), "w") as f:
         json.dump(out, f, indent=1)
-    tensors = {name: random_tensor(t, seed, dtype) for name, t in spec.tensor_specs().items()}
+    tensors = {name: random_tensor(t, seed, dtype, device).cpu() for name, t in spec.tensor_specs().items()}
     write_safetensors(os.path.join(folder, "model.safetensors"), tensors,
                       {"format": "pt", "seed": str(seed)})
     return folder

@@ -13,7 +13,8 @@ def test_help_lists_every_option(capsys):
     assert e.value.code == 0
     out = capsys.readouterr().out
     for opt in ("MODEL_DIR", "--prompt", "--prompt-ids", "--prompt-file", "--max-tokens", "--temperature", "--top-k",
-                "--top-p", "--repetition-penalty", "--stream", "--seed", "--dtype", "--stop-ids", "--max-context"):
+                "--top-p", "--repetition-penalty", "--stream", "--seed", "--dtype", "--stop-ids", "--max-context",
+                "--random-config", "--weights-seed", "--timings"):
         assert opt in out, opt
     assert "(0.0 = greedy)" in out
     p = cli.build_parser()
@@ -45,4 +46,14 @@ def test_prompt_file(tmp_path):
 
 def test_a_bad_model_folder_is_an_error_message(tmp_path, capsys):
     assert cli.main([str(tmp_path / "nowhere"), "--prompt-ids", "1"]) == 1
+    assert "error:" in capsys.readouterr().err
+
+
+def test_model_dir_or_random_config_exactly_one(tmp_path, capsys):
+    with pytest.raises(SystemExit) as e:
+        cli.main(["--prompt-ids", "1"])
+    assert "MODEL_DIR or --random-config" in str(e.value)
+    with pytest.raises(SystemExit):
+        cli.main([str(tmp_path), "--random-config", str(tmp_path / "c.json"), "--prompt-ids", "1"])
+    assert cli.main(["--random-config", str(tmp_path / "missing.json"), "--prompt-ids", "1"]) == 1
     assert "error:" in capsys.readouterr().err

@@ -109,7 +109,7 @@ def test_one_error_lists_missing_unexpected_and_misshaped(tmp_path):
     tensors = {n: f.tensor(n).clone() for n in f.names()}
     del f
     del tensors["model.layers.1.mlp.up_proj.weight"], tensors["model.norm.weight"]
-    tensors["lm_head.weight"] = torch.zeros(256, 64)
+    tensors["model.layers.0.self_attn.bias_q"] = torch.zeros(64)
     tensors["model.layers.0.self_attn.q_proj.weight"] = torch.zeros(64, 63)
     tensors["model.layers.0.input_layernorm.weight"] = torch.zeros(64, dtype=torch.int32)
     write_safetensors(path, tensors)
@@ -117,12 +117,61 @@ def test_one_error_lists_missing_unexpected_and_misshaped(tmp_path):
         load_weights(spec_of(cfg), folder, torch.float32, "cpu")
     err = e.value
     assert err.missing == ["model.layers.1.mlp.up_proj.weight", "model.norm.weight"]
-    assert err.unexpected == ["lm_head.weight"]
+    assert err.unexpected == ["model.layers.0.self_attn.bias_q"]
     assert [w[0] for w in err.wrong_shape] == ["model.layers.0.self_attn.q_proj.weight"]
     assert [w[0] for w in err.wrong_dtype] == ["model.layers.0.input_layernorm.weight"]
     text = str(err)
     for piece in ("missing (2)", "unexpected (1)", "expected [64, 64], file has [64, 63]", "wrong dtype"):
         assert piece in text
+
+
+def test_declared_extras_are_skipped_and_others_only_warn_when_asked(tmp_path):
+    """Buffers the architecture declares (rotary frequencies, the head's copy of a tied table) load
+    silently; any other extra tensor is an error by default and a listed warning with strict=False
+    (the reference warns and skips: rustml/nlp/main/src/core/weight_map.rs:360-362)."""
+    cfg, seed = tiny_configs.config("A")
+    folder = write_random_model(str(tmp_path / "m"), cfg, seed, "float32")
+    path = os.path.join(folder, "model.safetensors")
+    f = SafetensorsFile(path)
+    tensors = {n: f.tensor(n).clone() for n in f.names()}
+    del f
+    tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()
+    tensors["model.layers.1.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    write_safetensors(path, tensors)
+    spec = spec_of(cfg)
+    w = load_weights(spec, folder, torch.float32, "cpu")
+    assert set(w) == set(spec.tensor_specs())
+    tensors["something.else"] = torch.zeros(3)
+    write_safetensors(path, tensors)
+    with pytest.raises(WeightError) as e:
+        load_weights(spec, folder, torch.float32, "cpu")
+    assert e.value.unexpected == ["something.else"]
+    with pytest.warns(UserWarning, match="something.else"):
+        w = load_weights(spec, folder, torch.float32, "cpu", strict=False)
+    assert set(w) == set(spec.tensor_specs())
+    # an untied model reads lm_head.weight, so there it is not an extra
+    untied = dict(cfg, tie_word_embeddings=False)
+    assert "lm_head.weight" in spec_of(untied).tensor_specs() and "lm_head.weight" not in spec_of(untied).ignored_tensors
+
+
+def test_random_values_depend_on_seed_name_and_index_only():
+    """Counter-based values: a prefix of a longer tensor with the same key is the shorter tensor; two
+    names or two seeds give different numbers; the numbers are N(0, std)."""
+    from rust_deeplearning_b200.parts.spec import TensorSpec
+    from rust_deeplearning_b200.weights import counter_random as cr
+    a = random_tensor(TensorSpec("x.weight", (40, 50)), 3, torch.float32)
+    again = random_tensor(TensorSpec("x.weight", (40, 50)), 3, torch.float32)
+    longer = random_tensor(TensorSpec("x.weight", (80, 50)), 3, torch.float32)
+    assert torch.equal(a, again) and torch.equal(a, longer[:40])
+    assert not torch.equal(a, random_tensor(TensorSpec("y.weight", (40, 50)), 3, torch.float32))
+    assert not torch.equal(a, random_tensor(TensorSpec("x.weight", (40, 50)), 4, torch.float32))
+    odd = cr.normal(7, cr.tensor_key(3, "x.weight"), 0.02)
+    assert np.array_equal(odd, a.reshape(-1)[:7].numpy())
+    big = cr.normal(200001, cr.tensor_key(0, "z"), 0.5).astype(np.float64)
+    assert abs(big.mean()) < 0.01 and abs(big.std() - 0.5) < 0.01
+    assert abs(np.mean(big ** 4) / big.var() ** 2 - 3.0) < 0.1          # the fourth moment of a normal
+    # bfloat16 is the float32 value rounded to nearest even
+    assert torch.equal(random_tensor(TensorSpec("x.weight", (40, 50)), 3, torch.bfloat16), a.to(torch.bfloat16))
 
 
 def test_sharded_folder(tmp_path):
