@@ -40,10 +40,13 @@ class CacheError(RuntimeError):
 
 @dataclass(frozen=True)
 class KVRequirement:
-    """Keys and values a mixer keeps per sequence.  window None: all of them."""
+    """Keys and values a mixer keeps per sequence.  window None: all of them.  value_dim: the size of
+    a value row where it differs from a key row's (a mixer with compressed or widened values);
+    None: the same as head_dim."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -114,11 +117,12 @@ class KVGroup:
         n_pages = min(total_pages, max_seqs * self.ring_pages)
         self.pool = PagePool(n_pages)
         self.pages: Dict[int, List[int]] = {}          # slot -> page list (ring entries in order of first use)
-        shape = (len(runs), n_pages, requirement.n_kv_heads, page_size, requirement.head_dim)
+        k_shape = (len(runs), n_pages, requirement.n_kv_heads, page_size, requirement.head_dim)
+        v_shape = k_shape[:-1] + (requirement.value_dim or requirement.head_dim,)
         # zero-filled: kernels that copy whole pages give rows beyond a sequence's length the weight 0,
         # which needs those rows to hold finite numbers (never-written memory may not)
-        self.k = torch.zeros(shape, dtype=dtype, device=device) if allocate else None
-        self.v = torch.zeros(shape, dtype=dtype, device=device) if allocate else None
+        self.k = torch.zeros(k_shape, dtype=dtype, device=device) if allocate else None
+        self.v = torch.zeros(v_shape, dtype=dtype, device=device) if allocate else None
 
     def pages_needed(self, slot: int, length: int) -> int:
         want = min(-(-length // self.page_size), self.ring_pages)
@@ -140,7 +144,7 @@ class KVGroup:
         return out
 
     def nbytes(self):
-        return 0 if self.k is None else 2 * self.k.numel() * self.k.element_size()
+        return 0 if self.k is None else (self.k.numel() + self.v.numel()) * self.k.element_size()
 
 
 class StateGroup:
@@ -155,7 +159,7 @@ class RunCache(NamedTuple):
     """What a mixer gets for one run of its layer in one step."""
     kv_group: Optional[int]         # index into Cache.kv_groups, None if the run keeps no keys
     k: Optional[torch.Tensor]       # [pages, kv_heads, page_size, head_dim]
-    v: Optional[torch.Tensor]
+    v: Optional[torch.Tensor]       # [pages, kv_heads, page_size, value_dim or head_dim]
     page_size: int
     ring_pages: int
     state: Optional[torch.Tensor]   # [max_seqs, *shape], indexed by slot
@@ -189,7 +193,8 @@ class Cache:
                 src = self.needs[n.reads_cache_of]
                 if not (0 <= n.reads_cache_of < e) or src.kv is None or src.reads_cache_of is not None:
                     raise CacheError(f"run {e} reads the cache of run {n.reads_cache_of}, which keeps none of its own")
-                if n.kv is not None and (n.kv.n_kv_heads, n.kv.head_dim) != (src.kv.n_kv_heads, src.kv.head_dim):
+                if n.kv is not None and (n.kv.n_kv_heads, n.kv.head_dim, n.kv.value_dim or n.kv.head_dim) != \
+                        (src.kv.n_kv_heads, src.kv.head_dim, src.kv.value_dim or src.kv.head_dim):
                     raise CacheError(f"run {e} cannot read the cache of run {n.reads_cache_of}: head layout differs")
             elif n.kv is not None:
                 kv_by_req.setdefault(n.kv, []).append(e)

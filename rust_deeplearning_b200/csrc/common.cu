@@ -20,6 +20,17 @@ extern "C" void rdl_set_wait_test(int code, long long cycles, int extra_tx_bytes
     g_rdl_wait_test_extra = code ? extra_tx_bytes : 0;
 }
 
+int rdl_sm_count() {
+    static int count[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1;
+    if (count[dev] == 0) {
+        int n = 0;
+        count[dev] = (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) ? n : 1;
+    }
+    return count[dev];
+}
+
 static thread_local char g_error[512] = "";
 
 void rdl_set_error(const char* fmt, ...) {

@@ -52,6 +52,9 @@ static inline long long rdl_wait_cycles_for(int code) {
 }
 static inline int rdl_test_extra_tx_for(int code) { return g_rdl_wait_test_code == code ? g_rdl_wait_test_extra : 0; }
 
+// Multiprocessors of the current device (asked once per device; 1 if the question fails).
+int rdl_sm_count();
+
 static inline bool rdl_valid_dtype(int d) { return d == RDL_F32 || d == RDL_BF16; }
 static inline size_t rdl_dtype_size(int d) { return d == RDL_BF16 ? 2 : 4; }
 

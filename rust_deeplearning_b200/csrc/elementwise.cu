@@ -6,6 +6,7 @@
 //   x / sqrt(mean(x^2)+eps) * (w+o) core/main/src/core/tensor/ops.rs:735-743, nn/main/src/core/rms_norm.rs:43-50
 //   gelu_tanh(g) * u                nn/main/src/core/feed_forward.rs:151-161, core/main/src/core/tensor/ops.rs:433-438
 //   cap * tanh(z / cap)             nn/main/src/core/attention.rs:419-423
+#include "activations.cuh"
 #include "api.h"
 #include "common.cuh"
 #include "launch.cuh"
@@ -276,12 +277,6 @@ extern "C" int rdl_norm_residual_norm(const void* x, int x_dtype, const int* row
 // ---------------------------------------------------------------------------------------------
 // gated activation: out[t, i] = act(gu[t, i]) * gu[t, I + i]
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ float gelu_tanh(float x) {
-    const float k = 0.7978845608028654f;  // sqrt(2/pi)
-    return 0.5f * x * (1.0f + tanhf(k * (x + 0.044715f * x * x * x)));
-}
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
-
 __global__ void gated_activation_kernel(void* __restrict__ out, const void* __restrict__ gu, int dtype, int act,
                                         long long n_rows, int inter) {
     const long long total = n_rows * inter;
@@ -291,7 +286,7 @@ __global__ void gated_activation_kernel(void* __restrict__ out, const void* __re
         const int i = (int)(idx - t * inter);
         const float g = rdl_load(gu, t * 2 * inter + i, dtype);
         const float u = rdl_load(gu, t * 2 * inter + inter + i, dtype);
-        const float a = act == RDL_ACT_GELU_TANH ? gelu_tanh(g) : silu(g);
+        const float a = rdl_activation(g, act);
         rdl_store(out, idx, dtype, a * u);
     }
 }
@@ -314,8 +309,8 @@ __global__ void gated_activation_bf16x8_kernel(__nv_bfloat16* __restrict__ out, 
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const float2 g = __bfloat1622float2(g2[i]), u = __bfloat1622float2(u2[i]);
-            const float a0 = act == RDL_ACT_GELU_TANH ? gelu_tanh(g.x) : silu(g.x);
-            const float a1 = act == RDL_ACT_GELU_TANH ? gelu_tanh(g.y) : silu(g.y);
+            const float a0 = rdl_activation(g.x, act);
+            const float a1 = rdl_activation(g.y, act);
             r2[i] = __floats2bfloat162_rn(a0 * u.x, a1 * u.y);
         }
         *reinterpret_cast<uint4*>(out + t * inter + c * 8) = res;
@@ -325,20 +320,20 @@ __global__ void gated_activation_bf16x8_kernel(__nv_bfloat16* __restrict__ out, 
 extern "C" int rdl_gated_activation(void* out, const void* gate_up, int dtype, int activation, int n_rows, int inter,
                                     void* stream) {
     RDL_REQUIRE(rdl_valid_dtype(dtype), "gated_activation: bad dtype %d", dtype);
-    RDL_REQUIRE(activation == RDL_ACT_GELU_TANH || activation == RDL_ACT_SILU, "gated_activation: unknown activation %d", activation);
+    RDL_REQUIRE(rdl_activation_known(activation), "gated_activation: unknown activation %d", activation);
     RDL_REQUIRE(n_rows >= 0 && inter > 0, "gated_activation: bad sizes");
     if (n_rows == 0) return 0;
     const long long total = (long long)n_rows * inter;
     const int threads = 256;
     if (dtype == RDL_BF16 && inter % 8 == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)gate_up & 15) == 0) {
         const long long blocks8 = (total / 8 + threads - 1) / threads;
-        gated_activation_bf16x8_kernel<<<(unsigned)(blocks8 > 148 * 32 ? 148 * 32 : blocks8), threads, 0, (cudaStream_t)stream>>>(
+        gated_activation_bf16x8_kernel<<<(unsigned)(blocks8 > rdl_sm_count() * 32 ? rdl_sm_count() * 32 : blocks8), threads, 0, (cudaStream_t)stream>>>(
             (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, activation, n_rows, inter);
         RDL_CHECK_LAUNCH("gated_activation");
         return 0;
     }
     const long long blocks = (total + threads - 1) / threads;
-    gated_activation_kernel<<<(unsigned)(blocks > 148 * 16 ? 148 * 16 : blocks), threads, 0, (cudaStream_t)stream>>>(
+    gated_activation_kernel<<<(unsigned)(blocks > rdl_sm_count() * 16 ? rdl_sm_count() * 16 : blocks), threads, 0, (cudaStream_t)stream>>>(
         out, gate_up, dtype, activation, n_rows, inter);
     RDL_CHECK_LAUNCH("gated_activation");
     return 0;
@@ -358,7 +353,7 @@ extern "C" int rdl_softcap_inplace(void* z_f32, long long total, float cap, void
     RDL_REQUIRE(total >= 0, "softcap: bad size");
     if (total == 0) return 0;
     const long long blocks = (total + 255) / 256;
-    softcap_kernel<<<(unsigned)(blocks > 148 * 16 ? 148 * 16 : blocks), 256, 0, (cudaStream_t)stream>>>((float*)z_f32, total, cap);
+    softcap_kernel<<<(unsigned)(blocks > rdl_sm_count() * 16 ? rdl_sm_count() * 16 : blocks), 256, 0, (cudaStream_t)stream>>>((float*)z_f32, total, cap);
     RDL_CHECK_LAUNCH("softcap");
     return 0;
 }
@@ -372,7 +367,7 @@ extern "C" int rdl_residual_add(void* res_f32, const void* x, int x_dtype, long 
     RDL_REQUIRE(rdl_valid_dtype(x_dtype), "residual_add: bad dtype");
     if (total <= 0) return 0;
     const long long blocks = (total + 255) / 256;
-    residual_add_kernel<<<(unsigned)(blocks > 148 * 16 ? 148 * 16 : blocks), 256, 0, (cudaStream_t)stream>>>(
+    residual_add_kernel<<<(unsigned)(blocks > rdl_sm_count() * 16 ? rdl_sm_count() * 16 : blocks), 256, 0, (cudaStream_t)stream>>>(
         (float*)res_f32, x, x_dtype, total);
     RDL_CHECK_LAUNCH("residual_add");
     return 0;

@@ -24,6 +24,7 @@
 // bytes feed two instructions), which leaves every dot product unchanged.
 #include <cstdlib>
 
+#include "activations.cuh"
 #include "api.h"
 #include "common.cuh"
 #include "launch.cuh"
@@ -38,11 +39,6 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-
-__device__ __forceinline__ float gelu_tanh(float x) {
-    return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
-}
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
 
 struct SkinnyArgs {
     const __nv_bfloat16* x;     // [M, K]
@@ -251,7 +247,7 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(SkinnyArgs a
                     if (GATED) v1 += partial[w][i][slot + 8];
                 }
                 float y = v0;
-                if (GATED) y = (a.activation == RDL_ACT_GELU_TANH ? gelu_tanh(v0) : silu(v0)) * v1;
+                if (GATED) y = rdl_activation(v0, a.activation) * v1;
                 if (a.softcap > 0.f) y = a.softcap * tanhf(y / a.softcap);
                 rdl_store(a.out, (long long)m * a.N + n, a.out_dtype, y);
             }
@@ -270,8 +266,7 @@ void launch_stream_ku(const SkinnyArgs& a, int* status, cudaStream_t st) {
     if (!opted) {
         g_launch_error = cudaFuncSetAttribute(gemm_stream_kernel<NT, GATED, KU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
         if (g_launch_error != cudaSuccess) return;
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) sms = 148;
+        sms = rdl_sm_count();
         opted = true;
     }
     // What counts is the bytes a multiprocessor has in flight: two blocks with three tiles each, or, where
@@ -301,7 +296,7 @@ extern "C" int rdl_gemm_skinny(void* out, int out_dtype, const void* x, const vo
     RDL_REQUIRE(m >= 0 && m <= 16, "gemm_skinny: %d rows, at most 16 are supported", m);
     RDL_REQUIRE(n > 0 && k > 0 && k % 8 == 0, "gemm_skinny: n=%d, k=%d; k must be a multiple of 8", n, k);
     RDL_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0, "gemm_skinny: operands must start on 16-byte boundaries");
-    RDL_REQUIRE(!gated || activation == RDL_ACT_GELU_TANH || activation == RDL_ACT_SILU, "gemm_skinny: unknown activation %d", activation);
+    RDL_REQUIRE(!gated || rdl_activation_known(activation), "gemm_skinny: unknown activation %d", activation);
     RDL_REQUIRE(softcap >= 0.f, "gemm_skinny: soft-cap must not be negative");
     if (m == 0) return 0;
     SkinnyArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, out, m, n, k, out_dtype, activation, softcap,

@@ -27,6 +27,7 @@
 #include <mutex>
 #include <tuple>
 
+#include "activations.cuh"
 #include "api.h"
 #include "common.cuh"
 
@@ -89,14 +90,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// The activation feeds a bfloat16 result (8 bits of mantissa), so the hardware tanh (relative error about
-// 2^-11) and the fast exponential are accurate enough here and keep the epilogue short.
-__device__ __forceinline__ float gelu_tanh(float x) {
-    float t;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * (x + 0.044715f * x * x * x)));
-    return 0.5f * x * (1.0f + t);
-}
-__device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.0f + __expf(fminf(-x, 80.0f))); }   // the divisor stays below 2^126
 
 struct TcArgs {
     void* out;
@@ -149,13 +142,15 @@ __device__ __forceinline__ void epilogue_piece(const TcArgs& a, uint32_t taddr, 
     if (GATED) {
         float u[32];
         tmem_ld32(taddr + up_offset, u);
-        // the choice is made once a piece, not once a value: otherwise both activations are computed for each
+        // the gated result is rounded to bfloat16: the fast forms are accurate enough.  The choice is made
+        // once a piece, not once a value: otherwise both activations are computed for each.
         if (a.activation == RDL_ACT_GELU_TANH) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]) * u[i];
+            for (int i = 0; i < 32; ++i) v[i] = rdl_activation_fast(v[i], RDL_ACT_GELU_TANH) * u[i];
         } else {
+            const int act = a.activation;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = silu(v[i]) * u[i];
+            for (int i = 0; i < 32; ++i) v[i] = rdl_activation_fast(v[i], act) * u[i];
         }
     }
     if (a.softcap > 0.f) {
@@ -563,9 +558,7 @@ int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs& a, c
     RDL_REQUIRE(tiles <= 0x3fffffffLL, "gemm_tc: %lld tiles are too many", tiles);
     static int pairs_that_fit = 0;             // one block per multiprocessor: half as many pairs
     if (!pairs_that_fit) {
-        int dev = 0, sms = 0;
-        RDL_CUDA(cudaGetDevice(&dev), "gemm_tc");
-        RDL_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "gemm_tc");
+        const int sms = rdl_sm_count();
         pairs_that_fit = sms / 2 > 0 ? sms / 2 : 1;
     }
     const int pairs = tiles < pairs_that_fit ? (int)tiles : pairs_that_fit;
@@ -583,7 +576,7 @@ extern "C" int rdl_gemm_tc(void* out, int out_dtype, const void* x, const void* 
     RDL_REQUIRE(m >= 0 && n > 0 && k > 0 && k % 8 == 0, "gemm_tc: m=%d n=%d k=%d; k must be a multiple of 8", m, n, k);
     RDL_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0,
                 "gemm_tc: operands must start on 16-byte boundaries");
-    RDL_REQUIRE(!gated || activation == RDL_ACT_GELU_TANH || activation == RDL_ACT_SILU, "gemm_tc: unknown activation %d", activation);
+    RDL_REQUIRE(!gated || rdl_activation_known(activation), "gemm_tc: unknown activation %d", activation);
     RDL_REQUIRE(softcap >= 0.f, "gemm_tc: soft-cap must not be negative");
     if (m == 0) return 0;
     // Pairs of multiprocessors on 256 x 256 tiles where a tile's products are many (the gated form, or a long
@@ -592,11 +585,11 @@ extern "C" int rdl_gemm_tc(void* out, int out_dtype, const void* x, const void* 
     // bring.  RDL_GEMM_PAIR=0 / 1 forces single blocks / pairs, for comparison.
     static const int pair_mode = getenv("RDL_GEMM_PAIR") ? atoi(getenv("RDL_GEMM_PAIR")) : -1;
     const long long tiles_of_pairs = (long long)((n + 255) / 256) * ((m + 2 * BM - 1) / (2 * BM));
-    const bool pair = m > BM && (pair_mode == 1 || (pair_mode != 0 && (gated || k >= 4096 || tiles_of_pairs >= 4 * 74)));
+    const bool pair = m > BM && (pair_mode == 1 || (pair_mode != 0 && (gated || k >= 4096 || tiles_of_pairs >= 4 * (rdl_sm_count() / 2))));
     const int bn = pair ? PAIR_BN / 2 : (gated ? 128 : 256);      // weight rows per TMA box
-    // two row tiles a block when that still fills most of the 148 multiprocessors
+    // two row tiles a block when that still fills most (four in five) of the multiprocessors
     const long long tiles2 = (long long)((n + bn - 1) / bn) * ((m + 2 * BM - 1) / (2 * BM));
-    const int mt = pair ? 1 : (tiles2 >= 120 ? 2 : 1);
+    const int mt = pair ? 1 : (tiles2 * 5 >= rdl_sm_count() * 4 ? 2 : 1);
     CUtensorMap mx, mw;
     if (int e = make_map(&mx, x, m, k, mt * BM)) return e;
     {
@@ -617,8 +610,8 @@ extern "C" int rdl_gemm_tc(void* out, int out_dtype, const void* x, const void* 
         // gets more than one tile and tensor memory has room for it
         const int out_bn = gated ? PAIR_BN / 2 : PAIR_BN;
         const long long pair_tiles = (long long)((n + out_bn - 1) / out_bn) * ((m + 2 * BM - 1) / (2 * BM));
-        if (gated) return pair_tiles > 74 ? launch_pair<true, 2>(mx, mw, a, st) : launch_pair<true, 1>(mx, mw, a, st);
-        return pair_tiles > 74 ? launch_pair<false, 2>(mx, mw, a, st) : launch_pair<false, 1>(mx, mw, a, st);
+        if (gated) return pair_tiles > rdl_sm_count() / 2 ? launch_pair<true, 2>(mx, mw, a, st) : launch_pair<true, 1>(mx, mw, a, st);
+        return pair_tiles > rdl_sm_count() / 2 ? launch_pair<false, 2>(mx, mw, a, st) : launch_pair<false, 1>(mx, mw, a, st);
     }
     if (mt == 2) return gated ? launch_tc<128, true, 2>(mx, mw, a, st) : launch_tc<256, false, 2>(mx, mw, a, st);
     return gated ? launch_tc<128, true, 1>(mx, mw, a, st) : launch_tc<256, false, 1>(mx, mw, a, st);

@@ -97,7 +97,7 @@ extern "C" int rdl_random_normal(void* out, int dtype, long long n, unsigned lon
     }
     const long long pairs = (n + 1) / 2;
     const long long blocks = (pairs + 255) / 256;
-    random_normal_kernel<<<(unsigned)(blocks > 148 * 32 ? 148 * 32 : blocks), 256, 0, (cudaStream_t)stream>>>(out, dtype, n, key, std, tb);
+    random_normal_kernel<<<(unsigned)(blocks > rdl_sm_count() * 32 ? rdl_sm_count() * 32 : blocks), 256, 0, (cudaStream_t)stream>>>(out, dtype, n, key, std, tb);
     RDL_CHECK_LAUNCH("random_normal");
     return 0;
 }

@@ -18,14 +18,14 @@ import torch
 
 from ..kernels.ops import AttentionBatch
 
-QUERY_TILE = 64   # rows per query tile of the prefill attention kernel
-
 
 class BatchLayout:
     """Offsets of the fields inside the int32 buffer for given (padded) sizes."""
 
-    def __init__(self, n_tokens: int, n_seqs: int, n_want: int, n_tiles: int, table_widths: Sequence[int]):
+    def __init__(self, n_tokens: int, n_seqs: int, n_want: int, n_tiles: int, table_widths: Sequence[int],
+                 tile_rows: int = 0):
         self.n_tokens, self.n_seqs, self.n_want, self.n_tiles = n_tokens, n_seqs, n_want, n_tiles
+        self.tile_rows = tile_rows       # rows of a query tile, as the model's mixers ask for them (0: none)
         self.table_widths = list(table_widths)
         self.fields = {}
         off = 0
@@ -81,6 +81,9 @@ class StepBatch:
     device: torch.device
     scratch: Dict[str, torch.Tensor] = field(default_factory=dict)   # reusable work buffers, by name
     new_kv: Dict[int, tuple] = field(default_factory=dict)   # run -> (packed rows, key column, value column) of this step
+    # run -> the cache write it has put off until the runs that read its keys and values are through (a ring
+    # group's rows of earlier steps are still needed by this step's readers); the model calls them
+    deferred_writes: Dict[int, object] = field(default_factory=dict)
     cache_owner_of: Dict[int, int] = field(default_factory=dict)     # run -> run whose keys and values it reads
     shared_runs: frozenset = frozenset()                             # runs whose keys and values a later run reads
     status: Optional[torch.Tensor] = None                            # int32 flag kernels set when they give up a wait
@@ -132,8 +135,8 @@ def fill_batch(host: np.ndarray, layout: BatchLayout, *, tokens: Sequence[Sequen
                 raise ValueError(f"sequence {i}: wanted place {w} is outside its {n} tokens")
             want_rows[n_want] = row + w
             n_want += 1
-        if layout.n_tiles:
-            for q0 in range(0, n, QUERY_TILE):
+        if layout.n_tiles and layout.tile_rows:
+            for q0 in range(0, n, layout.tile_rows):
                 tile_seq[n_tiles] = i
                 tile_q0[n_tiles] = q0
                 n_tiles += 1
@@ -147,8 +150,9 @@ def fill_batch(host: np.ndarray, layout: BatchLayout, *, tokens: Sequence[Sequen
     return row, n_want, n_tiles
 
 
-def count_tiles(lengths: Sequence[int]) -> int:
-    return sum(-(-n // QUERY_TILE) for n in lengths)
+def count_tiles(lengths: Sequence[int], tile_rows: int) -> int:
+    """Query tiles of `tile_rows` rows that sequences of these lengths are cut into (a tile never spans two sequences)."""
+    return sum(-(-n // tile_rows) for n in lengths) if tile_rows else 0
 
 
 def batch_from_buffer(dev: torch.Tensor, layout: BatchLayout, *, real_tokens, real_seqs, n_want, n_tiles,

@@ -144,7 +144,8 @@ class Engine:
             logits = self._graph_step(slots, tokens, past, want, tables, widths, max(totals), fed)
         else:
             n_want = sum(len(w) for w in want)
-            layout = BatchLayout(sum(lens), n, max(n_want, 1), count_tiles(lens), widths)
+            tile_rows = self.model.query_tile_rows
+            layout = BatchLayout(sum(lens), n, max(n_want, 1), count_tiles(lens, tile_rows), widths, tile_rows)
             host = self._host_buffer(layout.size)
             real_tokens, n_want, n_tiles = fill_batch(host.numpy()[:layout.size], layout, tokens=tokens, past=past,
                                                       slots=slots, want=want, tables=tables,

@@ -65,9 +65,25 @@ def _build_dirs():
     yield os.path.join(tempfile.gettempdir(), f"rust_deeplearning_b200_build_{os.getuid()}")
 
 
+def _trusted(path):
+    """Loading a library runs its code in this process.  The folder inside the package is trusted as the
+    package's own Python files are.  The fallback folder lies under the shared temporary directory, where
+    another user could have put a folder of that name first: it, and a library in it, must belong to this
+    user and be writable by nobody else."""
+    if os.path.commonpath([os.path.abspath(path), _PKG]) == _PKG:
+        return True
+    try:
+        st = os.stat(path)
+    except OSError:
+        return False
+    return st.st_uid == os.getuid() and not (st.st_mode & 0o022)
+
+
 def _writable_dir(path):
     try:
-        os.makedirs(path, exist_ok=True)
+        os.makedirs(path, mode=0o700, exist_ok=True)
+        if not _trusted(path):
+            return False
         probe = os.path.join(path, f".probe_{os.getpid()}")
         with open(probe, "w"):
             pass
@@ -128,7 +144,7 @@ def build(force: bool = False) -> str:
     stamp = _fingerprint()
     for d in _build_dirs():
         lib, st = os.path.join(d, LIB_NAME), os.path.join(d, "stamp")
-        if not force and os.path.isfile(lib) and os.path.isfile(st):
+        if not force and os.path.isfile(lib) and os.path.isfile(st) and _trusted(d) and _trusted(lib):
             with open(st) as f:
                 if f.read().strip() == stamp:
                     return lib

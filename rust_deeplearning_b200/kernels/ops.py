@@ -8,6 +8,7 @@ raise.  Parts call them as `ops.<name>` (attribute lookup at call time).
 from __future__ import annotations
 
 import ctypes
+import functools
 import os
 from typing import NamedTuple, Optional, Tuple
 
@@ -16,6 +17,8 @@ import torch
 from . import library
 from .library import AttentionArgs, KernelError, SamplingArgs
 
+# Names of gated activations -> the codes of `csrc/api.h` (RDL_ACT_*).  The functions themselves are in
+# `csrc/activations.cuh`, the one place every kernel with a gated epilogue takes them from.
 ACTIVATIONS = {"gelu_pytorch_tanh": 0, "gelu_tanh": 0, "silu": 1}
 
 # The status word of the step that is running: every kernel that can report a fault (a token id
@@ -303,6 +306,9 @@ def rope_cache(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, 
     return qkv
 
 
+PREFILL_QUERY_TILE = 64    # query rows of a tile in the lists the prefill attention kernels take
+
+
 class AttentionBatch(NamedTuple):
     """The step's sequences as the attention kernels see them (device int32 tensors)."""
     n_tokens: int
@@ -312,7 +318,7 @@ class AttentionBatch(NamedTuple):
     seq_start: torch.Tensor    # [seqs + 1]
     seq_past: torch.Tensor     # [seqs]
     seq_cached: torch.Tensor   # [seqs] keys below this position are read from the cache
-    tile_seq: Optional[torch.Tensor] = None   # prefill: 64-row query tiles
+    tile_seq: Optional[torch.Tensor] = None   # prefill: query tiles of PREFILL_QUERY_TILE rows
     tile_q0: Optional[torch.Tensor] = None
     n_tiles: int = 0
     max_keys: int = 0          # decode: longest key run any token of the batch reads (window applied)
@@ -339,13 +345,18 @@ def _attention_args(q, q_stride, k_new, v_new, kv_stride, out, b: AttentionBatch
     return a
 
 
-def choose_keys_per_split(n_tokens: int, n_kv_heads: int, max_keys: int, page_size: int) -> int:
+@functools.lru_cache(maxsize=None)
+def sm_count(device_index: int) -> int:
+    return torch.cuda.get_device_properties(device_index).multi_processor_count
+
+
+def choose_keys_per_split(n_tokens: int, n_kv_heads: int, max_keys: int, page_size: int, sms: int = 148) -> int:
     """Keys per block of the decode kernel: runs of four pages (a block then streams its pages one after
     the other, and fewer partial results are merged), shorter ones while that leaves the GPU with
-    fewer than about one and a half blocks per multiprocessor."""
+    fewer than about one and a half blocks per multiprocessor (`sms` of them)."""
     blocks = lambda pages: n_tokens * n_kv_heads * ((max_keys + pages * page_size - 1) // (pages * page_size))
     for pages in (4, 2):
-        if blocks(pages) >= 222:
+        if 2 * blocks(pages) >= 3 * sms:
             return pages * page_size
     return page_size
 
@@ -407,7 +418,8 @@ def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n
             library.check(lib.rdl_attention_prefill(ctypes.byref(a), _stream(q)))
     elif kind == "decode":
         _need(pages is not None, "attention: decode reads the cache")
-        ks = keys_per_split or choose_keys_per_split(b.n_tokens, n_kv_heads, b.max_keys, pages.page_size)
+        ks = keys_per_split or choose_keys_per_split(b.n_tokens, n_kv_heads, b.max_keys, pages.page_size,
+                                                     sm_count(q.device.index or 0))
         a.keys_per_split = ks
         # a run of max_keys positions can straddle one more split than its length suggests
         a.max_splits = (max(b.max_keys, 1) + ks - 1) // ks + 1

@@ -24,10 +24,15 @@ from .spec import PartSpec
 
 
 class Attention:
+    # the step's batch description lists its prompts cut into tiles of this many query rows (the prefill kernels' tiling)
+    query_tile_rows = ops.PREFILL_QUERY_TILE
+
     def __init__(self, *, hidden_size, n_heads, n_kv_heads, head_dim, score_scale, softcap, window, position,
                  wq, wk, wv, wo):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads cannot share {n_kv_heads} key/value heads")
+        if wv.shape[0] != wk.shape[0]:
+            raise ValueError("this attention's kernels take key and value rows of one size")
         self.hidden_size, self.n_heads, self.n_kv_heads, self.head_dim = hidden_size, n_heads, n_kv_heads, head_dim
         self.score_scale, self.softcap, self.window = float(score_scale), softcap, window
         self.position = position
@@ -124,11 +129,17 @@ class Attention:
                 kind = "plain"
             ctx = ops.attention(qkv, ab, pages, new_kv=(qkv, self.q_width, self.q_width + self.kv_width), kind=kind,
                                 status=batch.status, **common)
-            if not write_first:
-                ops.rope_cache(qkv, nh, nkv, hd, tok_seq=batch.tok_seq, tok_pos=batch.tok_pos, pages=pages,
-                               seq_end=batch.seq_end)
             if run in batch.shared_runs:
                 batch.new_kv[run] = (qkv, self.q_width, self.q_width + self.kv_width)
+            if not write_first and pages is not None:
+                def write(qkv=qkv, pages=pages):
+                    ops.rope_cache(qkv, nh, nkv, hd, tok_seq=batch.tok_seq, tok_pos=batch.tok_pos, pages=pages,
+                                   seq_end=batch.seq_end)
+                if run in batch.shared_runs and cache.is_ring and batch.has_past:
+                    # later runs of this step read this run's rows of earlier steps from the ring: write after them
+                    batch.deferred_writes[run] = write
+                else:
+                    write()
         return ops.linear(ctx, self.w_o)
 
 

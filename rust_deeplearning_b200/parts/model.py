@@ -106,8 +106,20 @@ class Model:
         self.cache_owner_of = {e: (s.reads_cache_of if s.reads_cache_of is not None else e)
                                for e, s in enumerate(self.schedule)}
         self.shared_runs = frozenset(s.reads_cache_of for s in self.schedule if s.reads_cache_of is not None)
+        # the last run that reads each shared run's keys and values: a cache write that the owner puts off
+        # (a ring whose rows this step's readers still need) is done after it
+        self.last_reader = {}
+        for e, s in enumerate(self.schedule):
+            if s.reads_cache_of is not None:
+                self.last_reader[s.reads_cache_of] = e
         self.vocab_size, self.hidden_size = spec.vocab_size, spec.hidden_size
         self.max_positions = spec.max_positions
+        # Mixers may ask the step for its many-token sequences cut into query tiles of so many rows (a kernel's
+        # tiling); the step's batch description then carries the tile lists.  One size per model.
+        sizes = {getattr(layer.mixer, "query_tile_rows", 0) or 0 for layer in self.layers if hasattr(layer, "mixer")} - {0}
+        if len(sizes) > 1:
+            raise ValueError(f"the model's mixers ask for query tiles of different sizes: {sorted(sizes)}")
+        self.query_tile_rows = sizes.pop() if sizes else 0
 
     def needs(self) -> List[RunNeeds]:
         """What each schedule entry needs of the cache."""
@@ -122,8 +134,14 @@ class Model:
         batch.cache_owner_of, batch.shared_runs = self.cache_owner_of, self.shared_runs
         batch.new_kv.clear()
         stream = ResidualStream(self.embedding.forward(batch.tokens))
+        batch.deferred_writes.clear()
         for run, entry in enumerate(self.schedule):
             self.layers[entry.layer].forward(stream, batch, cache.run_cache(run), run)
+            for owner in [o for o in batch.deferred_writes if self.last_reader.get(o, o) <= run]:
+                batch.deferred_writes.pop(owner)()
+        for write in batch.deferred_writes.values():
+            write()
+        batch.deferred_writes.clear()
         batch.new_kv.clear()
         if batch.n_want == 0:
             stream.value()

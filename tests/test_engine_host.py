@@ -113,3 +113,34 @@ def test_wanted_places_and_errors(tmp_path, monkeypatch):
     with pytest.raises(StepError):
         engine.step([s0], [[]])
     assert engine.length(s0) == 7                 # failed steps changed nothing
+
+
+def test_a_run_that_reads_another_runs_ring_sees_the_rows_of_earlier_steps(tmp_path, monkeypatch):
+    """Schedule: layer 0 with a window of 8 keeps a ring of 3 pages of 4 rows; layer 1 reads layer 0's keys and
+    values.  A portion of 10 tokens on a prefix of 9 lands on ring rows that the portion's early queries still
+    read in layer 1, so layer 0's write has to wait until layer 1 has run.  Whole, in portions and token by
+    token must agree (the whole prompt reads no ring at all)."""
+    import dataclasses
+    from rust_deeplearning_b200.parts.spec import ScheduleEntry
+    kernel_refs.install(monkeypatch)
+    cfg, seed = tiny_configs.config("A")
+    cfg["layer_types"] = ["sliding_attention", "sliding_attention"]
+    folder = str(tmp_path / "shared")
+    write_random_model(folder, cfg, seed, "float32")
+    arch = architecture_for(cfg)
+    spec = arch.build_spec(arch.parse_config(cfg))
+    spec = dataclasses.replace(spec, schedule=(ScheduleEntry(0), ScheduleEntry(1, reads_cache_of=0)))
+    model = Model(spec, load_weights(spec, folder, torch.float32, "cpu"), torch.float32, "cpu")
+    engine = Engine(model, max_tokens=4096, page_size=4, use_graphs=False)
+    assert engine.cache.kv_groups[0].is_ring and engine.cache.kv_groups[0].ring_pages == 3
+    rng = np.random.default_rng(9)
+    ids = prompt(rng, 40, cfg["vocab_size"])
+    slot = engine.new_sequence()
+    whole = engine.step([slot], [ids], "all").double().numpy()
+    engine.release(slot)
+    slot = engine.new_sequence()
+    parts = [engine.step([slot], [ids[a:b]], "all") for a, b in ((0, 9), (9, 19), (19, 20), (20, 40))]
+    close(torch.cat(parts), whole)
+    engine.release(slot)
+    slot = engine.new_sequence()
+    close(torch.cat([engine.step([slot], [[t]], "all") for t in ids]), whole)

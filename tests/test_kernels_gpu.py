@@ -368,24 +368,88 @@ def test_decode_attention_rotates_and_writes_the_new_rows(shape, rotary):
         assert_close(got_pages.k, ref_pages.k, torch.bfloat16, rel=1.0, what="key cache")
 
 
-def test_attention_finds_one_far_key():
-    """One key among a thousand is made to dominate: the output must be that key's value row.
-    Shows a wrong page, a missed split or a window edge that random data would average away."""
-    for window, far in ((None, 3), (400, 1001 - 400), (400, 1001 - 401)):
-        c = Case(past=[1000], new=[1], n_heads=2, n_kv_heads=1, head_dim=64, page_size=64, window=window,
-                 dtype=torch.bfloat16, seed=50)
+@pytest.mark.parametrize("sizes", [dict(past=1000, window=400, n_heads=2, n_kv_heads=1, head_dim=64),
+                                   dict(past=6000, window=4096, n_heads=8, n_kv_heads=4, head_dim=256),
+                                   dict(past=4500, window=4096, n_heads=32, n_kv_heads=16, head_dim=128)])
+def test_attention_finds_one_far_key(sizes):
+    """One key among thousands is made to dominate: the output must be that key's value row.
+    Shows a wrong page, a missed split or a window edge that random data would average away.  The larger
+    cases have the real window of 4,096 on a ring of 65 pages that has wrapped."""
+    past, W = sizes["past"], sizes["window"]
+    nh, nkv, hd = sizes["n_heads"], sizes["n_kv_heads"], sizes["head_dim"]
+    G = nh // nkv
+    for window, far in ((None, 3), (W, past + 1 - W), (W, past - W), (W, past - 1), (W, past + 1 - W + 64)):
+        c = Case(past=[past], new=[1], n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_size=64, window=window,
+                 dtype=torch.bfloat16, seed=50, max_context=8192)
         b = c.batch("all")
         page, r = ref._cache_index(c.pages.tables[0], far, c.page_size, c.ring_pages)
-        c.qkv[0, :128] = 0.25
-        c.k[page, 0, r] = 8.0                       # score 128 against about 0 +- 4 elsewhere
-        want = ref.attention(c.qkv, b, c.pages, **c.kw(scale=1.0))
-        visible = window is None or 1000 - far < window
-        target = ref.cache_load(c.v[page, 0, r], r).double().cpu()
-        hit = (want[0, :64].double().cpu() - target).abs().max().item() < 1e-2
-        assert hit == visible
+        g = nkv - 1                                 # the last kv head: its query heads are the last G
+        c.qkv[0, (nh - G) * hd:nh * hd] = 0.25 * (64 / hd) ** 0.5
+        c.k[page, g, r] = 8.0 * (64 / hd) ** 0.5    # score 128 against about 0 +- 4 elsewhere
+        # the loops of the reference take minutes over thousands of keys and dozens of heads: there the plain
+        # kernel (itself compared with the reference above and in the small case here) stands in
+        want = (ref.attention(c.qkv, b, c.pages, **c.kw(scale=1.0)) if past <= 2000 else
+                ops.attention(c.qkv, b, c.pages, kind="plain", **c.kw(scale=1.0)))
+        visible = window is None or past - far < window
+        target = ref.cache_load(c.v[page, g, r], r).double().cpu()
+        hit = (want[0, (nh - 1) * hd:].double().cpu() - target).abs().max().item() < 1e-2
+        assert hit == visible, (window, far)
         for kind in ("decode", "plain"):
             got = ops.attention(c.qkv, b, c.pages, kind=kind, **c.kw(scale=1.0))
-            assert_close(got, want, torch.bfloat16, rel=6.0, what=f"{kind} window={window}")
+            assert_close(got, want, torch.bfloat16, rel=6.0, what=f"{kind} window={window} key={far}")
+
+
+@pytest.mark.parametrize("kind", ["prefill", "prefill_tc", "plain"])
+@pytest.mark.parametrize("window", [None, 200])
+def test_prefill_attention_finds_one_key(kind, window):
+    """The many-token kernels with one key made to dominate one query's scores: at the window's inner and
+    outer edge, and in the first and the last key tile that a query tile of 128 rows reads.  A kernel
+    that is off by one at the window's edge, skips a key tile too many or reads a tile twice gives another
+    row than the reference; random data would average that away."""
+    n = 700
+    hd, nh = 64, 2
+    for query in (127, 128, 390, 511, 699):
+        if window is None:
+            keys = [0, 63, 64, query - 1, query]
+        else:
+            lo = max(query - window + 1, 0)
+            keys = sorted({max(lo - 1, 0), lo, lo + 1, min((lo // 64 + 1) * 64, query), query - 1, query})
+        for key in keys:
+            c = Case(past=[0], new=[n], n_heads=nh, n_kv_heads=1, head_dim=hd, page_size=64, window=window,
+                     dtype=torch.bfloat16, seed=52)
+            q_cols, k_col = nh * hd, nh * hd
+            c.qkv[query, :q_cols] = 0.25
+            c.qkv[key, k_col:k_col + hd] = 8.0          # score 128 against about 0 +- 4 elsewhere
+            b = c.batch("past")
+            want = ref.attention(c.qkv, b, c.pages, new_kv=c.new_kv(), **c.kw(scale=1.0))
+            visible = key <= query and (window is None or query - key < window)
+            target = c.qkv[key, k_col + hd:k_col + 2 * hd].double().cpu()
+            hit = (want[query, :hd].double().cpu() - target).abs().max().item() < 1e-2
+            assert hit == visible, (query, key, window)
+            got = ops.attention(c.qkv, b, c.pages, new_kv=c.new_kv(), kind=kind, **c.kw(scale=1.0))
+            assert_close(got, want, torch.bfloat16, rel=6.0, what=f"{kind} window={window} query={query} key={key}")
+
+
+def test_prefill_attention_on_a_cached_prefix_finds_one_key():
+    """The same with the key in the cache (a portion of a prompt on top of earlier steps): the key is put on the
+    far side and on the near side of the window's edge, on a ring of pages that has wrapped."""
+    window = 100
+    for past, key in ((500, 500 + 20 - 99), (500, 500 + 20 - 100), (500, 470), (130, 60)):
+        c = Case(past=[past], new=[70], n_heads=2, n_kv_heads=1, head_dim=64, page_size=16, window=window,
+                 dtype=torch.bfloat16, seed=53)
+        query = 20                                       # row of the portion; its position is past + 20
+        page, r = ref._cache_index(c.pages.tables[0], key, c.page_size, c.ring_pages)
+        c.qkv[query, :128] = 0.25
+        c.k[page, 0, r] = 8.0
+        b = c.batch("past")
+        want = ref.attention(c.qkv, b, c.pages, new_kv=c.new_kv(), **c.kw(scale=1.0))
+        visible = past + query - key < window
+        target = ref.cache_load(c.v[page, 0, r], r).double().cpu()
+        hit = (want[query, :64].double().cpu() - target).abs().max().item() < 1e-2
+        assert hit == visible, (past, key)
+        for kind in ("prefill", "plain"):
+            got = ops.attention(c.qkv, b, c.pages, new_kv=c.new_kv(), kind=kind, **c.kw(scale=1.0))
+            assert_close(got, want, torch.bfloat16, rel=6.0, what=f"{kind} past={past} key={key}")
 
 
 # ------------------------------------------------------------------------------------------

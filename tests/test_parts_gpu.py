@@ -10,6 +10,7 @@ import torch
 import plain_gemma2 as plain
 from rust_deeplearning_b200.cache.cache import Cache, RunNeeds
 from rust_deeplearning_b200.engine.batch import BatchLayout, batch_from_buffer, count_tiles, fill_batch
+from rust_deeplearning_b200.kernels import ops
 from rust_deeplearning_b200.parts.registry import BuildContext, build_part
 from rust_deeplearning_b200.parts.norm import ResidualStream, RMSNorm
 from rust_deeplearning_b200.parts.spec import LayerSpec, PartSpec, TensorSpec
@@ -47,7 +48,7 @@ def make_batch(cache, slots, tokens_per_seq, want="all"):
     tables = [g.table_rows(slots) for g in cache.kv_groups]
     widths = [g.table_width for g in cache.kv_groups]
     wants = [list(range(l)) for l in lens]
-    layout = BatchLayout(sum(lens), len(slots), sum(lens), count_tiles(lens), widths)
+    layout = BatchLayout(sum(lens), len(slots), sum(lens), count_tiles(lens, ops.PREFILL_QUERY_TILE), widths, ops.PREFILL_QUERY_TILE)
     host = np.zeros(layout.size, dtype=np.int32)
     real, n_want, n_tiles = fill_batch(host, layout, tokens=tokens_per_seq, past=past, slots=slots, want=wants, tables=tables)
     dev = torch.from_numpy(host).to(DEV)

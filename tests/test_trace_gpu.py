@@ -121,3 +121,23 @@ def test_replay_unequal_batches_one_after_another(tmp_path, name, dtype):
     # the largest batch holds 128 + 64 + 128 positions (rounded up to 64): the cache fits one batch only
     out = replay(name, dtype, steps, max_tokens=320, out_dir=str(tmp_path))
     check(name, dtype, steps, out, seqs)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_replay_portions_and_mixed_steps(tmp_path, name, dtype):
+    """Steps the generation loop never forms but the step function takes: a request fed in portions of many
+    tokens (7 / 23 / 15, then 70 / 60 for another) and steps that mix a portion or a whole prompt with
+    single tokens of requests under way."""
+    V = tiny_configs.config(name)[0]["vocab_size"]
+    seqs = {"p": mh.prompt(600, 45, V), "q": mh.prompt(601, 130, V), "r": mh.prompt(602, 12, V), "s": mh.prompt(603, 20, V)}
+    all_of = lambda rid, a, b: {"id": rid, "tokens": seqs[rid][a:b], "want": list(range(b - a))}
+    steps = [
+        {"step": 0, "entries": [all_of("p", 0, 7)], "end": []},
+        {"step": 1, "entries": [all_of("p", 7, 30), all_of("q", 0, 70)], "end": []},               # a portion beside a prompt
+        {"step": 2, "entries": [all_of("p", 30, 45), all_of("q", 70, 130), all_of("r", 0, 11)], "end": ["p", "q"]},
+        {"step": 3, "entries": [all_of("r", 11, 12), all_of("s", 0, 19)], "end": ["r"]},           # one token beside a prompt
+        {"step": 4, "entries": [all_of("s", 19, 20)], "end": ["s"]},
+    ]
+    out = replay(name, dtype, steps, max_tokens=384, out_dir=str(tmp_path))
+    check(name, dtype, steps, out, seqs)

@@ -10,6 +10,7 @@ import ctypes
 import pytest
 import torch
 
+import kernel_refs as ref
 from rust_deeplearning_b200.kernels import library, ops
 from test_kernels_gpu import Case, assert_close
 
@@ -34,22 +35,34 @@ def static_decode(case, batch, keys_per_split, softcap):
     return status, out
 
 
-@pytest.mark.parametrize("shape", [
+SHAPES = [
     dict(past=[0, 63, 64, 700], n_heads=8, n_kv_heads=4, head_dim=256, page_size=64, window=None),
     dict(past=[2000, 17, 130], n_heads=4, n_kv_heads=2, head_dim=128, page_size=64, window=100),
-])
-def test_static_scratch_entry_point_matches_the_ordinary_one(shape):
-    shape = dict(shape)
-    past = shape.pop("past")
-    case = Case(past=past, new=[1] * len(past), dtype=torch.bfloat16, seed=70, **shape)
-    batch = case.batch("all")
-    for call, softcap in enumerate((None, 7.0)):          # two calls in a row on the shared array
+]
+
+
+def test_static_scratch_entry_point_matches_the_ordinary_one_and_the_plain_reference():
+    """Calls in a row on the one shared array, alternating between two shapes (other token counts, head
+    counts and numbers of runs), so that what one call leaves in the array - counters, partial sums of
+    runs the next call does not have - would show in the next call's result.  Every result is compared
+    with the ordinary entry point and with the plain reference of the operation."""
+    cases = []
+    for k, shape in enumerate(SHAPES):
+        shape = dict(shape)
+        past = shape.pop("past")
+        case = Case(past=past, new=[1] * len(past), dtype=torch.bfloat16, seed=70 + k, **shape)
+        cases.append((case, case.batch("all")))
+    for call, (which, softcap) in enumerate(((0, None), (1, 7.0), (0, 7.0), (1, None), (1, None))):
+        case, batch = cases[which]
         want = ops.attention(case.qkv, batch, case.pages, kind="decode", keys_per_split=case.page_size,
                              **case.kw(softcap=softcap))
+        plain = ref.attention(case.qkv, batch, case.pages, **case.kw(softcap=softcap))
         status, got = static_decode(case, batch, case.page_size, softcap)
         assert status == 0, library.load().rdl_last_error().decode()
         torch.cuda.synchronize()
-        assert_close(got, want, torch.bfloat16, rel=6.0, what=f"call {call}")
+        assert not torch.isnan(got.float()).any(), f"call {call}: rows left unwritten"
+        assert_close(got, want, torch.bfloat16, rel=6.0, what=f"call {call} against the ordinary entry point")
+        assert_close(got, plain, torch.bfloat16, rel=6.0, what=f"call {call} against the plain reference")
 
 
 def test_static_scratch_entry_point_refuses_what_does_not_fit():

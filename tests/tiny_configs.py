@@ -1,5 +1,7 @@
 """Tiny Gemma 2 configurations for the tests.  A and B differ in every size and option;
-C switches the options off (no window, no soft-caps) and has sizes that are no power of two."""
+C switches the options off (no window, no soft-caps) and has sizes that are no power of two;
+D has a head size of 64, the smallest the tensor-memory prefill attention and the decode kernel's
+fixed-size form take, so that those run inside a whole model."""
 import copy
 
 TINY_A = {
@@ -32,7 +34,17 @@ TINY_C = {
     "eos_token_id": 3,
 }
 
-CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2)}
+TINY_D = {
+    "architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2",
+    "num_hidden_layers": 2, "hidden_size": 136, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "head_dim": 64, "intermediate_size": 200, "vocab_size": 301, "rms_norm_eps": 1e-6,
+    "rope_theta": 10000.0, "sliding_window": 100, "query_pre_attn_scalar": 50,
+    "attn_logit_softcapping": 30.0, "final_logit_softcapping": 20.0, "max_position_embeddings": 1024,
+    "hidden_activation": "gelu_pytorch_tanh", "tie_word_embeddings": True,
+    "bos_token_id": 2, "eos_token_id": 1,
+}
+
+CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3)}
 
 
 def config(name):
