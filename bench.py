@@ -34,6 +34,11 @@ GEMMA2_2B = {
     "attn_logit_softcapping": 50.0, "final_logit_softcapping": 30.0, "max_position_embeddings": 8192,
     "hidden_activation": "gelu_pytorch_tanh", "tie_word_embeddings": True, "bos_token_id": 2, "eos_token_id": 1,
 }
+# BASELINE.json configs[3] and [4]: the 9B and 27B shapes
+GEMMA2_9B = dict(GEMMA2_2B, num_hidden_layers=42, hidden_size=3584, num_attention_heads=16, num_key_value_heads=8,
+                 head_dim=256, intermediate_size=14336, query_pre_attn_scalar=256)
+GEMMA2_27B = dict(GEMMA2_2B, num_hidden_layers=46, hidden_size=4608, num_attention_heads=32, num_key_value_heads=16,
+                  head_dim=128, intermediate_size=36864, query_pre_attn_scalar=144)
 CONTEXT = 8192
 PROMPT = 2048
 NEW_TOKENS = 128
@@ -132,10 +137,10 @@ def prefill_flops(cfg, layers, T):
     return linear + attn + 2 * V * H      # logits at the last row only
 
 
-def decode_run(engine, batch, steps, warmup, vocab, torch, rng):
-    """Prefill `batch` prompts of PROMPT tokens, then time `steps` single-token steps on the device."""
+def decode_run(engine, batch, steps, warmup, vocab, torch, rng, prompt_len=PROMPT):
+    """Prefill `batch` prompts of `prompt_len` tokens, then time `steps` single-token steps on the device."""
     slots = [engine.new_sequence() for _ in range(batch)]
-    prompts = [[int(v) for v in rng.integers(0, vocab, size=PROMPT)] for _ in range(batch)]
+    prompts = [[int(v) for v in rng.integers(0, vocab, size=prompt_len)] for _ in range(batch)]
     engine.step(slots, prompts, [[] for _ in slots])
     feed = [[[int(v)] for v in rng.integers(0, vocab, size=batch)] for _ in range(steps + warmup)]
     from rust_deeplearning_b200.kernels import library
@@ -158,6 +163,72 @@ def decode_run(engine, batch, steps, warmup, vocab, torch, rng):
     return ms, launches, mid
 
 
+def spread(lo, hi, n):
+    """n prompt lengths from lo to hi in equal steps."""
+    return [lo + (hi - lo) * i // (n - 1) for i in range(n)]
+
+
+def workload(cfg, prompt_lens, new_tokens, pk, torch, rng, seed=0):
+    """One of the larger shapes end to end on the engine: all prompts in one step (device-timed), then
+    `new_tokens` single-token steps; the steps around the middle of the run are timed on the device.
+    Returns a flat dict of figures."""
+    import gc
+    from rust_deeplearning_b200 import Engine, random_model
+    from rust_deeplearning_b200.config.base import architecture_for
+    torch.cuda.empty_cache()
+    torch.cuda.reset_peak_memory_stats()
+    model = random_model(cfg, seed=seed, dtype="bfloat16", device="cuda:0")
+    torch.cuda.synchronize()
+    load_peak = torch.cuda.max_memory_allocated()
+    arch = architecture_for(cfg)
+    wbytes = weight_bytes(arch.build_spec(arch.parse_config(cfg)))
+    V, L = cfg["vocab_size"], cfg["num_hidden_layers"]
+    longest = max(prompt_lens) + new_tokens
+    per_seq = [-(-(n + new_tokens) // 64) * 64 for n in prompt_lens]
+    engine = Engine(model, max_tokens=sum(per_seq), max_seqs=len(prompt_lens), max_context=-(-longest // 64) * 64)
+    prompts = [[int(v) for v in rng.integers(0, V, size=n)] for n in prompt_lens]
+    slots = [engine.new_sequence() for _ in prompts]
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    p0, p1 = ev(), ev()
+    torch.cuda.synchronize()
+    p0.record()
+    engine.step(slots, prompts, "last")
+    p1.record()
+    torch.cuda.synchronize()
+    prefill_ms = p0.elapsed_time(p1)
+    first = max(3, new_tokens // 2 - 10)             # the timed steps lie around the middle of the run
+    timed = min(20, new_tokens - 1 - first)
+    feed = rng.integers(0, V, size=(new_tokens - 1, len(prompts)))
+    t0, t1 = ev(), ev()
+    for k in range(new_tokens - 1):
+        if k == first:
+            t0.record()
+        if k == first + timed:
+            t1.record()
+        engine.step(slots, [[int(v)] for v in feed[k]], "last")
+    if first + timed >= new_tokens - 1:
+        t1.record()
+    torch.cuda.synchronize()
+    engine.check_status()
+    ms = t0.elapsed_time(t1) / timed
+    mid = [n + first + timed // 2 for n in prompt_lens]
+    step_bytes = wbytes + cache_bytes_read(cfg, L, mid)
+    out = {"layers": L, "prompts": f"{len(prompt_lens)} of {min(prompt_lens)}..{max(prompt_lens)} tokens", "new_tokens": new_tokens,
+           "decode_tok_s": round(len(prompts) / (ms * 1e-3), 1), "decode_ms_per_step": round(ms, 3),
+           "decode_step_gb": round(step_bytes / 1e9, 2),
+           "decode_hbm_frac": round(step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4),
+           "prefill_tokens": sum(prompt_lens), "prefill_ms": round(prefill_ms, 1),
+           "prefill_tok_s": round(sum(prompt_lens) / (prefill_ms * 1e-3), 1),
+           "weights_gb": round(wbytes / 1e9, 2), "load_peak_gb": round(load_peak / 1e9, 2),
+           "cache_gb": round(engine.cache.nbytes() / 1e9, 2)}
+    for s in slots:
+        engine.release(s)
+    del engine, model
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -168,6 +239,8 @@ def main():
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one small case (for profiling) and print a short line instead of the full record")
     ap.add_argument("--batch", type=int, default=8, help="batch of the --only decode case")
+    ap.add_argument("--context", type=int, default=PROMPT, help="prompt length of the --only decode case")
+    ap.add_argument("--no-large", action="store_true", help="leave out the 9B and 27B shapes and the long contexts")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -206,8 +279,8 @@ def main():
         # one case, few steps: what a profiler is pointed at
         engine = Engine(model, max_tokens=args.batch * CONTEXT, max_seqs=args.batch, max_context=CONTEXT)
         if args.only == "decode":
-            ms, launches, _ = decode_run(engine, args.batch, args.steps, args.warmup, V, torch, rng)
-            print(json.dumps({"case": "decode", "batch": args.batch, "layers": layers, "ms_per_step": round(ms, 4),
+            ms, launches, _ = decode_run(engine, args.batch, args.steps, args.warmup, V, torch, rng, args.context)
+            print(json.dumps({"case": "decode", "batch": args.batch, "context": args.context, "layers": layers, "ms_per_step": round(ms, 4),
                               "tokens_per_s": round(args.batch / (ms * 1e-3), 1), "launches": launches}))
         else:
             prompt = [int(v) for v in rng.integers(0, V, size=PROMPT)]
@@ -253,6 +326,31 @@ def main():
     prefill_ms = statistics.median(times)
     pflops = prefill_flops(cfg, layers, PROMPT)
 
+    # ---- long contexts on the same model: decode above the window (the windowed layers' ring is in use), a long prompt ----
+    long_points = {}
+    if not args.no_large:
+        LONG = 6000
+        for b in (1, 8):
+            ms, _, mid = decode_run(engine, b, 20, 3, V, torch, rng, LONG)
+            long_points[f"decode_b{b}_ctx{LONG}"] = round(b / (ms * 1e-3), 1)
+            long_points[f"decode_b{b}_ctx{LONG}_hbm_frac"] = round((wbytes + cache_bytes_read(cfg, layers, mid)) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+        long_prompt = [int(v) for v in rng.integers(0, V, size=CONTEXT)]
+        times8k = []
+        for k in range(3):
+            slot = engine.new_sequence()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            engine.step([slot], [long_prompt], "last")
+            stop.record()
+            torch.cuda.synchronize()
+            engine.release(slot)
+            if k >= 1:
+                times8k.append(start.elapsed_time(stop))
+        ms8k = statistics.median(times8k)
+        long_points[f"prefill_{CONTEXT}_tok_s"] = round(CONTEXT / (ms8k * 1e-3), 1)
+        long_points[f"prefill_{CONTEXT}_frac"] = round(prefill_flops(cfg, layers, CONTEXT) / (ms8k * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)
+
     # ---- end to end through the Python entry point: host tokens in and out ----
     del engine
     torch.cuda.empty_cache()
@@ -273,6 +371,16 @@ def main():
     gen.generate_batch_results(prompts, args.warmup + args.steps + 1, stream=on_token)
     e2e_tps = 8 * args.steps / (marks["t1"] - marks["t0"])
     h2d = next(iter(gen.engine._graphs.values())).layout.size * 4 if gen.engine._graphs else 0
+
+    # ---- the larger shapes of the reference's list: 9B (8 unequal prompts, 256 new) and 27B (16 prompts, 128 new) ----
+    large = {}
+    if not args.no_large and args.layers is None:
+        del gen, model
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        large["gemma2_9b"] = workload(GEMMA2_9B, spread(64, 6000, 8), 256, pk, torch, rng)
+        large["gemma2_27b"] = workload(GEMMA2_27B, spread(1024, 4096, 16), 128, pk, torch, rng)
     clock_info = clocks.stop()
 
     step_bytes = wbytes + cache_bytes_read(cfg, layers, mid8)
@@ -290,6 +398,9 @@ def main():
             "sliding_window": cfg["sliding_window"], "global_batch": 8, "seq_len": CONTEXT, "prompt_len": PROMPT,
             "new_tokens": NEW_TOKENS, "parallelism": "single GPU", "cache": "paged, 64 positions a page, sized for 8192 a sequence",
             "l2": "inputs larger than L2: 5.2 GB of weights read per step",
+            "points_long": "2B shape: decode at batch 1 and 8 from 6000-token prompts, one prompt of 8192 tokens",
+            "points_9b": "42 layers, hidden 3584, 16/8 heads, head 256, intermediate 14336; 8 prompts 64..6000, 256 new",
+            "points_27b": "46 layers, hidden 4608, 32/16 heads, head 128, intermediate 36864; 16 prompts 1024..4096, 128 new",
         },
         "clocks": clock_info,
         "e2e": {"value": round(e2e_tps, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8 * 4},
@@ -300,8 +411,14 @@ def main():
                      "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"]},
         "points": {"decode_b1": round(1 / (ms1 * 1e-3), 1), "decode_b64": round(64 / (ms64 * 1e-3), 1),
                    "decode_b64_hbm_frac": round((wbytes + cache_bytes_read(cfg, layers, mid64)) / (ms64 * 1e-3) / 1e9
-                                                / pk["hbm_gbs"], 4)},
+                                                / pk["hbm_gbs"], 4),
+                   "decode_b1_hbm_frac": round((wbytes + cache_bytes_read(cfg, layers, [PROMPT + NEW_TOKENS // 2])) / (ms1 * 1e-3) / 1e9
+                                               / pk["hbm_gbs"], 4)},
     }
+    out["points"].update(long_points)
+    for name, figures in large.items():
+        for k, v in figures.items():
+            out["points"][f"{name}_{k}"] = v
     print(json.dumps(out))
     return 0
 
