@@ -21,3 +21,10 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_terminal_summary(terminalreporter):
+    """The largest logit error the engine tests saw, relative to the largest logit, per dtype."""
+    mh = sys.modules.get("model_helpers")
+    for dtype, ratio in sorted(getattr(mh, "OBSERVED", {}).items()):
+        terminalreporter.write_line(f"largest logit error / largest logit, {dtype}: {ratio:.3e}")

@@ -63,20 +63,26 @@ def prompt(seed: int, n: int, vocab: int):
     return [int(v) for v in rng.integers(0, vocab, size=n)]
 
 
-def tolerance(dtype: str, want: np.ndarray) -> float:
-    """float32: 5e-5 absolute on logits of order one or less (float32 rounding through a few
-    layers).  bfloat16: 3 % of the largest logit (bfloat16 keeps 8 bits; activations are rounded
-    a few times per layer) plus a small absolute floor."""
+def tolerance(dtype: str, want: np.ndarray, bf16_fraction: float = 0.02) -> float:
+    """Set from what the tests observe (conftest prints the largest error over the largest logit at the end
+    of a session).  float32: 2e-5 of the largest logit, at least 2e-5 (observed: 2e-6).  bfloat16: 2 % of the
+    largest logit plus a small absolute floor (observed on the tiny configurations: 1.1 %; the tests at
+    real layer sizes, where thousands of terms average the roundings out, observe 0.2 % and pass 0.5 %)."""
     scale = float(np.abs(want).max())
-    return 5e-5 * max(1.0, scale) if dtype == "float32" else 0.03 * scale + 1e-3
+    return 2e-5 * max(1.0, scale) if dtype == "float32" else bf16_fraction * scale + 1e-3
 
 
-def assert_logits(got: torch.Tensor, want: np.ndarray, dtype: str, what=""):
+OBSERVED = {}    # dtype -> largest (error / largest logit) seen by assert_logits in this session; conftest prints it
+
+
+def assert_logits(got: torch.Tensor, want: np.ndarray, dtype: str, what="", bf16_fraction: float = 0.02):
     got = got.detach().float().cpu().double().numpy()
     assert got.shape == want.shape, (what, got.shape, want.shape)
     assert np.isfinite(got).all(), f"{what}: non-finite logits"
     err = np.abs(got - want)
-    tol = tolerance(dtype, want)
+    tol = tolerance(dtype, want, bf16_fraction)
+    if err.size:
+        OBSERVED[dtype] = max(OBSERVED.get(dtype, 0.0), float(err.max()) / max(float(np.abs(want).max()), 1e-9))
     if err.max() > tol:
         r, c = np.unravel_index(err.argmax(), err.shape)
         first_bad = int(np.argmax(err.max(axis=1) > tol))

@@ -22,6 +22,7 @@ import model_helpers as mh
 import plain_gemma2 as plain
 
 pytestmark = pytest.mark.gpu
+REAL_BF16 = 0.005      # bfloat16 tolerance as a fraction of the largest logit: observed 0.0015 (2B widths) and 0.0019 (27B widths)
 
 WIDTHS = {
     "2b": dict(hidden_size=2304, num_attention_heads=8, num_key_value_heads=4, head_dim=256, intermediate_size=9216,
@@ -107,32 +108,32 @@ def test_bfloat16_engine_in_four_cuts(shape):
     slot = eng.new_sequence()
     got = eng.step([slot], [ids], "all")
     report(f"{shape} bfloat16 whole", got, want[0])
-    mh.assert_logits(got, want[0], "bfloat16", f"{shape} whole")
+    mh.assert_logits(got, want[0], "bfloat16", f"{shape} whole", bf16_fraction=REAL_BF16)
     eng.release(slot)
     # 2. the last 32 one by one: weight-streaming products, decode attention on a wrapped ring
     slot = eng.new_sequence()
     eng.step([slot], [ids[:1268]], [[]])
     rows = [eng.step([slot], [[ids[t]]], "last").clone() for t in range(1268, 1300)]
     report(f"{shape} bfloat16 last 32 one by one", torch.cat(rows), want[0][1268:])
-    mh.assert_logits(torch.cat(rows), want[0][1268:], "bfloat16", f"{shape} last 32 one by one")
+    mh.assert_logits(torch.cat(rows), want[0][1268:], "bfloat16", f"{shape} last 32 one by one", bf16_fraction=REAL_BF16)
     eng.release(slot)
     # 3. in portions: 700 + 500 + 100 tokens; the second and third read a cached prefix on the wrapped ring
     slot = eng.new_sequence()
     parts = [eng.step([slot], [ids[a:b]], "all").clone() for a, b in ((0, 700), (700, 1200), (1200, 1300))]
     report(f"{shape} bfloat16 portions", torch.cat(parts), want[0])
-    mh.assert_logits(torch.cat(parts), want[0], "bfloat16", f"{shape} portions")
+    mh.assert_logits(torch.cat(parts), want[0], "bfloat16", f"{shape} portions", bf16_fraction=REAL_BF16)
     eng.release(slot)
     # 4. a batch of unequal lengths, the shorter requests ending earlier, then the next batch on their slots
     for round_ in range(2):
         cut = [len(s) - k for s, k in zip(seqs, (6, 3, 9))]
         slots = [eng.new_sequence() for _ in seqs]
         got = eng.step(slots, [s[:c] for s, c in zip(seqs, cut)], "last")
-        mh.assert_logits(got, np.stack([w[c - 1] for w, c in zip(want, cut)]), "bfloat16", f"{shape} batch prompts")
+        mh.assert_logits(got, np.stack([w[c - 1] for w, c in zip(want, cut)]), "bfloat16", f"{shape} batch prompts", bf16_fraction=REAL_BF16)
         pos = list(cut)
         live = [0, 1, 2]
         while live:
             got = eng.step([slots[i] for i in live], [[seqs[i][pos[i]]] for i in live], "last")
-            mh.assert_logits(got, np.stack([want[i][pos[i]] for i in live]), "bfloat16", f"{shape} batch decode at {pos}")
+            mh.assert_logits(got, np.stack([want[i][pos[i]] for i in live]), "bfloat16", f"{shape} batch decode at {pos}", bf16_fraction=REAL_BF16)
             for i in live:
                 pos[i] += 1
             for i in [i for i in live if pos[i] == len(seqs[i])]:
@@ -165,5 +166,5 @@ def test_window_of_4096_wraps_its_ring(shape):
             got.append(eng.step([slot], [ids[a:b]], [places]).clone())
         got += [eng.step([slot], [[ids[t]]], "last").clone() for t in range(4200, 4240)]
         report(f"{shape} window 4096, portions {portions}", torch.cat(got), want)
-        mh.assert_logits(torch.cat(got), want, "bfloat16", f"{shape} window 4096 {portions}")
+        mh.assert_logits(torch.cat(got), want, "bfloat16", f"{shape} window 4096 {portions}", bf16_fraction=REAL_BF16)
         eng.release(slot)
