@@ -1,7 +1,8 @@
 """Whole-model logits at real layer sizes: two-layer models (one windowed layer, one global) with the
-widths of the 2B shape (hidden 2304, 8 heads on 4, head size 256, intermediate 9216) and of the 27B shape
-(hidden 4608, 32 heads on 16, head size 128, query scale 144), the vocabulary cut to a few thousand so
-that the plain implementation stays affordable.  At these sizes the engine takes the kernels the tiny
+widths of the 2B shape (hidden 2304, 8 heads on 4, head size 256, intermediate 9216), of the 9B shape
+(hidden 3584, 16 heads on 8, head size 256, intermediate 14336) and of the 27B shape (hidden 4608, 32
+heads on 16, head size 128, query scale 144; intermediate 12288, a third of the real one), the
+vocabulary cut to a few thousand so that the plain implementation stays affordable.  At these sizes the engine takes the kernels the tiny
 configurations never reach: the tensor-memory prefill attention, the decode kernel's fixed-size forms,
 both forms of the tcgen05 product (single blocks and pairs, sums of more than 4,096 terms).
 
@@ -22,11 +23,13 @@ import model_helpers as mh
 import plain_gemma2 as plain
 
 pytestmark = pytest.mark.gpu
-REAL_BF16 = 0.005      # bfloat16 tolerance as a fraction of the largest logit: observed 0.0015 (2B widths) and 0.0019 (27B widths)
+REAL_BF16 = 0.005      # bfloat16 tolerance as a fraction of the largest logit: observed 0.0015 to 0.0019 at the three widths
 
 WIDTHS = {
     "2b": dict(hidden_size=2304, num_attention_heads=8, num_key_value_heads=4, head_dim=256, intermediate_size=9216,
                query_pre_attn_scalar=256, vocab_size=4096),
+    "9b": dict(hidden_size=3584, num_attention_heads=16, num_key_value_heads=8, head_dim=256, intermediate_size=14336,
+               query_pre_attn_scalar=256, vocab_size=3500),
     "27b": dict(hidden_size=4608, num_attention_heads=32, num_key_value_heads=16, head_dim=128, intermediate_size=12288,
                 query_pre_attn_scalar=144, vocab_size=3000),
 }
@@ -78,7 +81,7 @@ def report(what, got, want):
     return err
 
 
-@pytest.mark.parametrize("shape", ["2b", "27b"])
+@pytest.mark.parametrize("shape", ["2b", "9b", "27b"])
 def test_float32_engine_against_the_plain_implementation(shape):
     from rust_deeplearning_b200 import Engine
     eng = Engine(loaded(shape, "float32"), max_tokens=2048)
@@ -97,7 +100,7 @@ def test_float32_engine_against_the_plain_implementation(shape):
         assert torch.equal(eng.step([slot], [[ids[t]]], "all"), whole[t:t + 1]), f"position {t} differs from the whole run"
 
 
-@pytest.mark.parametrize("shape", ["2b", "27b"])
+@pytest.mark.parametrize("shape", ["2b", "9b", "27b"])
 def test_bfloat16_engine_in_four_cuts(shape):
     from rust_deeplearning_b200 import Engine
     eng = Engine(loaded(shape, "bfloat16"), max_tokens=4096, max_seqs=4)
