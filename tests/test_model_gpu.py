@@ -10,7 +10,7 @@ import tiny_configs
 
 pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
-NAMES = ["A", "B", "C"]
+NAMES = ["A", "B", "C", "D", "E"]
 
 
 def vocab(name):

@@ -44,7 +44,19 @@ TINY_D = {
     "bos_token_id": 2, "eos_token_id": 1,
 }
 
-CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3)}
+# awkward sizes: a head size that is no multiple of 16 (the fast attention kernels do not take it), widths
+# that are no multiple of 8 (the tensor-core products do not take them), a window shorter than a page row
+TINY_E = {
+    "architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2",
+    "num_hidden_layers": 2, "hidden_size": 50, "num_attention_heads": 5, "num_key_value_heads": 5,
+    "head_dim": 24, "intermediate_size": 70, "vocab_size": 97, "rms_norm_eps": 1e-6,
+    "rope_theta": 10000.0, "sliding_window": 5, "query_pre_attn_scalar": 24,
+    "attn_logit_softcapping": 50.0, "final_logit_softcapping": 30.0, "max_position_embeddings": 256,
+    "hidden_activation": "gelu_pytorch_tanh", "tie_word_embeddings": False,
+    "bos_token_id": 2, "eos_token_id": 1,
+}
+
+CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3), "E": (TINY_E, 4)}
 
 
 def config(name):
