@@ -72,9 +72,19 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+// policy: an L2 cache policy (createpolicy); 0: none
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, unsigned long long policy = 0) {
+    if (policy)
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                     ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
+    else
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ unsigned long long l2_evict_first_policy() {
+    unsigned long long p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -163,6 +173,9 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
     // A page's keys and its values are each one contiguous block: one bulk copy each (issued by thread 0).
     // Tile i of the run is the keys (i even) or the values (i odd) of page page_first + i / 2.
     const int n_tiles = 2 * (page_last - page_first + 1);
+    // a step reads every page once: the pages pass through L2 marked to be evicted first and leave the step's
+    // activations (and the next kernels' inputs) in place
+    const unsigned long long kv_policy = l2_evict_first_policy();
     auto issue = [&](int i) {
         if (*gave_up) return;
         issued = i + 1;
@@ -171,7 +184,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
         const uint32_t place = (uint32_t)(i % 3);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         mbar_expect_tx(bars + 8 * place, tile_bytes + (i == 0 ? (uint32_t)a.test_extra_tx : 0u));
-        bulk_load(tiles_s + place * tile_bytes, ((i & 1) ? vcache : kcache) + off, tile_bytes, bars + 8 * place);
+        bulk_load(tiles_s + place * tile_bytes, ((i & 1) ? vcache : kcache) + off, tile_bytes, bars + 8 * place, kv_policy);
     };
     auto wait_tile = [&](int i) { return mbar_wait_bounded(bars + 8 * (uint32_t)(i % 3), (uint32_t)((i / 3) & 1), a.wait_cycles, gave_up); };
     // The kernel before this one writes the step's new rows: positions from seq_past on.  A first page

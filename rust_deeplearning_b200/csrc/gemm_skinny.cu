@@ -75,9 +75,19 @@ __device__ __forceinline__ void st_mbar_expect_tx(uint32_t bar, uint32_t bytes) 
 __device__ __forceinline__ void st_mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void st_bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+// policy: an L2 cache policy (createpolicy); 0: none
+__device__ __forceinline__ void st_bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, unsigned long long policy = 0) {
+    if (policy)
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                     ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
+    else
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ unsigned long long l2_evict_first_policy() {
+    unsigned long long p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
 }
 __device__ __forceinline__ bool st_mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -134,6 +144,9 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(SkinnyArgs a
             int s = 0;                                   // place in the ring, and how often it has been gone round
             uint32_t round = 0;
             bool first_copy = true;
+            // The weights are read once a step: they pass through L2 marked to be evicted first, so that what the step
+            // reads again and again - the rows of activations, the residual stream - stays there.
+            const unsigned long long policy = l2_evict_first_policy();
             for (int unit = blockIdx.x; unit < n_units; unit += gridDim.x) {
                 long long row;
                 bool row_ok;
@@ -156,7 +169,7 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(SkinnyArgs a
                         st_mbar_expect_tx(full_s + 8 * s, bytes * (uint32_t)n_ok + (first_copy ? (uint32_t)a.test_extra_tx : 0u));
                     }
                     __syncwarp(0xffffu);
-                    if (row_ok) st_bulk_load(tiles_s + (uint32_t)(s * ST_TILE_BYTES + lane * ST_PITCH), a.w + row * K + k0, bytes, full_s + 8 * s);
+                    if (row_ok) st_bulk_load(tiles_s + (uint32_t)(s * ST_TILE_BYTES + lane * ST_PITCH), a.w + row * K + k0, bytes, full_s + 8 * s, policy);
                     first_copy = false;
                     if (++s == stages) { s = 0; ++round; }
                 }
