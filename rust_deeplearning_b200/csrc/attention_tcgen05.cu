@@ -5,13 +5,10 @@
 // (cp.async.bulk.tensor, 128-byte swizzle) straight out of the packed [tokens, heads * head_dim]
 // rows; scores S = Q K^T (128 x 64 a tile) and the output O += P V (128 x head_dim) are tcgen05.mma
 // products whose accumulators live in tensor memory; keys and values are double-buffered.
-// Warp 0 loads, warp 1 issues products, warps 2-9 do the softmax: two threads own a query row, each
-// half of its 64 scores (tcgen05.ld), apply scale, soft-cap and masks in float, exchange their maxima
-// (a 64-thread barrier of the two warps that share a quarter of the rows), keep the running maximum
-// and their half of the sum, write their probabilities as bfloat16 into shared memory (the A
-// operand of P V) and, at the end, normalise and store their half of the output row.  With one
-// thread a row (one warp a scheduler) nothing hid the latency of the row's 128 dependent
-// transcendentals and the tensor pipe idled half of the time; two warps a scheduler keep it fed.
+// Warp 0 loads, warp 1 issues products, warps 2-5 do the softmax: each of their 128 threads owns
+// one query row, reads its 64 scores with tcgen05.ld, applies scale, soft-cap and masks in float,
+// keeps the running maximum and sum, writes the probabilities as bfloat16 into shared memory (the
+// A operand of P V) and, at the end, normalises and stores its output row.
 //
 // The output in tensor memory is rescaled only when a row's maximum has grown by more than 2^8
 // since the last rescale (the probabilities are then at most 256, far inside bfloat16's and
@@ -24,7 +21,7 @@
 
 namespace {
 
-constexpr int QM = 128, KN = 64, SOFTMAX_WARPS = 8, ATC_THREADS = 64 + SOFTMAX_WARPS * 32, HALF = KN / 2;
+constexpr int QM = 128, KN = 64, ATC_THREADS = 192;
 constexpr long long WAIT_CYCLES = RDL_WAIT_CYCLES;
 constexpr float RESCALE_STEP = 8.0f;
 
@@ -147,12 +144,9 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
     unsigned char* sP = sV + 2 * kv_bytes;             // [128 rows][128 bytes]
     __shared__ __align__(8) unsigned long long q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full, s_empty, p_full, pv_done;
     __shared__ uint32_t tmem_slot;
-    __shared__ float xch[2][2][QM];        // [tile parity][half][row]: what the two threads of a row tell each other
-    __shared__ int s_fail;                 // a softmax thread's wait ran out: nobody waits any more, the result is void
     const uint32_t tmem_cols = hd <= 64 ? 128 : (hd <= 192 ? 256 : 512);   // 64 for S, head_dim for O, a power of two
 
     if (threadIdx.x == 0) {
-        s_fail = 0;
         mbar_init(smem_u32(&q_full), 1);
         for (int s = 0; s < 2; ++s) {
             mbar_init(smem_u32(&k_full[s]), 1);
@@ -161,8 +155,8 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
             mbar_init(smem_u32(&v_empty[s]), 1);
         }
         mbar_init(smem_u32(&s_full), 1);
-        mbar_init(smem_u32(&s_empty), SOFTMAX_WARPS);
-        mbar_init(smem_u32(&p_full), SOFTMAX_WARPS);
+        mbar_init(smem_u32(&s_empty), 4);
+        mbar_init(smem_u32(&p_full), 4);
         mbar_init(smem_u32(&pv_done), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -259,9 +253,8 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
             }
         }
     } else {
-        // ---- softmax and output: two threads a query row, one half of the tile's 64 keys each ----
-        const int q = warp & 3;                                  // the quarter of the rows (tensor-memory lanes) this warp may touch
-        const int half = (warp - 2) >> 2;                        // warps 2-5: keys 0-31 of a tile, warps 6-9: keys 32-63
+        // ---- softmax and output: thread = query row ----
+        const int q = warp & 3;
         const int r = q * 32 + lane;
         const int pr = q0 + r;                                   // the row's position in its sequence
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
@@ -269,65 +262,57 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
         // score -> base-2 logit: with a soft-cap, tanh(s * scale / cap) * cap * log2(e); else s * scale * log2(e)
         const bool capped = a.softcap > 0.f;
         const float c_in = capped ? a.score_scale / a.softcap : a.score_scale * LOG2E;
-        const float c_out = capped ? a.softcap * LOG2E : 1.0f;
+        const float c_out = a.softcap * LOG2E;
         const int pr_warp_first = q0 + q * 32, pr_warp_last = pr_warp_first + 31;
-        // the two warps of a quarter meet at a barrier of their own (ids 2-5; 0 and 1 are taken)
-        auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(2 + q) : "memory"); };
-        // The softmax threads meet at barriers (pairs of warps, and all of them at the end), so none of them may
-        // leave the loop alone: a wait that runs out sets a flag, after which nobody waits and all run on to the end.
-        volatile int* fail = &s_fail;
-        auto wait = [&](unsigned long long* bar, uint32_t parity) {
-            if (*fail) return;
-            if (!mbar_wait_bounded(smem_u32(bar), parity)) *fail = 1;
-        };
-        float m_ref = -INFINITY, l = 0.f;                        // m_ref: in units of the base-2 logit; l: this thread's half of the sum
-        for (int j = 0; j < n_kv; ++j) {
-            wait(&s_full, j & 1);
+        float m_ref = -INFINITY, l = 0.f;
+        for (int j = 0; j < n_kv && ok; ++j) {
+            if (!mbar_wait_bounded(smem_u32(&s_full), j & 1)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            float t[HALF];
-            tmem_ld32(tmem_s + lane_base + half * HALF, t);
+            float t[KN];
+            {
+                float half[32];
+                tmem_ld32(tmem_s + lane_base, half);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) t[i] = half[i];
+                tmem_ld32(tmem_s + lane_base + 32, half);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) t[32 + i] = half[i];
+            }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&s_empty));      // the score buffer may be overwritten
-            const int key0 = kv_first + j * KN + half * HALF;    // the first key of this thread's half
-            // t becomes tanh(s * scale / cap) (or s * scale * log2(e) without a cap): the factor cap * log2(e) goes
-            // into the one multiply-add in front of the exponential, the maximum is taken of the tanh values
+            const int key0 = kv_first + j * KN;
             if (capped) {
 #pragma unroll
-                for (int i = 0; i < HALF; ++i) t[i] = tanh_fast(t[i] * c_in);
+                for (int i = 0; i < KN; ++i) t[i] = tanh_fast(t[i] * c_in) * c_out;
             } else {
 #pragma unroll
-                for (int i = 0; i < HALF; ++i) t[i] *= c_in;
+                for (int i = 0; i < KN; ++i) t[i] *= c_in;
             }
             // tiles that every row of this warp sees whole need no masks (the test is the same for all lanes)
-            const bool interior = key0 + HALF - 1 <= pr_warp_first && (a.window == 0 || pr_warp_last - key0 < a.window);
+            const bool interior = key0 + KN - 1 <= pr_warp_first && (a.window == 0 || pr_warp_last - key0 < a.window);
             if (!interior) {
-                const int hi = pr - key0, lo = a.window > 0 ? pr - a.window + 1 - key0 : -1;   // columns [lo, hi] of the half are visible
+                const int hi = pr - key0, lo = a.window > 0 ? pr - a.window + 1 - key0 : -1;   // tile columns [lo, hi] are visible
 #pragma unroll
-                for (int i = 0; i < HALF; ++i)
+                for (int i = 0; i < KN; ++i)
                     if (i > hi || i < lo) t[i] = -INFINITY;
             }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int i = 0; i < HALF; i += 4) {
+            for (int i = 0; i < KN; i += 4) {
                 mx4[0] = fmaxf(mx4[0], t[i]); mx4[1] = fmaxf(mx4[1], t[i + 1]);
                 mx4[2] = fmaxf(mx4[2], t[i + 2]); mx4[3] = fmaxf(mx4[3], t[i + 3]);
             }
-            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * c_out;     // c_out > 0: the order is kept
-            // the row's maximum over both halves
-            xch[j & 1][half][r] = mx;
-            pair_sync();
-            mx = fmaxf(mx, xch[j & 1][half ^ 1][r]);
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // P V of the tile before must be finished before its probabilities are overwritten or O is touched
-            if (j > 0) wait(&pv_done, (j - 1) & 1);
+            if (j > 0 && !mbar_wait_bounded(smem_u32(&pv_done), (j - 1) & 1)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const bool grow = mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
-            if (__any_sync(0xffffffffu, grow)) {                 // the same lanes grow in both warps of the pair
+            if (__any_sync(0xffffffffu, grow)) {
                 const float m_new = grow ? mx : m_ref;
                 const float factor = (grow && m_ref > -INFINITY) ? exp2_fast(m_ref - m_new) : 1.0f;
                 if (j > 0) {
-                    // each of the two threads rescales its half of the output row's columns
-                    for (int c = half * (hd / 2); c < (half + 1) * (hd / 2); c += 32) {
+                    for (int c = 0; c < hd; c += 32) {
                         float o[32];
                         tmem_ld32(tmem_o + lane_base + c, o);
 #pragma unroll
@@ -343,17 +328,17 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
             float rs4[4] = {0.f, 0.f, 0.f, 0.f};
             unsigned char* prow = sP + r * 128;
 #pragma unroll
-            for (int c = 0; c < HALF / 8; ++c) {
+            for (int c = 0; c < KN / 8; ++c) {
                 float e[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) { e[i] = exp2_fast(fmaf(t[c * 8 + i], c_out, -ms)); rs4[i & 3] += e[i]; }
+                for (int i = 0; i < 8; ++i) { e[i] = exp2_fast(t[c * 8 + i] - ms); rs4[i & 3] += e[i]; }
                 uint4 raw;
                 __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&raw);
                 hp[0] = __floats2bfloat162_rn(e[0], e[1]);
                 hp[1] = __floats2bfloat162_rn(e[2], e[3]);
                 hp[2] = __floats2bfloat162_rn(e[4], e[5]);
                 hp[3] = __floats2bfloat162_rn(e[6], e[7]);
-                *reinterpret_cast<uint4*>(prow + (((half * (HALF / 8) + c) ^ (r & 7)) * 16)) = raw;
+                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) * 16)) = raw;
             }
             l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // the tensor core reads these writes
@@ -361,13 +346,8 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&p_full));
         }
-        wait(&pv_done, (n_kv - 1) & 1);
+        if (ok && !mbar_wait_bounded(smem_u32(&pv_done), (n_kv - 1) & 1)) ok = false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (*fail) ok = false;
-        // the row's sum: both halves
-        xch[n_kv & 1][half][r] = l;
-        pair_sync();
-        l += xch[n_kv & 1][half ^ 1][r];
         // The rows go through shared memory (the query tile is no longer needed) so that the stores to
         // global memory are whole 16-byte chunks of consecutive addresses: thread -> row on the way in
         // (chunks swizzled by the row, no bank conflicts), thread -> chunk on the way out.
@@ -375,7 +355,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
             const float inv = 1.0f / l;
             unsigned char* srow = sQ + (size_t)r * (hd * 2);
 #pragma unroll
-            for (int c = half * (hd / 2); c < (half + 1) * (hd / 2); c += 32) {
+            for (int c = 0; c < hd; c += 32) {
                 float o[32];
                 tmem_ld32(tmem_o + lane_base + c, o);
 #pragma unroll
@@ -390,13 +370,13 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
                 }
             }
         }
-        asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_WARPS * 32) : "memory");           // the softmax warps, whatever became of their waits
+        asm volatile("bar.sync 1, 128;" ::: "memory");           // the four softmax warps, whatever became of their waits
         {
             constexpr int CHUNKS = hd / 8;                       // 16-byte chunks of a row
             __nv_bfloat16* obase = (__nv_bfloat16*)a.out + (long long)(row0 + q0) * a.out_stride + (long long)h * hd;
             const int tt = threadIdx.x - 64;
 #pragma unroll 4
-            for (int idx = tt; idx < QM * CHUNKS; idx += SOFTMAX_WARPS * 32) {
+            for (int idx = tt; idx < QM * CHUNKS; idx += 128) {
                 const int row = idx / CHUNKS, c = idx - row * CHUNKS;
                 if (row < rows)
                     *reinterpret_cast<uint4*>(obase + (long long)row * a.out_stride + c * 8) =
