@@ -465,8 +465,10 @@ def test_uniform_matches_host():
         assert lib.rdl_sampling_uniform(seed, stream, step) == np.float32(uniform_for(seed, stream, step))
 
 
-@pytest.mark.parametrize("vocab", [131, 256000])
+@pytest.mark.parametrize("vocab", [131, 40000, 100003, 256000, 300001])
 def test_sampling(vocab):
+    """Vocabularies of one, two, four and eight blocks a row (32,768 elements each) of the on-chip sampler, and one
+    too long for it (the one-block-a-row kernel)."""
     rows = 5
     logits = rnd((rows, vocab), torch.float32, 60, 3.0)
     logits[1, 7] = logits[1, 100] = logits[1].max() + 1.0          # a tie: the first maximum wins
