@@ -10,7 +10,7 @@ extern "C" {
 #define RDL_ACT_GELU_TANH 0
 #define RDL_ACT_SILU 1
 
-#define RDL_ABI_VERSION 9
+#define RDL_ABI_VERSION 10
 
 const char* rdl_last_error(void);
 int rdl_abi_version(void);
@@ -103,6 +103,50 @@ int rdl_gemm_f32(void* out, const void* x, const void* w, int m, int n, int k, v
 // when a block gives up a bounded wait for a copy.
 int rdl_gemm_skinny(void* out, int out_dtype, const void* x, const void* w, int m, int n, int k,
                     int gated, int activation, float softcap, int* status, void* stream);
+
+// The norms around a few-row product taken off the step's critical path ("deferred norms").
+// A branch of the residual stream h ends in a product P (up to 8 rows, as many columns as the stream is wide)
+// and is followed by
+//   h' = h + norm1(y)     y = P's result, norm1(y) = y / sqrt(mean(y^2) + eps1) * (w1 + off1)
+//   x  = norm2(h')        norm2 likewise with (w2, eps2, off2)
+//   z  = x W^T            the next product C.
+// Written out: x[k] = s2 (h[k] + s1 a'[k]) (w2[k] + off2) with a' = y (w1 + off1), s1 = 1 / sqrt(mean(y^2) + eps1),
+// s2 = 1 / sqrt(mean(h'^2) + eps2) and mean(h'^2) = (sum h^2 + 2 s1 sum h a' + s1^2 sum a'^2) / width.  Hence
+//   z = s2 (W ht + s1 W at),   ht = h (w2 + off2),   at = a' (w2 + off2):
+// C multiplies the two bfloat16 row blocks ht and at (one operand of 16 rows) as soon as they are there and
+// applies the two numbers of each row in its epilogue.  P's epilogue writes a', at and, for every 16 columns,
+// the four partial sums; C adds those up in a fixed order, and its blocks form h' and the next ht, a slice
+// each.  No kernel stands between P and C, and nothing on the way waits for a whole row.
+#define RDL_NORM_BRANCH 1      // the call is P
+#define RDL_NORM_DEFERRED 2    // the call is C
+typedef struct {
+    int mode;
+    float* sums;                     // [units of 16 columns][8 rows][4]: sum y^2, sum h^2, sum h a', sum a'^2
+    int n_sums;                      // C: the units P had (P: taken from n)
+    // P
+    const float* residual;           // h [rows][n]
+    const void* w1; int w1_dtype; float off1;
+    const void* w2; int w2_dtype; float off2;
+    void* branch;                    // out: a', bfloat16 [rows][n]
+    void* scaled;                    // out: at, bfloat16 [rows][n] (rows 8.. of C's operand)
+    // C; its x is bfloat16 [16][k]: rows 0..7 ht, rows 8..15 at
+    float eps1, eps2;
+    const void* branch_in;           // a' [rows][k]
+    const float* residual_in;        // h [rows][k]
+    float* residual_out;             // out, optional: h' [rows][k]; not the buffer of residual_in
+    const void* w_next; int w_next_dtype; float off_next;    // optional: (w + off) of the norm h' is asked for next
+    void* scaled_next;               // out, optional: h' (w_next + off_next), bfloat16 [rows][k]
+    const int* row_index; int n_out; // output row j is the operand's row row_index[j] (NULL: j); n_out <= 8 rows
+} DeferredNormArgs;
+// rdl_gemm_skinny with m <= 8 and one side of a deferred norm.  P: plain epilogue only (not gated, no soft-cap),
+// `out` unused.  C: any epilogue; m counts the rows of each half of the operand.
+int rdl_gemm_skinny_norm(void* out, int out_dtype, const void* x, const void* w, int m, int n, int k,
+                         int gated, int activation, float softcap, const DeferredNormArgs* norm, int* status, void* stream);
+// Rows of a residual stream outside a product: h' = h + s1 a' with s1 from the sums (sums NULL: h' = h), written
+// to residual_out (optional; may be residual_in), and scaled = h' (w + off) as bfloat16 (optional).
+int rdl_stream_rows(const float* sums, int n_sums, float eps1, const void* branch, const float* residual_in,
+                    float* residual_out, const void* w, int w_dtype, float off, void* scaled,
+                    int n_rows, int width, void* stream);
 
 // The same product and epilogues for any number of rows on tcgen05 tensor cores (TMA-fed, accumulators in
 // tensor memory).  n must be a positive number, k a multiple of 8; status (optional) is set non-zero

@@ -22,6 +22,13 @@
 //
 // The k index inside a 32-wide step is permuted identically for both operands (a lane's 16
 // bytes feed two instructions), which leaves every dot product unchanged.
+//
+// Deferred norms (MODE; the algebra is in api.h at DeferredNormArgs).  A product whose result is a branch
+// of the residual stream (MODE 1) writes, instead of y: a' = y (w1 + off1) and a' (w2 + off2) as bfloat16,
+// and for its 16 columns the sums of y^2, h^2, h a' and a'^2 of every row.  The product that follows the two
+// norms (MODE 2) multiplies the 16-row operand [h (w2 + off2); a' (w2 + off2)], adds the partial sums up
+// (each thread a 32nd of the units, then 32 terms in order), and forms s2 (z_h + s1 z_a) in its epilogue;
+// every block also updates a slice of the stream (h' = h + s1 a') and of the next operand's first half.
 #include <cstdlib>
 
 #include "activations.cuh"
@@ -50,6 +57,7 @@ struct SkinnyArgs {
     float softcap;              // > 0: cap * tanh(v / cap)
     long long wait_cycles;      // clock cycles after which a wait is given up
     int test_extra_tx;          // tests only: bytes announced beyond what the block's first copy delivers
+    DeferredNormArgs d;         // MODE 1 and 2
 };
 
 thread_local cudaError_t g_launch_error = cudaSuccess;
@@ -113,12 +121,15 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     return v;
 }
 
-template <int NT, bool GATED, int KU>
-__global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(SkinnyArgs a, int stages, int* status) {
+template <int NT, bool GATED, int KU, int MODE>
+__global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(const __grid_constant__ SkinnyArgs a, int stages, int* status) {
+    static_assert(MODE == 0 || (MODE == 1 && NT == 1 && !GATED) || (MODE == 2 && NT == 2), "deferred norms: P has 8 rows, C an operand of 16");
     constexpr int ST_KT = st_kt(KU), ST_PITCH = st_pitch(KU), ST_TILE_BYTES = st_tile_bytes(KU), KW = 32 * KU;
     extern __shared__ __align__(128) unsigned char st_tiles[];
     __shared__ __align__(8) unsigned long long full_bar[ST_MAX_STAGES], empty_bar[ST_MAX_STAGES];
     __shared__ float partial[ST_WARPS][NT][ROWS * 8];
+    __shared__ float4 sum_part[MODE == 2 ? 32 : 1][8];     // MODE 2: the partial sums, a 32nd of the units each
+    __shared__ float2 row_scale[8];                         // MODE 2: (s1, s2) of every row
     __shared__ int gave_up;
     constexpr int OUT_ROWS = GATED ? 8 : ROWS;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -183,7 +194,7 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(SkinnyArgs a
         bool x_ok[NT];
 #pragma unroll
         for (int i = 0; i < NT; ++i) {
-            x_ok[i] = i * 8 + g < a.M;
+            x_ok[i] = MODE == 2 ? g < a.M : i * 8 + g < a.M;      // MODE 2: both halves of the operand have M rows
             xrow[i] = a.x + (long long)(i * 8 + g) * K;
         }
         const uint4 zero4 = make_uint4(0, 0, 0, 0);
@@ -204,6 +215,46 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(SkinnyArgs a
         constexpr bool X_AHEAD = NT == 1;
         uint4 xcur[NT][KU], xnext[X_AHEAD ? NT : 1][KU];
         if (X_AHEAD) load_x(kw, xcur);
+        // MODE 2: this block's slice of the stream (one element a thread and round), asked for now, stored once s1 is known
+        const DeferredNormArgs& d = a.d;
+        const int tid = threadIdx.x;
+        long long slice_e = -1;
+        float slice_h = 0.f, slice_a = 0.f, slice_w = 0.f;
+        bool first_unit = true;
+        if constexpr (MODE == 2) {
+            load_x(kw, xcur);              // the first tile's rows are on their way while the sums are added up
+            const long long total = (long long)a.M * K, per = (total + gridDim.x - 1) / gridDim.x;
+            auto slice_load = [&](long long e) {
+                slice_h = d.residual_in[e];
+                slice_a = __bfloat162float(((const __nv_bfloat16*)d.branch_in)[e]);
+                slice_w = d.scaled_next ? rdl_load(d.w_next, e % K, d.w_next_dtype) + d.off_next : 0.f;
+            };
+            if (d.residual_out || d.scaled_next) {
+                const long long e = blockIdx.x * per + tid;
+                if (tid < per && e < total) { slice_e = e; slice_load(e); }
+            }
+            // the partial sums: thread (part, m) adds the units part, part + 32, ... of row m
+            const int m = tid & 7, part = tid >> 3;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int u = part; u < d.n_sums; u += 32) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(d.sums) + u * 8 + m);
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+            sum_part[part][m] = acc;
+            asm volatile("bar.sync 1, %0;" ::"n"(ST_WARPS * 32) : "memory");
+            if (tid < 8) {
+                float4 t = sum_part[0][tid];
+#pragma unroll
+                for (int q = 1; q < 32; ++q) {
+                    const float4 v = sum_part[q][tid];
+                    t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+                }
+                const float s1 = rsqrtf(t.x / (float)K + d.eps1);
+                const float hh = t.y + 2.f * s1 * t.z + s1 * s1 * t.w;           // sum of (h + s1 a')^2
+                row_scale[tid] = make_float2(s1, rsqrtf(fmaxf(hh, 0.f) / (float)K + d.eps2));
+            }
+            // row_scale is read after the first unit's barrier below
+        }
         const uint32_t frag = tiles_s + (uint32_t)(g * ST_PITCH + (kw + t * 8) * 2);
         int s = 0;
         uint32_t round = 0;
@@ -211,10 +262,20 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(SkinnyArgs a
             float acc[NT][4];
 #pragma unroll
             for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+            // MODE 1: thread (m, r) of the epilogue asks for its element of the stream and its two norm weights now
+            float br_h = 0.f, br_g1 = 0.f, br_g2 = 0.f;
+            if constexpr (MODE == 1) {
+                const int m = tid >> 4, n = unit * ROWS + (tid & 15);
+                if (tid < 8 * ROWS && m < a.M && n < a.N) {
+                    br_h = d.residual[(long long)m * a.N + n];
+                    br_g1 = rdl_load(d.w1, n, d.w1_dtype) + d.off1;
+                    br_g2 = rdl_load(d.w2, n, d.w2_dtype) + d.off2;
+                }
+            }
             for (int tk = 0; tk < tiles_per_unit; ++tk) {
                 // the activations of the tile after this one (the next unit starts again at k = 0)
                 if (X_AHEAD) load_x((tk + 1 < tiles_per_unit ? (tk + 1) * ST_KT : 0) + kw, reinterpret_cast<uint4 (&)[NT][KU]>(xnext));
-                else load_x(tk * ST_KT + kw, xcur);
+                else if (!(MODE == 2 && tk == 0 && unit == (int)blockIdx.x)) load_x(tk * ST_KT + kw, xcur);
                 st_wait(full_s + 8 * s, round & 1, a.wait_cycles, gave_up_v);
                 const int kb = tk * ST_KT + kw;
                 if (kb < K) {
@@ -248,6 +309,69 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(SkinnyArgs a
                 for (int e = 0; e < 4; ++e) partial[warp][i][(2 * t + (e & 1)) * ROWS + g + 8 * (e >> 1)] = acc[i][e];
             asm volatile("bar.sync 1, %0;" ::"n"(ST_WARPS * 32) : "memory");
             const int n0 = unit * OUT_ROWS;
+            if constexpr (MODE == 1) {
+                // the first four warps: thread (m, r) has column n0 + r of row m; 16 neighbouring lanes add up a row's sums
+                if (tid < 8 * ROWS) {
+                    const int m = tid >> 4, r = tid & 15, n = n0 + r;
+                    const bool ok = m < a.M && n < a.N;
+                    float y = 0.f;
+#pragma unroll
+                    for (int w = 0; w < ST_WARPS; ++w) y += partial[w][0][m * ROWS + r];
+                    if (!ok) y = 0.f;
+                    const __nv_bfloat16 a1b = __float2bfloat16_rn(y * br_g1);
+                    const float a1 = __bfloat162float(a1b);                  // what the stream will add, s1 times
+                    float s0 = y * y, s1 = br_h * br_h, s2 = br_h * a1, s3 = a1 * a1;
+#pragma unroll
+                    for (int o = 8; o > 0; o >>= 1) {
+                        s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+                        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+                        s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+                        s3 += __shfl_xor_sync(0xffffffffu, s3, o);
+                    }
+                    if (ok) {
+                        ((__nv_bfloat16*)d.branch)[(long long)m * a.N + n] = a1b;
+                        ((__nv_bfloat16*)d.scaled)[(long long)m * a.N + n] = __float2bfloat16_rn(a1 * br_g2);
+                    }
+                    if (r == 0) reinterpret_cast<float4*>(d.sums)[unit * 8 + m] = make_float4(s0, s1, s2, s3);   // rows beyond M: zeros
+                }
+            } else if constexpr (MODE == 2) {
+                if (first_unit) {
+                    first_unit = false;
+                    // the block's slice of the stream and of the next operand
+                    const long long total = (long long)a.M * K, per = (total + gridDim.x - 1) / gridDim.x;
+                    const long long end = (blockIdx.x + 1) * per < total ? (blockIdx.x + 1) * per : total;
+                    for (long long e = slice_e; e >= 0 && e < end;) {
+                        const float hn = slice_h + row_scale[e / K].x * slice_a;
+                        if (d.residual_out) d.residual_out[e] = hn;
+                        if (d.scaled_next) ((__nv_bfloat16*)d.scaled_next)[e] = __float2bfloat16_rn(hn * slice_w);
+                        e += ST_WARPS * 32;
+                        if (e < end) {
+                            slice_h = d.residual_in[e];
+                            slice_a = __bfloat162float(((const __nv_bfloat16*)d.branch_in)[e]);
+                            slice_w = d.scaled_next ? rdl_load(d.w_next, e % K, d.w_next_dtype) + d.off_next : 0.f;
+                        }
+                    }
+                }
+                for (int idx = tid; idx < d.n_out * OUT_ROWS; idx += ST_WARPS * 32) {
+                    const int j = idx / OUT_ROWS, r = idx - j * OUT_ROWS;
+                    const int n = n0 + r;
+                    const int m = d.row_index ? d.row_index[j] : j;
+                    if (n >= a.N || m < 0 || m >= a.M) continue;
+                    const float2 sc = row_scale[m];
+                    const int slot = m * ROWS + r;
+                    float h0 = 0.f, a0 = 0.f, h1 = 0.f, a1 = 0.f;
+#pragma unroll
+                    for (int w = 0; w < ST_WARPS; ++w) {
+                        h0 += partial[w][0][slot];
+                        a0 += partial[w][1][slot];
+                        if (GATED) { h1 += partial[w][0][slot + 8]; a1 += partial[w][1][slot + 8]; }
+                    }
+                    float y = sc.y * (h0 + sc.x * a0);
+                    if (GATED) y = rdl_activation(y, a.activation) * (sc.y * (h1 + sc.x * a1));
+                    if (a.softcap > 0.f) y = a.softcap * tanhf(y / a.softcap);
+                    rdl_store(a.out, (long long)j * a.N + n, a.out_dtype, y);
+                }
+            } else
             for (int idx = threadIdx.x; idx < NT * 8 * OUT_ROWS; idx += ST_WARPS * 32) {
                 const int m = idx / OUT_ROWS, r = idx - m * OUT_ROWS;
                 const int n = n0 + r;
@@ -270,14 +394,14 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(SkinnyArgs a
     if (*gave_up_v && status && lane == 0) atomicExch(status, RDL_FAULT_GEMM_STREAM);
 }
 
-template <int NT, bool GATED, int KU>
+template <int NT, bool GATED, int KU, int MODE>
 void launch_stream_ku(const SkinnyArgs& a, int* status, cudaStream_t st) {
     constexpr int smem_max = 2 * st_stages(KU) * st_tile_bytes(KU);
     static_assert(2 * st_stages(KU) <= ST_MAX_STAGES, "the ring's barriers");
     static bool opted = false;
     static int sms = 0;
     if (!opted) {
-        g_launch_error = cudaFuncSetAttribute(gemm_stream_kernel<NT, GATED, KU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
+        g_launch_error = cudaFuncSetAttribute(gemm_stream_kernel<NT, GATED, KU, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
         if (g_launch_error != cudaSuccess) return;
         sms = rdl_sm_count();
         opted = true;
@@ -287,17 +411,17 @@ void launch_stream_ku(const SkinnyArgs& a, int* status, cudaStream_t st) {
     const int units = (a.N + (GATED ? 8 : ROWS) - 1) / (GATED ? 8 : ROWS);
     const int stages = units <= sms ? 2 * st_stages(KU) : st_stages(KU);
     const int fit = units <= sms ? sms : 2 * sms;
-    g_launch_error = rdl_launch(gemm_stream_kernel<NT, GATED, KU>, dim3(units < fit ? units : fit), dim3(ST_THREADS), (size_t)stages * st_tile_bytes(KU), st, a, stages, status);
+    g_launch_error = rdl_launch(gemm_stream_kernel<NT, GATED, KU, MODE>, dim3(units < fit ? units : fit), dim3(ST_THREADS), (size_t)stages * st_tile_bytes(KU), st, a, stages, status);
 }
 
-template <int NT, bool GATED>
+template <int NT, bool GATED, int MODE = 0>
 void launch_stream(const SkinnyArgs& a, int* status, cudaStream_t st) {
     const int waste4 = (a.K + st_kt(4) - 1) / st_kt(4) * st_kt(4) - a.K, waste3 = (a.K + st_kt(3) - 1) / st_kt(3) * st_kt(3) - a.K;
     // Tiles of 768 k where they divide the row better, unless the output is very wide: there the kernel runs in
     // its steady state, where the larger copies of 1024 k were measured faster (the output head: 162 against 174 us).
     const int units = (a.N + (GATED ? 8 : ROWS) - 1) / (GATED ? 8 : ROWS);
-    if (waste3 < waste4 && units <= 4096) launch_stream_ku<NT, GATED, 3>(a, status, st);
-    else launch_stream_ku<NT, GATED, 4>(a, status, st);
+    if (waste3 < waste4 && units <= 4096) launch_stream_ku<NT, GATED, 3, MODE>(a, status, st);
+    else launch_stream_ku<NT, GATED, 4, MODE>(a, status, st);
 }
 
 }  // namespace
@@ -313,7 +437,7 @@ extern "C" int rdl_gemm_skinny(void* out, int out_dtype, const void* x, const vo
     RDL_REQUIRE(softcap >= 0.f, "gemm_skinny: soft-cap must not be negative");
     if (m == 0) return 0;
     SkinnyArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, out, m, n, k, out_dtype, activation, softcap,
-                 rdl_wait_cycles_for(RDL_FAULT_GEMM_STREAM), rdl_test_extra_tx_for(RDL_FAULT_GEMM_STREAM)};
+                 rdl_wait_cycles_for(RDL_FAULT_GEMM_STREAM), rdl_test_extra_tx_for(RDL_FAULT_GEMM_STREAM), DeferredNormArgs{}};
     cudaStream_t st = (cudaStream_t)stream;
     g_launch_error = cudaSuccess;
     if (m <= 8) {
@@ -324,5 +448,82 @@ extern "C" int rdl_gemm_skinny(void* out, int out_dtype, const void* x, const vo
         else launch_stream<2, false>(a, status, st);
     }
     RDL_CHECK_EX(g_launch_error, "gemm_skinny");
+    return 0;
+}
+
+extern "C" int rdl_gemm_skinny_norm(void* out, int out_dtype, const void* x, const void* w, int m, int n, int k,
+                                    int gated, int activation, float softcap, const DeferredNormArgs* norm, int* status,
+                                    void* stream) {
+    RDL_REQUIRE(x && w && norm, "gemm_skinny_norm: missing operand");
+    RDL_REQUIRE(m >= 0 && m <= 8, "gemm_skinny_norm: %d rows, at most 8 are supported", m);
+    RDL_REQUIRE(n > 0 && k > 0 && k % 8 == 0, "gemm_skinny_norm: n=%d, k=%d; k must be a multiple of 8", n, k);
+    RDL_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0, "gemm_skinny_norm: operands must start on 16-byte boundaries");
+    RDL_REQUIRE(norm->sums && (uintptr_t)norm->sums % 16 == 0, "gemm_skinny_norm: the partial sums must lie on a 16-byte boundary");
+    if (m == 0) return 0;
+    SkinnyArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, out, m, n, k, out_dtype, activation, softcap,
+                 rdl_wait_cycles_for(RDL_FAULT_GEMM_STREAM), rdl_test_extra_tx_for(RDL_FAULT_GEMM_STREAM), *norm};
+    cudaStream_t st = (cudaStream_t)stream;
+    g_launch_error = cudaSuccess;
+    if (norm->mode == RDL_NORM_BRANCH) {
+        RDL_REQUIRE(!gated && softcap == 0.f, "gemm_skinny_norm: a branch's product has the plain epilogue");
+        RDL_REQUIRE(norm->residual && norm->w1 && norm->w2 && norm->branch && norm->scaled, "gemm_skinny_norm: a branch needs the stream, both norms' weights and its two outputs");
+        RDL_REQUIRE(rdl_valid_dtype(norm->w1_dtype) && rdl_valid_dtype(norm->w2_dtype), "gemm_skinny_norm: bad dtype of a norm's weight");
+        launch_stream<1, false, 1>(a, status, st);
+    } else if (norm->mode == RDL_NORM_DEFERRED) {
+        RDL_REQUIRE(out && rdl_valid_dtype(out_dtype), "gemm_skinny_norm: missing output or bad output dtype %d", out_dtype);
+        RDL_REQUIRE(!gated || rdl_activation_known(activation), "gemm_skinny_norm: unknown activation %d", activation);
+        RDL_REQUIRE(softcap >= 0.f, "gemm_skinny_norm: soft-cap must not be negative");
+        RDL_REQUIRE(norm->n_sums > 0 && norm->n_out >= 0 && norm->n_out <= 8, "gemm_skinny_norm: %d units of sums, %d output rows", norm->n_sums, norm->n_out);
+        const bool side = norm->residual_out || norm->scaled_next;
+        RDL_REQUIRE(!side || (norm->branch_in && norm->residual_in), "gemm_skinny_norm: the stream's update needs the branch and the stream");
+        RDL_REQUIRE(!norm->residual_out || norm->residual_out != norm->residual_in, "gemm_skinny_norm: the updated stream needs a buffer of its own (other blocks still read the old one)");
+        RDL_REQUIRE(!norm->scaled_next || (norm->w_next && rdl_valid_dtype(norm->w_next_dtype)), "gemm_skinny_norm: the next operand needs the next norm's weight");
+        if (gated) launch_stream<2, true, 2>(a, status, st);
+        else launch_stream<2, false, 2>(a, status, st);
+    } else {
+        RDL_REQUIRE(false, "gemm_skinny_norm: unknown mode %d", norm->mode);
+    }
+    RDL_CHECK_EX(g_launch_error, "gemm_skinny_norm");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Rows of a residual stream outside a product: what the deferred-norm products do on the side, for the
+// first and the last link of a chain and for a consumer that cannot take the deferred form.  One block a row.
+// ---------------------------------------------------------------------------------------------
+namespace {
+__global__ void stream_rows_kernel(const float* __restrict__ sums, int n_sums, float eps1, const __nv_bfloat16* __restrict__ branch,
+                                   const float* __restrict__ residual_in, float* __restrict__ residual_out,
+                                   const void* __restrict__ w, int w_dtype, float off, __nv_bfloat16* __restrict__ scaled, int width) {
+    __shared__ float scratch[33];
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
+    const int m = blockIdx.x;
+    float s1 = 0.f;
+    if (sums) {
+        float t = 0.f;
+        for (int u = threadIdx.x; u < n_sums; u += blockDim.x) t += sums[((long long)u * 8 + m) * 4];
+        s1 = rsqrtf(block_sum(t, scratch) / (float)width + eps1);
+    }
+    for (int k = threadIdx.x; k < width; k += blockDim.x) {
+        const long long e = (long long)m * width + k;
+        float h = residual_in[e];
+        if (sums) h += s1 * __bfloat162float(branch[e]);
+        if (residual_out) residual_out[e] = h;
+        if (scaled) scaled[e] = __float2bfloat16_rn(h * (rdl_load(w, k, w_dtype) + off));
+    }
+}
+}  // namespace
+
+extern "C" int rdl_stream_rows(const float* sums, int n_sums, float eps1, const void* branch, const float* residual_in,
+                               float* residual_out, const void* w, int w_dtype, float off, void* scaled,
+                               int n_rows, int width, void* stream) {
+    RDL_REQUIRE(residual_in && n_rows >= 0 && n_rows <= 8 && width > 0, "stream_rows: bad sizes rows=%d width=%d (at most 8 rows)", n_rows, width);
+    RDL_REQUIRE(!sums || (branch && n_sums > 0), "stream_rows: sums without a branch");
+    RDL_REQUIRE(!scaled || (w && rdl_valid_dtype(w_dtype)), "stream_rows: the scaled rows need a norm's weight");
+    if (n_rows == 0) return 0;
+    RDL_CHECK_EX(rdl_launch(stream_rows_kernel, dim3(n_rows), dim3(256), 0, (cudaStream_t)stream, sums, n_sums, eps1,
+                            (const __nv_bfloat16*)branch, residual_in, residual_out, w, w_dtype, off, (__nv_bfloat16*)scaled, width),
+                 "stream_rows");
     return 0;
 }

@@ -23,7 +23,7 @@ from concurrent.futures import ThreadPoolExecutor
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(_PKG, "csrc")
 LIB_NAME = "librdl_b200_kernels.so"
-ABI_VERSION = 9
+ABI_VERSION = 10
 
 # fast math is never enabled: the 32-bit path relies on exact tanhf/expf/sqrtf and plain FMA
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -187,6 +187,25 @@ FAULTS = {
 }
 
 
+class DeferredNormArgs(ctypes.Structure):
+    """One side of a deferred norm around a few-row product (`csrc/api.h`)."""
+    _fields_ = [
+        ("mode", ctypes.c_int), ("sums", ctypes.c_void_p), ("n_sums", ctypes.c_int),
+        ("residual", ctypes.c_void_p),
+        ("w1", ctypes.c_void_p), ("w1_dtype", ctypes.c_int), ("off1", ctypes.c_float),
+        ("w2", ctypes.c_void_p), ("w2_dtype", ctypes.c_int), ("off2", ctypes.c_float),
+        ("branch", ctypes.c_void_p), ("scaled", ctypes.c_void_p),
+        ("eps1", ctypes.c_float), ("eps2", ctypes.c_float),
+        ("branch_in", ctypes.c_void_p), ("residual_in", ctypes.c_void_p), ("residual_out", ctypes.c_void_p),
+        ("w_next", ctypes.c_void_p), ("w_next_dtype", ctypes.c_int), ("off_next", ctypes.c_float),
+        ("scaled_next", ctypes.c_void_p),
+        ("row_index", ctypes.c_void_p), ("n_out", ctypes.c_int),
+    ]
+
+
+NORM_BRANCH, NORM_DEFERRED = 1, 2
+
+
 class SamplingArgs(ctypes.Structure):
     _fields_ = [("temperature", ctypes.c_float), ("top_k", ctypes.c_int), ("top_p", ctypes.c_float),
                 ("repetition_penalty", ctypes.c_float), ("seed", ctypes.c_ulonglong)]
@@ -207,6 +226,8 @@ _SIGNATURES = {
     "rdl_rope_cache": [_P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P, _P],
     "rdl_gemm_f32": [_P, _P, _P, _I, _I, _I, _P],
     "rdl_gemm_skinny": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
+    "rdl_gemm_skinny_norm": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, ctypes.POINTER(DeferredNormArgs), _P, _P],
+    "rdl_stream_rows": [_P, _I, _F, _P, _P, _P, _P, _I, _F, _P, _I, _I, _P],
     "rdl_gemm_tc": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
     "rdl_random_normal": [_P, _I, _LL, ctypes.c_ulonglong, ctypes.c_double, _P],
     "rdl_sample": [_P, _P, _I, _I, ctypes.POINTER(SamplingArgs), _P, _P, _P, _P, _P, _P],

@@ -221,15 +221,151 @@ def _gemm_bf16(x, weight, n_out, out_dtype, gated, activation, softcap, status):
     return out
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+# ------------------------------------------------------------------------------------------
+# deferred norms: "norm the branch, add it to the stream, norm the sum" without a kernel of its own
+# ------------------------------------------------------------------------------------------
+# With up to DEFERRED_MAX_ROWS rows (decode) the two norms between the last product of a branch (P) and the
+# first product after them (C) cost more than the products: a kernel that waits for whole rows twice.  The
+# norms are scalings by one number a row and one number a column, so they can be split (the algebra stands in
+# csrc/api.h at DeferredNormArgs): P's epilogue applies the column factors and writes partial sums of squares,
+# C multiplies an operand of 2 x 8 rows (the stream's rows and the branch's rows, both with the second norm's
+# column factors) and applies the row factors in its epilogue.  Three small types carry this through the parts.
+
+DEFERRED_MAX_ROWS = 8
+
+
+class BranchSink(NamedTuple):
+    """What the last product of a branch is given so that it can deliver its result in the split form."""
+    residual: torch.Tensor     # float32 [rows, width]: the stream the branch will be added to
+    post: NormParams           # the norm of the branch before the sum
+    then: NormParams           # the norm the sum is asked for next
+    operand: torch.Tensor      # bfloat16 [16, width]: rows 0..7 are (by the time the product runs) residual * (then.weight + then.offset)
+
+
+class Branch:
+    """A branch delivered through a BranchSink: a' = y (post.weight + post.offset) [rows, width] in bfloat16,
+    the partial sums [units, 8, 4] and, in rows 8.. of the sink's operand, a' (then.weight + then.offset)."""
+
+    def __init__(self, sink: BranchSink, values: torch.Tensor, sums: torch.Tensor):
+        self.sink, self.values, self.sums = sink, values, sums
+        self.shape, self.dtype, self.device = values.shape, values.dtype, values.device
+
+
+class DeferredRows:
+    """Stands for then(residual + post(branch)) [rows, width], or for `row_index`'s rows of it, in the act dtype.
+    `linear` and `linear_gated` take it in place of a tensor; `materialise()` gives the tensor.  Its first
+    use also writes the updated stream to `residual_out` and, if `next_norm` is given, the first half of
+    `next_operand` (the rows of the updated stream times that norm's column factors)."""
+
+    def __init__(self, branch: Branch, residual_out: torch.Tensor, next_norm: Optional[NormParams] = None,
+                 next_operand: Optional[torch.Tensor] = None, row_index: Optional[torch.Tensor] = None):
+        self.branch, self.residual_out = branch, residual_out
+        self.next_norm, self.next_operand, self.row_index = next_norm, next_operand, row_index
+        rows = row_index.numel() if row_index is not None else branch.shape[0]
+        self.shape, self.dtype, self.device = (rows, branch.shape[1]), branch.dtype, branch.device
+        self.consumed = False
+
+    def _args(self) -> "library.DeferredNormArgs":
+        b, k = self.branch, self.branch.sink
+        d = library.DeferredNormArgs()
+        d.mode = library.NORM_DEFERRED
+        d.sums, d.n_sums = b.sums.data_ptr(), b.sums.shape[0]
+        d.eps1, d.eps2 = float(k.post.eps), float(k.then.eps)
+        d.n_out = self.shape[0]
+        if self.row_index is not None:
+            d.row_index = self.row_index.data_ptr()
+        if not self.consumed:
+            d.branch_in, d.residual_in, d.residual_out = b.values.data_ptr(), k.residual.data_ptr(), self.residual_out.data_ptr()
+            if self.next_norm is not None:
+                w = self.next_norm.weight
+                d.w_next, d.w_next_dtype, d.off_next = w.data_ptr(), _dtype_code(w), float(self.next_norm.offset)
+                d.scaled_next = self.next_operand.data_ptr()
+        return d
+
+    def materialise(self) -> torch.Tensor:
+        b, k = self.branch, self.branch.sink
+        rows, width = b.shape
+        if not self.consumed:
+            n = self.next_norm
+            library.check(library.load().rdl_stream_rows(
+                _ptr(b.sums), b.sums.shape[0], float(k.post.eps), _ptr(b.values), _ptr(k.residual), _ptr(self.residual_out),
+                _ptr(n.weight) if n else None, _dtype_code(n.weight) if n else 0, float(n.offset) if n else 0.0,
+                _ptr(self.next_operand) if n else None, rows, width, _stream(b.values)))
+            self.consumed = True
+        return norm_residual_norm(self.residual_out, second=k.then, out_dtype=self.dtype, row_index=self.row_index)
+
+
+def scaled_rows(residual: torch.Tensor, norm: NormParams, operand: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The first half of a deferred product's operand, made by a kernel of its own (the first link of a chain):
+    rows 0.. of a bfloat16 [16, width] buffer = residual * (norm.weight + norm.offset)."""
+    rows, width = residual.shape
+    _need(residual.dtype is torch.float32 and residual.is_contiguous() and rows <= DEFERRED_MAX_ROWS, "scaled_rows: up to 8 contiguous float32 rows")
+    if operand is None:
+        operand = torch.empty((2 * DEFERRED_MAX_ROWS, width), dtype=torch.bfloat16, device=residual.device)
+    library.check(library.load().rdl_stream_rows(None, 0, 0.0, None, _ptr(residual), None, _ptr(norm.weight), _dtype_code(norm.weight),
+                                                 float(norm.offset), _ptr(operand), rows, width, _stream(residual)))
+    return operand
+
+
+def deferred_ok(rows: int, width: int, dtype: torch.dtype) -> bool:
+    """Whether rows of this many and this width can take the split form at all."""
+    return dtype is torch.bfloat16 and 0 < rows <= DEFERRED_MAX_ROWS and width % 8 == 0
+
+
+def linear_branch(x: torch.Tensor, weight: torch.Tensor, sink: Optional[BranchSink], status: Optional[torch.Tensor] = None):
+    """x W^T as a branch of a residual stream: a `Branch` where the split form applies, else the plain result."""
+    if sink is None or not (_skinny_ok(x, weight) and deferred_ok(x.shape[0], weight.shape[0], x.dtype)
+                            and tuple(sink.residual.shape) == (x.shape[0], weight.shape[0])):
+        return linear(x, weight, status=status)
+    rows, width = x.shape[0], weight.shape[0]
+    for p in (sink.post, sink.then):
+        _need(p.weight.is_contiguous() and p.weight.numel() == width, f"a norm's weight must hold {width} values")
+    _need(sink.operand.dtype is torch.bfloat16 and tuple(sink.operand.shape) == (2 * DEFERRED_MAX_ROWS, width)
+          and sink.operand.is_contiguous(), "the sink's operand must be bfloat16 [16, width]")
+    values = torch.empty((rows, width), dtype=torch.bfloat16, device=x.device)
+    sums = torch.empty(((width + 15) // 16, 8, 4), dtype=torch.float32, device=x.device)
+    d = library.DeferredNormArgs()
+    d.mode = library.NORM_BRANCH
+    d.sums = sums.data_ptr()
+    d.residual = sink.residual.data_ptr()
+    d.w1, d.w1_dtype, d.off1 = sink.post.weight.data_ptr(), _dtype_code(sink.post.weight), float(sink.post.offset)
+    d.w2, d.w2_dtype, d.off2 = sink.then.weight.data_ptr(), _dtype_code(sink.then.weight), float(sink.then.offset)
+    d.branch, d.scaled = values.data_ptr(), sink.operand.data_ptr() + DEFERRED_MAX_ROWS * width * 2
+    library.check(library.load().rdl_gemm_skinny_norm(None, 0, _ptr(x), _ptr(weight), rows, width, x.shape[1], 0, 0, 0.0,
+                                                      ctypes.byref(d), _status(status), _stream(x)))
+    return Branch(sink, values, sums)
+
+
+def _linear_deferred(x: DeferredRows, weight: torch.Tensor, n_out: int, out_dtype, gated: bool, activation: int, softcap, status):
+    """The product after a deferred norm, or None if this weight cannot take it."""
+    width = x.branch.shape[1]
+    if not (weight.dtype is torch.bfloat16 and weight.is_contiguous() and weight.data_ptr() % 16 == 0 and weight.shape[1] == width):
+        return None
+    out = torch.empty((x.shape[0], n_out), dtype=out_dtype, device=weight.device)
+    d = x._args()
+    library.check(library.load().rdl_gemm_skinny_norm(_ptr(out), _dtype_code(out), _ptr(x.branch.sink.operand), _ptr(weight),
+                                                      x.branch.shape[0], n_out, width, int(gated), activation, float(softcap or 0.0),
+                                                      ctypes.byref(d), _status(status), _stream(out)))
+    x.consumed = True
+    return out
+
+
+def linear(x, weight: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
            softcap: Optional[float] = None, status: Optional[torch.Tensor] = None):
     """x [rows, in] times weight [out, in] transposed; optionally cap * tanh(. / cap) on the result.
+    x may be `DeferredRows` (the rows after a deferred norm).
 
     float32: the library's own FMA kernel (no tensor cores, no reduced-precision mode).
     bfloat16: up to 16 rows (decode) the weight-streaming tensor-core kernels, from 128 rows the TMA +
     tcgen05 kernels, all with float accumulation and the soft-cap in their epilogue.  17 to 127 rows, and
     operands that do not meet the alignment rules, go to a library product (cuBLAS through torch), which
     is what the reference's engine uses for all its products."""
+    if isinstance(x, DeferredRows):
+        _need(softcap is None or out_dtype is torch.float32, "linear: the soft-cap is applied to float32 results")
+        out = _linear_deferred(x, weight, weight.shape[0], out_dtype or x.dtype, False, 0, softcap, status)
+        if out is not None:
+            return out
+        x = x.materialise()
     _need(x.dim() == 2 and weight.dim() == 2 and x.shape[1] == weight.shape[1],
           f"linear: shapes {tuple(x.shape)} and {tuple(weight.shape)} do not fit")
     _need(x.dtype is weight.dtype, f"linear: input is {x.dtype}, weight is {weight.dtype}")
@@ -251,12 +387,17 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: Optional[torch.dtyp
     return out
 
 
-def linear_gated(x: torch.Tensor, weight_gate_up: torch.Tensor, activation: str, status: Optional[torch.Tensor] = None):
+def linear_gated(x, weight_gate_up: torch.Tensor, activation: str, status: Optional[torch.Tensor] = None):
     """act(x Wg^T) * (x Wu^T) for the row-concatenated matrix [Wg; Wu] ([2I, in]) -> [rows, I].
     In bfloat16 this is one kernel (the activation is the product's epilogue); otherwise a product
     and the gated activation kernel."""
     _need(activation in ACTIVATIONS, f"unknown activation '{activation}', known: {sorted(ACTIVATIONS)}")
     _need(weight_gate_up.shape[0] % 2 == 0, "linear_gated: the weight must hold gate rows and as many up rows")
+    if isinstance(x, DeferredRows):
+        out = _linear_deferred(x, weight_gate_up, weight_gate_up.shape[0] // 2, x.dtype, True, ACTIVATIONS[activation], None, status)
+        if out is not None:
+            return out
+        x = x.materialise()
     if _own_bf16_kernel(x, weight_gate_up):
         return _gemm_bf16(x, weight_gate_up, weight_gate_up.shape[0] // 2, x.dtype, True, ACTIVATIONS[activation], None, status)
     return gated_activation(linear(x, weight_gate_up), activation)

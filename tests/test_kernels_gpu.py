@@ -158,6 +158,67 @@ def test_skinny_gemm_with_more_units_than_blocks_fit(m):
     assert_close(ops.linear(x, w[:n2]), ref.linear(x, w[:n2]), torch.bfloat16, what="plain")
 
 
+@pytest.mark.parametrize("m", [1, 3, 8])
+@pytest.mark.parametrize("width,k_in,n_out", [(2304, 2048, 4096), (80, 96, 131), (1000, 264, 20003), (3584, 512, 600)])
+def test_deferred_norms_around_few_row_products(m, width, k_in, n_out):
+    """norm(branch) + stream, norm of the sum, next product - with the two norms split between the epilogue of the
+    product before and the product after (no kernel of their own): the product's result, the updated stream
+    and the next operand's first half against the float64 formulas; a second product on the same rows, a
+    selection of rows, and the same rows made into a tensor."""
+    x, w_p = rnd((m, k_in), torch.bfloat16, 70), rnd((width, k_in), torch.bfloat16, 71, 0.2)
+    h = rnd((m, width), torch.float32, 72, 2.0)
+    post = ops.NormParams(rnd((width,), torch.bfloat16, 73, 0.5), 1e-5, 1.0)
+    then = ops.NormParams(rnd((width,), torch.float32, 74, 0.5), 1e-6, 0.0)       # a norm weight kept in 32 bits
+    nxt = ops.NormParams(rnd((width,), torch.bfloat16, 75, 0.5), 1e-6, 1.0)
+    w_c = rnd((n_out, width), torch.bfloat16, 76, 0.2)
+    w_gu = rnd((2 * 72, width), torch.bfloat16, 77, 0.2)
+    # float64
+    y = x.double() @ w_p.double().t()
+    h_new = h.double() + ref._rms(y, post)
+    xn = ref._rms(h_new, then)
+    z = xn @ w_c.double().t()
+    # split form
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    operand = ops.scaled_rows(h, then)
+    assert_close(operand[:m], h.double() * (then.weight.double() + then.offset), torch.bfloat16, rel=1.0, what="first half of the operand")
+    br = ops.linear_branch(x, w_p, ops.BranchSink(h, post, then, operand), status=status)
+    assert isinstance(br, ops.Branch)
+    h_out, next_operand = torch.empty_like(h), torch.empty_like(operand)
+    d = ops.DeferredRows(br, h_out, nxt, next_operand)
+    got = ops.linear(d, w_c, status=status)
+    assert d.consumed and got.dtype is torch.bfloat16
+    assert_close(got, z, torch.bfloat16, what="product after the norms")
+    assert_close(h_out, h_new, torch.bfloat16, rel=1.0, what="updated stream")       # the branch is rounded to bfloat16 before the sum, as in the one-kernel form
+    assert_close(next_operand[:m], h_new * (nxt.weight.double() + nxt.offset), torch.bfloat16, rel=1.5, what="next operand")
+    # the former route, for the record: a product, the fused norm kernel, a product
+    res = h.clone()
+    old = ops.linear(ops.norm_residual_norm(ops.linear(x, w_p), first=post, residual=res, second=then, out_dtype=torch.bfloat16), w_c)
+    scale = z.abs().max().item()
+    print(f"[deferred norms] m={m} width={width}: error / scale split {(got.double().cpu() - z.cpu()).abs().max().item() / scale:.2e}, "
+          f"separate kernels {(old.double().cpu() - z.cpu()).abs().max().item() / scale:.2e}")
+    # a second product on the same rows (gated, float32 output with soft-cap), then a selection of rows
+    assert_close(ops.linear_gated(d, w_gu, "gelu_pytorch_tanh", status=status),
+                 ref.gated_activation(xn @ w_gu.double().t(), "gelu_pytorch_tanh"), torch.bfloat16, what="gated")
+    assert_close(ops.linear(d, w_c, out_dtype=torch.float32, softcap=3.0, status=status), 3.0 * torch.tanh(z / 3.0),
+                 torch.bfloat16, what="float32 with soft-cap")
+    rows = torch.tensor([m - 1, 0], dtype=torch.int32, device=DEV)
+    h_out2 = torch.empty_like(h)
+    d2 = ops.DeferredRows(br, h_out2, row_index=rows)
+    assert_close(ops.linear(d2, w_c, status=status), z[rows.long()], torch.bfloat16, what="selected rows")
+    assert torch.equal(h_out2, h_out)
+    # the same rows as a tensor (a consumer that cannot take the split form)
+    h_out3, next3 = torch.empty_like(h), torch.empty_like(operand)
+    d3 = ops.DeferredRows(br, h_out3, nxt, next3)
+    assert_close(d3.materialise(), xn, torch.bfloat16, what="materialised")
+    assert_close(h_out3, h_new, torch.bfloat16, rel=1.0, what="updated stream, materialised")
+    assert_close(next3[:m], h_new * (nxt.weight.double() + nxt.offset), torch.bfloat16, rel=1.5, what="next operand, materialised")
+    # a weight the streaming kernel does not take (a view that starts off a 16-byte boundary): the rows are made into a tensor
+    w_odd = torch.empty(n_out * width + 1, dtype=torch.bfloat16, device=DEV)[1:].view(n_out, width).copy_(w_c)
+    d4 = ops.DeferredRows(br, torch.empty_like(h), nxt, torch.empty_like(operand))
+    assert_close(ops.linear(d4, w_odd), z, torch.bfloat16, what="library product after materialising")
+    assert status.item() == 0
+
+
 @pytest.mark.parametrize("m", [128, 129, 200, 2048])
 @pytest.mark.parametrize("n,k", [(256, 64), (384, 96), (131, 80), (2304, 2048), (520, 1160)])
 def test_tcgen05_gemm(m, n, k):
