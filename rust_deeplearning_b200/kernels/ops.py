@@ -232,6 +232,7 @@ def _gemm_bf16(x, weight, n_out, out_dtype, gated, activation, softcap, status):
 # column factors) and applies the row factors in its epilogue.  Three small types carry this through the parts.
 
 DEFERRED_MAX_ROWS = 8
+DEFERRED_NORMS = os.environ.get("RDL_DEFERRED_NORMS", "1") != "0"     # 0: the norm kernels everywhere, for comparison
 
 
 class BranchSink(NamedTuple):
@@ -295,6 +296,16 @@ class DeferredRows:
         return norm_residual_norm(self.residual_out, second=k.then, out_dtype=self.dtype, row_index=self.row_index)
 
 
+def add_branch_(branch: Branch) -> torch.Tensor:
+    """residual += s1 * a' in place: a split branch that no product takes further."""
+    k = branch.sink
+    rows, width = branch.shape
+    library.check(library.load().rdl_stream_rows(_ptr(branch.sums), branch.sums.shape[0], float(k.post.eps), _ptr(branch.values),
+                                                 _ptr(k.residual), _ptr(k.residual), None, 0, 0.0, None, rows, width,
+                                                 _stream(branch.values)))
+    return k.residual
+
+
 def scaled_rows(residual: torch.Tensor, norm: NormParams, operand: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The first half of a deferred product's operand, made by a kernel of its own (the first link of a chain):
     rows 0.. of a bfloat16 [16, width] buffer = residual * (norm.weight + norm.offset)."""
@@ -309,7 +320,7 @@ def scaled_rows(residual: torch.Tensor, norm: NormParams, operand: Optional[torc
 
 def deferred_ok(rows: int, width: int, dtype: torch.dtype) -> bool:
     """Whether rows of this many and this width can take the split form at all."""
-    return dtype is torch.bfloat16 and 0 < rows <= DEFERRED_MAX_ROWS and width % 8 == 0
+    return DEFERRED_NORMS and dtype is torch.bfloat16 and 0 < rows <= DEFERRED_MAX_ROWS and width % 8 == 0
 
 
 def linear_branch(x: torch.Tensor, weight: torch.Tensor, sink: Optional[BranchSink], status: Optional[torch.Tensor] = None):

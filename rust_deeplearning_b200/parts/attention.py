@@ -10,6 +10,8 @@ Interface of a mixer:
   needs() -> (KVRequirement | None, StateRequirement | None)  what it keeps per sequence
   forward(x [rows, hidden] normed, batch: StepBatch, cache: RunCache, run: int) -> [rows, hidden]
 `cache.owns_kv` False means this run reads the keys and values another run wrote.
+Optional offers for the split form of the norms around few-row products (`parts/norm.py`):
+`takes_deferred_rows` (x may be `ops.DeferredRows`) and `delivers_branch` (forward takes `sink`).
 """
 from __future__ import annotations
 
@@ -57,7 +59,10 @@ class Attention:
             return pos.tables(), pos.rotary_dim
         return None, 0
 
-    def forward(self, x: torch.Tensor, batch, cache: RunCache, run: int) -> torch.Tensor:
+    takes_deferred_rows = True     # x goes into the q/k/v (or q) product and nowhere else
+    delivers_branch = True         # the output projection may deliver the result through a stream's sink
+
+    def forward(self, x, batch, cache: RunCache, run: int, sink=None):
         nh, nkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
         pages = self._pages(batch, cache)
         fast = x.dtype is torch.bfloat16 and hd % 16 == 0 and hd <= 256
@@ -85,7 +90,7 @@ class Attention:
                 ab = batch.attention_batch("past", self.window)
                 ctx = ops.attention(q, ab, pages, new_kv=(rows, k_col, v_col),
                                     kind="prefill" if fast and batch.n_tiles else "plain", **common)
-            return ops.linear(ctx, self.w_o)
+            return ops.linear_branch(ctx, self.w_o, sink)
 
         qkv = ops.linear(x, self.w_qkv)
         if batch.is_decode and fast_decode and pages is not None and (tables is not None or self.position is None) \
@@ -140,7 +145,7 @@ class Attention:
                     batch.deferred_writes[run] = write
                 else:
                     write()
-        return ops.linear(ctx, self.w_o)
+        return ops.linear_branch(ctx, self.w_o, sink)
 
 
 def cache_owner(batch, run: int) -> int:

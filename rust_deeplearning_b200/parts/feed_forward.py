@@ -5,7 +5,10 @@ sizes and the activation's name are parameters.  gate and up are one product ove
 row-concatenated matrices; the activation and the product with `up` run in float32.
 
 Interface of a feed-forward: `forward(x [rows, hidden] normed) -> [rows, hidden]`.  Rows are
-independent of each other, so packing and batching never concern it.
+independent of each other, so packing and batching never concern it.  Two optional offers, for the split
+form of the norms around few-row products (`parts/norm.py`): `takes_deferred_rows` (x may be
+`ops.DeferredRows`; it goes into `ops.linear` / `ops.linear_gated` only) and `delivers_branch` (forward takes
+`sink` and ends in `ops.linear_branch`).
 """
 from __future__ import annotations
 
@@ -24,8 +27,11 @@ class GatedMLP:
         self.w_gate_up = torch.cat([w_gate, w_up], dim=0).contiguous()
         self.w_down = w_down
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return ops.linear(ops.linear_gated(x, self.w_gate_up, self.activation), self.w_down)
+    takes_deferred_rows = True     # x goes into one product and nowhere else
+    delivers_branch = True         # the last product may deliver the result through a stream's sink
+
+    def forward(self, x, sink=None):
+        return ops.linear_branch(ops.linear_gated(x, self.w_gate_up, self.activation), self.w_down, sink)
 
 
 def _build_gated_mlp(spec: PartSpec, ctx: BuildContext) -> GatedMLP:

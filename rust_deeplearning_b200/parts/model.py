@@ -46,7 +46,9 @@ class LinearHead:
     def __init__(self, weight: torch.Tensor, softcap: Optional[float]):
         self.weight, self.softcap = weight, softcap
 
-    def forward(self, n: torch.Tensor) -> torch.Tensor:
+    takes_deferred_rows = True      # n goes into one product and nowhere else
+
+    def forward(self, n) -> torch.Tensor:
         return ops.linear(n, self.weight, out_dtype=torch.float32, softcap=self.softcap)
 
 
@@ -66,10 +68,27 @@ class SandwichBlock:
         self.post_ff = norms.get("post_feed_forward")
         self.act_dtype = act_dtype
 
+    @property
+    def first_norm(self):
+        """The norm this block asks the stream for first, if its mixer's first product takes the rows in the
+        split form (`ops.DeferredRows`); the model tells the block before, so that its last product can prepare them."""
+        return self.pre_mixer if getattr(self.mixer, "takes_deferred_rows", False) else None
+
     def forward(self, stream: ResidualStream, batch, cache, run: int):
-        a = self.mixer.forward(stream.normed(self.pre_mixer, self.act_dtype), batch, cache, run)
+        # Parts say what they can do with the split form of the norms (few rows; see ResidualStream):
+        # takes_deferred_rows - x goes into ops.linear / ops.linear_gated only; delivers_branch - forward takes
+        # `sink` and ends in ops.linear_branch.  Everything else runs through the norm kernels.
+        mixer, ff = self.mixer, self.feed_forward
+        m_in, m_out = getattr(mixer, "takes_deferred_rows", False), getattr(mixer, "delivers_branch", False)
+        f_in, f_out = getattr(ff, "takes_deferred_rows", False), getattr(ff, "delivers_branch", False)
+        after, stream.norm_after_block = stream.norm_after_block, None
+        x = stream.normed(self.pre_mixer, self.act_dtype, deferred_ok=m_in, upcoming=self.pre_ff if (m_out and f_in) else None)
+        sink = stream.branch_sink(self.post_mixer, self.pre_ff) if (m_out and f_in) else None
+        a = mixer.forward(x, batch, cache, run, sink=sink) if sink is not None else mixer.forward(x, batch, cache, run)
         stream.add(a, self.post_mixer)
-        f = self.feed_forward.forward(stream.normed(self.pre_ff, self.act_dtype))
+        x = stream.normed(self.pre_ff, self.act_dtype, deferred_ok=f_in, upcoming=after if f_out else None)
+        sink = stream.branch_sink(self.post_ff, after) if (f_out and after is not None) else None
+        f = ff.forward(x, sink=sink) if sink is not None else ff.forward(x)
         stream.add(f, self.post_ff)
 
 
@@ -135,8 +154,15 @@ class Model:
         batch.new_kv.clear()
         stream = ResidualStream(self.embedding.forward(batch.tokens))
         batch.deferred_writes.clear()
+        lazy_head = getattr(self.head, "takes_deferred_rows", False)
         for run, entry in enumerate(self.schedule):
+            # what the stream will be asked for after this block, where the asker's first product takes the split form
+            if run + 1 < len(self.schedule):
+                stream.norm_after_block = getattr(self.layers[self.schedule[run + 1].layer], "first_norm", None)
+            else:
+                stream.norm_after_block = self.final_norm if (lazy_head and batch.n_want) else None
             self.layers[entry.layer].forward(stream, batch, cache.run_cache(run), run)
+            stream.norm_after_block = None
             for owner in [o for o in batch.deferred_writes if self.last_reader.get(o, o) <= run]:
                 batch.deferred_writes.pop(owner)()
         for write in batch.deferred_writes.values():
@@ -146,7 +172,7 @@ class Model:
         if batch.n_want == 0:
             stream.value()
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
-        n = stream.normed_rows(self.final_norm, batch.want_rows, self.dtype)
+        n = stream.normed_rows(self.final_norm, batch.want_rows, self.dtype, deferred_ok=lazy_head)
         return self.head.forward(n)
 
 
