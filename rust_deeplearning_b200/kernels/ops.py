@@ -232,6 +232,10 @@ def _gemm_bf16(x, weight, n_out, out_dtype, gated, activation, softcap, status):
 # column factors) and applies the row factors in its epilogue.  Three small types carry this through the parts.
 
 DEFERRED_MAX_ROWS = 8
+# A very wide product (the output head) runs for most of its time in its steady state, where multiplying 16 rows
+# instead of 8 costs more than the two small kernels it saves (256,000 outputs: 230 against 165 us): its rows are
+# made into a tensor first.
+DEFERRED_MAX_OUTPUTS = 65536
 DEFERRED_NORMS = os.environ.get("RDL_DEFERRED_NORMS", "1") != "0"     # 0: the norm kernels everywhere, for comparison
 
 
@@ -351,6 +355,8 @@ def _linear_deferred(x: DeferredRows, weight: torch.Tensor, n_out: int, out_dtyp
     """The product after a deferred norm, or None if this weight cannot take it."""
     width = x.branch.shape[1]
     if not (weight.dtype is torch.bfloat16 and weight.is_contiguous() and weight.data_ptr() % 16 == 0 and weight.shape[1] == width):
+        return None
+    if n_out > DEFERRED_MAX_OUTPUTS:
         return None
     out = torch.empty((x.shape[0], n_out), dtype=out_dtype, device=weight.device)
     d = x._args()
