@@ -9,6 +9,7 @@
 // exponentials, row maxima and row sums are float.
 #include "api.h"
 #include "common.cuh"
+#include "launch.cuh"
 
 namespace {
 
@@ -77,6 +78,8 @@ __global__ void __launch_bounds__(NTHREADS) attention_prefill_kernel(AttentionAr
     const __nv_bfloat16* vcache = (const __nv_bfloat16*)a.v_cache;
     const uint4 zero4 = make_uint4(0, 0, 0, 0);
 
+    rdl_grid_wait();               // the batch description above is constant; the rows come from the kernel before
+    rdl_grid_launch_dependents();
     // ---- query tile ----
     for (int idx = tid; idx < BM * CH; idx += NTHREADS) {
         const int r = idx / CH, c = idx - r * CH;
@@ -256,8 +259,7 @@ int launch_prefill(const AttentionArgs* a, cudaStream_t st) {
         opted = true;
     }
     dim3 grid(a->n_tiles, a->n_heads);
-    attention_prefill_kernel<HD><<<grid, NTHREADS, smem, st>>>(*a);
-    RDL_CHECK_LAUNCH("attention_prefill");
+    RDL_CHECK_EX(rdl_launch(attention_prefill_kernel<HD>, grid, dim3(NTHREADS), (size_t)smem, st, *a), "attention_prefill");
     return 0;
 }
 

@@ -17,6 +17,7 @@
 #include <cuda.h>
 
 #include "api.h"
+#include "launch.cuh"
 #include "common.cuh"
 
 namespace {
@@ -168,6 +169,9 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_s = tmem_slot, tmem_o = tmem_slot + KN;
+    // barriers and tensor memory were set up while the kernel before (the rotation) was still running
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
 
     // the tiles of keys this block visits: positions [kv_first, p_last], 64 at a time
     const int p_first = q0, p_last = q0 + rows - 1;
@@ -421,8 +425,7 @@ int launch_tc(dim3 grid, int smem, cudaStream_t st, const CUtensorMap& map_q, co
         RDL_CUDA(cudaFuncSetAttribute(attention_tc_kernel<DB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "attention_prefill_tc");
         opted = true;
     }
-    attention_tc_kernel<DB><<<grid, ATC_THREADS, smem, st>>>(map_q, map_kv, t);
-    RDL_CHECK_LAUNCH("attention_prefill_tc");
+    RDL_CHECK_EX(rdl_launch(attention_tc_kernel<DB>, grid, dim3(ATC_THREADS), (size_t)smem, st, map_q, map_kv, t), "attention_prefill_tc");
     return 0;
 }
 

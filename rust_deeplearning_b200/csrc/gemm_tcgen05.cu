@@ -30,6 +30,7 @@
 #include "activations.cuh"
 #include "api.h"
 #include "common.cuh"
+#include "launch.cuh"
 
 namespace {
 
@@ -255,6 +256,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_kernel(const __grid_con
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_slot;
     bool ok = true;
+    // barriers and tensor memory were set up while the kernel before was still running; its results are needed from here on
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -420,6 +424,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_slot;
     bool ok = true;
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -540,8 +546,7 @@ int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs& a, cud
     const long long tiles = (long long)((a.N + BN - 1) / BN) * ((a.M + MT * BM - 1) / (MT * BM));
     RDL_REQUIRE(tiles <= 0x7fffffffLL, "gemm_tc: %lld tiles exceed the grid limit", tiles);
     dim3 grid((unsigned)tiles);
-    gemm_tc_kernel<BN, GATED, MT><<<grid, TC_THREADS, smem, st>>>(mx, mw, a);
-    RDL_CHECK_LAUNCH("gemm_tc");
+    RDL_CHECK_EX(rdl_launch(gemm_tc_kernel<BN, GATED, MT>, grid, dim3(TC_THREADS), (size_t)smem, st, mx, mw, a), "gemm_tc");
     return 0;
 }
 
@@ -562,8 +567,7 @@ int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const TcArgs& a, c
         pairs_that_fit = sms / 2 > 0 ? sms / 2 : 1;
     }
     const int pairs = tiles < pairs_that_fit ? (int)tiles : pairs_that_fit;
-    gemm_tc_pair_kernel<GATED, NACC><<<dim3((unsigned)(2 * pairs)), PAIR_THREADS, smem, st>>>(mx, mw, a);
-    RDL_CHECK_LAUNCH("gemm_tc");
+    RDL_CHECK_EX(rdl_launch(gemm_tc_pair_kernel<GATED, NACC>, dim3((unsigned)(2 * pairs)), dim3(PAIR_THREADS), (size_t)smem, st, mx, mw, a), "gemm_tc");
     return 0;
 }
 
