@@ -115,6 +115,14 @@ __device__ __forceinline__ bool st_wait(uint32_t bar, uint32_t parity, long long
     }
     return true;
 }
+// A norm weight's element as raw bits, and its value: a load whose result is not used at once does not hold its
+// thread up, so the prologues below ask for everything first and convert afterwards.
+__device__ __forceinline__ uint32_t raw_load(const void* p, long long i, int dtype) {
+    return dtype == RDL_BF16 ? (uint32_t)((const unsigned short*)p)[i] : ((const uint32_t*)p)[i];
+}
+__device__ __forceinline__ float raw_value(uint32_t bits, int dtype) {
+    return dtype == RDL_BF16 ? __uint_as_float(bits << 16) : __uint_as_float(bits);
+}
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -219,26 +227,32 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(const __grid
         const DeferredNormArgs& d = a.d;
         const int tid = threadIdx.x;
         long long slice_e = -1;
-        float slice_h = 0.f, slice_a = 0.f, slice_w = 0.f;
+        float slice_h = 0.f;
+        uint32_t slice_a = 0u, slice_w = 0u;               // raw bits until the stores
         bool first_unit = true;
         if constexpr (MODE == 2) {
             load_x(kw, xcur);              // the first tile's rows are on their way while the sums are added up
             const long long total = (long long)a.M * K, per = (total + gridDim.x - 1) / gridDim.x;
-            auto slice_load = [&](long long e) {
-                slice_h = d.residual_in[e];
-                slice_a = __bfloat162float(((const __nv_bfloat16*)d.branch_in)[e]);
-                slice_w = d.scaled_next ? rdl_load(d.w_next, e % K, d.w_next_dtype) + d.off_next : 0.f;
-            };
             if (d.residual_out || d.scaled_next) {
                 const long long e = blockIdx.x * per + tid;
-                if (tid < per && e < total) { slice_e = e; slice_load(e); }
+                if (tid < per && e < total) {
+                    slice_e = e;
+                    slice_h = d.residual_in[e];
+                    slice_a = raw_load(d.branch_in, e, RDL_BF16);
+                    if (d.scaled_next) slice_w = raw_load(d.w_next, e % K, d.w_next_dtype);
+                }
             }
-            // the partial sums: thread (part, m) adds the units part, part + 32, ... of row m
+            // the partial sums: thread (part, m) adds the units part, part + 32, ... of row m, eight loads in flight at a time
             const int m = tid & 7, part = tid >> 3;
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int u = part; u < d.n_sums; u += 32) {
-                const float4 v = __ldcg(reinterpret_cast<const float4*>(d.sums) + u * 8 + m);
-                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            for (int u0 = part; u0 < d.n_sums; u0 += 8 * 32) {
+                float4 v[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    v[i] = u0 + 32 * i < d.n_sums ? __ldcg(reinterpret_cast<const float4*>(d.sums) + (u0 + 32 * i) * 8 + m)
+                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { acc.x += v[i].x; acc.y += v[i].y; acc.z += v[i].z; acc.w += v[i].w; }
             }
             sum_part[part][m] = acc;
             asm volatile("bar.sync 1, %0;" ::"n"(ST_WARPS * 32) : "memory");
@@ -263,13 +277,14 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(const __grid
 #pragma unroll
             for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
             // MODE 1: thread (m, r) of the epilogue asks for its element of the stream and its two norm weights now
-            float br_h = 0.f, br_g1 = 0.f, br_g2 = 0.f;
+            float br_h = 0.f;
+            uint32_t br_w1 = 0u, br_w2 = 0u;                 // raw bits until the epilogue
             if constexpr (MODE == 1) {
                 const int m = tid >> 4, n = unit * ROWS + (tid & 15);
                 if (tid < 8 * ROWS && m < a.M && n < a.N) {
                     br_h = d.residual[(long long)m * a.N + n];
-                    br_g1 = rdl_load(d.w1, n, d.w1_dtype) + d.off1;
-                    br_g2 = rdl_load(d.w2, n, d.w2_dtype) + d.off2;
+                    br_w1 = raw_load(d.w1, n, d.w1_dtype);
+                    br_w2 = raw_load(d.w2, n, d.w2_dtype);
                 }
             }
             for (int tk = 0; tk < tiles_per_unit; ++tk) {
@@ -318,6 +333,7 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(const __grid
 #pragma unroll
                     for (int w = 0; w < ST_WARPS; ++w) y += partial[w][0][m * ROWS + r];
                     if (!ok) y = 0.f;
+                    const float br_g1 = raw_value(br_w1, d.w1_dtype) + d.off1, br_g2 = raw_value(br_w2, d.w2_dtype) + d.off2;
                     const __nv_bfloat16 a1b = __float2bfloat16_rn(y * br_g1);
                     const float a1 = __bfloat162float(a1b);                  // what the stream will add, s1 times
                     float s0 = y * y, s1 = br_h * br_h, s2 = br_h * a1, s3 = a1 * a1;
@@ -341,14 +357,15 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(const __grid
                     const long long total = (long long)a.M * K, per = (total + gridDim.x - 1) / gridDim.x;
                     const long long end = (blockIdx.x + 1) * per < total ? (blockIdx.x + 1) * per : total;
                     for (long long e = slice_e; e >= 0 && e < end;) {
-                        const float hn = slice_h + row_scale[e / K].x * slice_a;
+                        const float hn = slice_h + row_scale[e / K].x * raw_value(slice_a, RDL_BF16);
                         if (d.residual_out) d.residual_out[e] = hn;
-                        if (d.scaled_next) ((__nv_bfloat16*)d.scaled_next)[e] = __float2bfloat16_rn(hn * slice_w);
+                        if (d.scaled_next)
+                            ((__nv_bfloat16*)d.scaled_next)[e] = __float2bfloat16_rn(hn * (raw_value(slice_w, d.w_next_dtype) + d.off_next));
                         e += ST_WARPS * 32;
                         if (e < end) {
                             slice_h = d.residual_in[e];
-                            slice_a = __bfloat162float(((const __nv_bfloat16*)d.branch_in)[e]);
-                            slice_w = d.scaled_next ? rdl_load(d.w_next, e % K, d.w_next_dtype) + d.off_next : 0.f;
+                            slice_a = raw_load(d.branch_in, e, RDL_BF16);
+                            if (d.scaled_next) slice_w = raw_load(d.w_next, e % K, d.w_next_dtype);
                         }
                     }
                 }
