@@ -128,8 +128,9 @@ typedef struct {
     const void* w1; int w1_dtype; float off1;
     const void* w2; int w2_dtype; float off2;
     void* branch;                    // out: a', bfloat16 [rows][n]
-    void* scaled;                    // out: at, bfloat16 [rows][n] (rows 8.. of C's operand)
-    // C; its x is bfloat16 [16][k]: rows 0..7 ht, rows 8..15 at
+    void* scaled;                    // out: at, bfloat16 [rows][n] (the second half of C's operand)
+    // C; its x is bfloat16 [16][k]: rows 0.. ht, and at from row 8 on (from row 4 on with up to 4 rows: the
+    // halves then share one 8-row fragment of the tensor-core product)
     float eps1, eps2;
     const void* branch_in;           // a' [rows][k]
     const float* residual_in;        // h [rows][k]

@@ -131,7 +131,9 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
 
 template <int NT, bool GATED, int KU, int MODE>
 __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(const __grid_constant__ SkinnyArgs a, int stages, int* status) {
-    static_assert(MODE == 0 || (MODE == 1 && NT == 1 && !GATED) || (MODE == 2 && NT == 2), "deferred norms: P has 8 rows, C an operand of 16");
+    // MODE 2 with NT == 1: up to 4 rows; both halves of the operand then share one fragment (rows 0..3 and 4..7)
+    static_assert(MODE == 0 || (MODE == 1 && NT == 1 && !GATED) || MODE == 2, "deferred norms: up to 8 rows");
+    constexpr bool PACKED = MODE == 2 && NT == 1;
     constexpr int ST_KT = st_kt(KU), ST_PITCH = st_pitch(KU), ST_TILE_BYTES = st_tile_bytes(KU), KW = 32 * KU;
     extern __shared__ __align__(128) unsigned char st_tiles[];
     __shared__ __align__(8) unsigned long long full_bar[ST_MAX_STAGES], empty_bar[ST_MAX_STAGES];
@@ -202,7 +204,8 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(const __grid
         bool x_ok[NT];
 #pragma unroll
         for (int i = 0; i < NT; ++i) {
-            x_ok[i] = MODE == 2 ? g < a.M : i * 8 + g < a.M;      // MODE 2: both halves of the operand have M rows
+            // MODE 2: both halves of the operand have M rows (packed: the halves are rows 0..3 and 4..7 of one fragment)
+            x_ok[i] = PACKED ? (g & 3) < a.M : (MODE == 2 ? g < a.M : i * 8 + g < a.M);
             xrow[i] = a.x + (long long)(i * 8 + g) * K;
         }
         const uint4 zero4 = make_uint4(0, 0, 0, 0);
@@ -231,7 +234,7 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(const __grid
         uint32_t slice_a = 0u, slice_w = 0u;               // raw bits until the stores
         bool first_unit = true;
         if constexpr (MODE == 2) {
-            load_x(kw, xcur);              // the first tile's rows are on their way while the sums are added up
+            if (!X_AHEAD) load_x(kw, xcur);              // the first tile's rows are on their way while the sums are added up
             const long long total = (long long)a.M * K, per = (total + gridDim.x - 1) / gridDim.x;
             if (d.residual_out || d.scaled_next) {
                 const long long e = blockIdx.x * per + tid;
@@ -290,7 +293,7 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(const __grid
             for (int tk = 0; tk < tiles_per_unit; ++tk) {
                 // the activations of the tile after this one (the next unit starts again at k = 0)
                 if (X_AHEAD) load_x((tk + 1 < tiles_per_unit ? (tk + 1) * ST_KT : 0) + kw, reinterpret_cast<uint4 (&)[NT][KU]>(xnext));
-                else if (!(MODE == 2 && tk == 0 && unit == (int)blockIdx.x)) load_x(tk * ST_KT + kw, xcur);
+                else if (!(MODE == 2 && tk == 0 && unit == (int)blockIdx.x)) load_x(tk * ST_KT + kw, xcur);     // (that tile's rows were asked for above)
                 st_wait(full_s + 8 * s, round & 1, a.wait_cycles, gave_up_v);
                 const int kb = tk * ST_KT + kw;
                 if (kb < K) {
@@ -375,13 +378,15 @@ __global__ void __launch_bounds__(ST_THREADS, 2) gemm_stream_kernel(const __grid
                     const int m = d.row_index ? d.row_index[j] : j;
                     if (n >= a.N || m < 0 || m >= a.M) continue;
                     const float2 sc = row_scale[m];
-                    const int slot = m * ROWS + r;
+                    // the stream's half and the branch's half of the operand: two fragments, or rows m and m + 4 of one
+                    const int slot = m * ROWS + r, slot_a = PACKED ? slot + 4 * ROWS : slot;
+                    constexpr int IA = PACKED ? 0 : NT - 1;
                     float h0 = 0.f, a0 = 0.f, h1 = 0.f, a1 = 0.f;
 #pragma unroll
                     for (int w = 0; w < ST_WARPS; ++w) {
                         h0 += partial[w][0][slot];
-                        a0 += partial[w][1][slot];
-                        if (GATED) { h1 += partial[w][0][slot + 8]; a1 += partial[w][1][slot + 8]; }
+                        a0 += partial[w][IA][slot_a];
+                        if (GATED) { h1 += partial[w][0][slot + 8]; a1 += partial[w][IA][slot_a + 8]; }
                     }
                     float y = sc.y * (h0 + sc.x * a0);
                     if (GATED) y = rdl_activation(y, a.activation) * (sc.y * (h1 + sc.x * a1));
@@ -495,8 +500,13 @@ extern "C" int rdl_gemm_skinny_norm(void* out, int out_dtype, const void* x, con
         RDL_REQUIRE(!side || (norm->branch_in && norm->residual_in), "gemm_skinny_norm: the stream's update needs the branch and the stream");
         RDL_REQUIRE(!norm->residual_out || norm->residual_out != norm->residual_in, "gemm_skinny_norm: the updated stream needs a buffer of its own (other blocks still read the old one)");
         RDL_REQUIRE(!norm->scaled_next || (norm->w_next && rdl_valid_dtype(norm->w_next_dtype)), "gemm_skinny_norm: the next operand needs the next norm's weight");
-        if (gated) launch_stream<2, true, 2>(a, status, st);
-        else launch_stream<2, false, 2>(a, status, st);
+        if (m <= 4) {       // both halves of the operand in one fragment: rows 0..3 and 4..7 of x
+            if (gated) launch_stream<1, true, 2>(a, status, st);
+            else launch_stream<1, false, 2>(a, status, st);
+        } else {
+            if (gated) launch_stream<2, true, 2>(a, status, st);
+            else launch_stream<2, false, 2>(a, status, st);
+        }
     } else {
         RDL_REQUIRE(false, "gemm_skinny_norm: unknown mode %d", norm->mode);
     }

@@ -244,12 +244,12 @@ class BranchSink(NamedTuple):
     residual: torch.Tensor     # float32 [rows, width]: the stream the branch will be added to
     post: NormParams           # the norm of the branch before the sum
     then: NormParams           # the norm the sum is asked for next
-    operand: torch.Tensor      # bfloat16 [16, width]: rows 0..7 are (by the time the product runs) residual * (then.weight + then.offset)
+    operand: torch.Tensor      # bfloat16 [16, width]: its first rows are (by the time the product runs) residual * (then.weight + then.offset)
 
 
 class Branch:
     """A branch delivered through a BranchSink: a' = y (post.weight + post.offset) [rows, width] in bfloat16,
-    the partial sums [units, 8, 4] and, in rows 8.. of the sink's operand, a' (then.weight + then.offset)."""
+    the partial sums [units, 8, 4] and, in the operand's second half (`second_half_row`), a' (then.weight + then.offset)."""
 
     def __init__(self, sink: BranchSink, values: torch.Tensor, sums: torch.Tensor):
         self.sink, self.values, self.sums = sink, values, sums
@@ -322,6 +322,12 @@ def scaled_rows(residual: torch.Tensor, norm: NormParams, operand: Optional[torc
     return operand
 
 
+def second_half_row(rows: int) -> int:
+    """The operand's row at which the branch's half starts: 8, or 4 with up to 4 rows (the two halves then share one
+    8-row fragment of the tensor-core product and cost what 8 plain rows cost)."""
+    return 4 if rows <= 4 else DEFERRED_MAX_ROWS
+
+
 def deferred_ok(rows: int, width: int, dtype: torch.dtype) -> bool:
     """Whether rows of this many and this width can take the split form at all."""
     return DEFERRED_NORMS and dtype is torch.bfloat16 and 0 < rows <= DEFERRED_MAX_ROWS and width % 8 == 0
@@ -345,7 +351,7 @@ def linear_branch(x: torch.Tensor, weight: torch.Tensor, sink: Optional[BranchSi
     d.residual = sink.residual.data_ptr()
     d.w1, d.w1_dtype, d.off1 = sink.post.weight.data_ptr(), _dtype_code(sink.post.weight), float(sink.post.offset)
     d.w2, d.w2_dtype, d.off2 = sink.then.weight.data_ptr(), _dtype_code(sink.then.weight), float(sink.then.offset)
-    d.branch, d.scaled = values.data_ptr(), sink.operand.data_ptr() + DEFERRED_MAX_ROWS * width * 2
+    d.branch, d.scaled = values.data_ptr(), sink.operand.data_ptr() + second_half_row(rows) * width * 2
     library.check(library.load().rdl_gemm_skinny_norm(None, 0, _ptr(x), _ptr(weight), rows, width, x.shape[1], 0, 0, 0.0,
                                                       ctypes.byref(d), _status(status), _stream(x)))
     return Branch(sink, values, sums)
