@@ -171,3 +171,24 @@ def test_the_engine_decodes_without_norm_kernels(name, monkeypatch):
         mh.assert_logits(torch.cat(rows), want[30:40], "bfloat16", f"{name}, split form {split}")
         eng.release(slot)
     assert counts[True] < counts[False], counts
+
+
+@pytest.mark.parametrize("name", ["A", "D"])
+def test_seven_sequences_decode_together(name):
+    """Five to eight rows take the 16-row operand (up to four share one fragment): seven sequences of unequal length,
+    single-token steps through the captured graph, every logit against the plain implementation."""
+    import numpy as np
+    import model_helpers as mh
+    import tiny_configs
+    cfg = tiny_configs.config(name)[0]
+    V = cfg["vocab_size"]
+    seqs = [mh.prompt(810 + i, 12 + 5 * i, V) for i in range(7)]
+    want = [mh.plain_logits(name, s) for s in seqs]
+    eng = mh.engine(name, "bfloat16", max_seqs=8)
+    slots = [eng.new_sequence() for _ in seqs]
+    cut = [len(s) - 6 for s in seqs]
+    eng.step(slots, [s[:c] for s, c in zip(seqs, cut)], [[] for _ in seqs])
+    for k in range(6):
+        got = eng.step(slots, [[s[c + k]] for s, c in zip(seqs, cut)], "last")
+        mh.assert_logits(got, np.stack([w[c + k] for w, c in zip(want, cut)]), "bfloat16", f"{name}, step {k}")
+    assert eng.graph_replays > 0
