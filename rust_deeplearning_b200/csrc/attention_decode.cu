@@ -39,7 +39,6 @@ namespace {
 constexpr int DEC_THREADS = 128;
 constexpr int DEC_WARPS = DEC_THREADS / 32;
 constexpr int QROWS = 8;                          // most query heads per kv head: the columns of one score product
-constexpr int DEC_CLUSTER = 8;                    // blocks of a (token, kv head) in the cluster form
 
 __device__ __forceinline__ float tanh_fast(float x) {
     float y;
@@ -105,48 +104,15 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     return true;
 }
 
-// Cluster helpers: the rank of this block, the cluster-wide barrier (release / acquire), a float4 from another
-// block's shared memory.
-__device__ __forceinline__ uint32_t cl_rank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void cl_sync() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ uint32_t cl_map(const void* smem_ptr, uint32_t rank) {
-    uint32_t a = (uint32_t)__cvta_generic_to_shared(smem_ptr), r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ float4 cl_ld_f32x4(uint32_t addr) {
-    float4 v;
-    asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
-    return v;
-}
-__device__ __forceinline__ float cl_ld_f32(uint32_t addr) {
-    float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
-    return v;
-}
-
 // HD: head_dim padded to 64, 128 or 256 (head_dim itself is a multiple of 16).  EXACT: head_dim == HD;
 // row sizes and the swizzle are then compile-time constants and a fragment's address is a register
 // plus an immediate.
-// CLUSTER: the blocks of a (token, kv head) form one thread-block cluster (grid.x of them).  They share the
-// token's pages evenly, whatever its length (no run is longer than another by more than a page), and their
-// results are merged through distributed shared memory behind one cluster barrier: no scratch, no counter,
-// no trip to memory between the last page and the output.  Every block of the cluster reaches both barriers,
-// with or without pages of its own and whatever became of its waits.
-template <int HD, bool EXACT, bool CLUSTER>
+template <int HD, bool EXACT>
 __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(AttentionArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) unsigned long long bar_storage[3];     // one per tile of the ring
     __shared__ float sm_m[DEC_WARPS][QROWS], sm_l[DEC_WARPS][QROWS];
     __shared__ int s_flag;
-    __shared__ float res_m[QROWS], res_l[QROWS];   // CLUSTER: the block's maximum and normaliser per head
     __shared__ int s_gave_up;      // a wait ran out: the block no longer waits or issues, and its result is void
     // new_rows: the rotated query heads of the group, then the new key row and the new value row
     __shared__ __align__(16) __nv_bfloat16 new_s[(QROWS + 2) * 256];
@@ -163,24 +129,13 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
         asm volatile("prefetch.global.L1 [%0];" ::"l"(a.tables + (long long)t * a.table_width + guess));
     }
     const int seq = a.tok_seq[t], p = a.tok_pos[t];
-    if (p < 0) return;  // a padding row of a fixed-size batch (the same for every block of a cluster)
+    if (p < 0) return;  // a padding row of a fixed-size batch
     const int lo = first_key(p, a.window);
-    int n_splits, k_begin, k_end;
-    if (CLUSTER) {
-        // the token's pages, shared out evenly among the cluster's blocks
-        const int pg_lo = lo / ps, n_pages = p / ps - pg_lo + 1;
-        const int per = (n_pages + (int)gridDim.x - 1) / (int)gridDim.x;
-        n_splits = (n_pages + per - 1) / per;
-        k_begin = max(lo, (pg_lo + sp * per) * ps);
-        k_end = min(p + 1, (pg_lo + (sp + 1) * per) * ps);
-    } else {
-        const int split0 = lo / a.keys_per_split;
-        n_splits = p / a.keys_per_split - split0 + 1;
-        if (sp >= n_splits) return;
-        k_begin = max(lo, (split0 + sp) * a.keys_per_split);
-        k_end = min(p + 1, (split0 + sp + 1) * a.keys_per_split);   // exclusive
-    }
-    const bool work = sp < n_splits;               // CLUSTER: a block without pages still takes part in the merge
+    const int split0 = lo / a.keys_per_split;
+    const int n_splits = p / a.keys_per_split - split0 + 1;
+    if (sp >= n_splits) return;
+    const int k_begin = max(lo, (split0 + sp) * a.keys_per_split);
+    const int k_end = min(p + 1, (split0 + sp + 1) * a.keys_per_split);   // exclusive
     const int* table = a.tables + (long long)seq * a.table_width;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int quad = lane >> 2, tq = lane & 3;
@@ -195,7 +150,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
     const uint32_t tiles_s = (uint32_t)__cvta_generic_to_shared(smem);
     const uint32_t bars = (uint32_t)__cvta_generic_to_shared(&bar_storage[0]);
 
-    const int page_first = work ? k_begin / ps : 0, page_last = work ? (k_end - 1) / ps : -1;
+    const int page_first = k_begin / ps, page_last = (k_end - 1) / ps;
     // Ask L2 for the run's pages now.  Nothing read up to here was written by an earlier kernel of this
     // step (the batch description and page lists come from the host; the newest row of the last page is
     // written by the kernel before this one, but a prefetch only moves lines into L2, where that write
@@ -241,7 +196,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
     const bool fuse = a.new_rows != 0;
     const bool early = fuse || (a.seq_past != nullptr && (page_first + 1) * ps <= a.seq_past[seq] &&
                                 (a.window <= 0 || t == a.seq_start[seq + 1] - 1));
-    if (early && work && tid == 0) {
+    if (early && tid == 0) {
         issue(0);
         issue(1);
         if (fuse && n_tiles > 2) issue(2);       // with new_rows no page of the run changes any more
@@ -249,7 +204,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
     rdl_grid_wait();
     rdl_grid_launch_dependents();
     const bool has_new = fuse && sp == n_splits - 1;          // this block's run ends with the token's own position
-    if (fuse && work) {
+    if (fuse) {
         // 16-byte chunks of the group's query heads and, in the block that reads position p, of the new key
         // and value rows: rotate (queries and key), keep in shared memory, write the new rows to the cache
         const int half = a.rotary_dim >> 1;
@@ -345,7 +300,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
         return vb[0] - va[0] + vr * row_bytes + rdl_swizzled_chunk(vr, 2 * db + ((lane >> 3) & 1), chunks) * 16;
     };
 
-    if (tid == 0 && work) {
+    if (tid == 0) {
         if (!early) {
             issue(0);
             issue(1);
@@ -513,11 +468,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
             osum.z = fmaf(wt, v.z, osum.z); osum.w = fmaf(wt, v.w, osum.w);
             lsum = fmaf(wt, sm_l[w][h], lsum);
         }
-        if (CLUSTER) {
-            // the block's result takes the place of the first warp's (this thread alone reads and writes these four)
-            *reinterpret_cast<float4*>(sm_o + h * HD + d) = osum;
-            if (d == 0) { res_m[h] = M; res_l[h] = lsum; }
-        } else if (n_splits == 1) {
+        if (n_splits == 1) {
             const float inv = 1.0f / lsum;
             __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(out + (long long)(g * G + h) * hd + d);
             o2[0] = __floats2bfloat162_rn(osum.x * inv, osum.y * inv);
@@ -527,42 +478,6 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(Attention
             *reinterpret_cast<float4*>(partials + run * hd + d) = osum;
             if (d == 0) *reinterpret_cast<float2*>(stats + run * 2) = make_float2(M, lsum);
         }
-    }
-    if (CLUSTER) {
-        // ---- the cluster's first block merges the blocks' results, read from their shared memory ----
-        cl_sync();
-        if (cl_rank() == 0) {
-            for (int idx = tid; idx < G * hd / 4; idx += DEC_THREADS) {
-                const int h = (idx * 4) / hd, d = idx * 4 - h * hd;
-                float4 part[DEC_CLUSTER];
-                float pm[DEC_CLUSTER], pl[DEC_CLUSTER];
-#pragma unroll
-                for (int r = 0; r < DEC_CLUSTER; ++r) {
-                    const bool there = r < n_splits;
-                    part[r] = there ? cl_ld_f32x4(cl_map(sm_o + h * HD + d, r)) : make_float4(0.f, 0.f, 0.f, 0.f);
-                    pm[r] = there ? cl_ld_f32(cl_map(&res_m[h], r)) : -INFINITY;
-                    pl[r] = there ? cl_ld_f32(cl_map(&res_l[h], r)) : 0.f;
-                }
-                float M = -INFINITY;
-#pragma unroll
-                for (int r = 0; r < DEC_CLUSTER; ++r) M = fmaxf(M, pm[r]);
-                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                float L = 0.f;
-#pragma unroll
-                for (int r = 0; r < DEC_CLUSTER; ++r) {
-                    const float wt = pm[r] == -INFINITY ? 0.f : exp2f(pm[r] - M);
-                    acc.x = fmaf(wt, part[r].x, acc.x); acc.y = fmaf(wt, part[r].y, acc.y);
-                    acc.z = fmaf(wt, part[r].z, acc.z); acc.w = fmaf(wt, part[r].w, acc.w);
-                    L = fmaf(wt, pl[r], L);
-                }
-                const float inv = 1.0f / L;
-                __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(out + (long long)(g * G + h) * hd + d);
-                o2[0] = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
-                o2[1] = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
-            }
-        }
-        cl_sync();             // no block leaves while the first may still read its shared memory
-        return;
     }
     if (n_splits == 1) return;
 
@@ -659,37 +574,17 @@ int launch_decode(const AttentionArgs* a, cudaStream_t st) {
     if (runs > smem) smem = runs;
     RDL_REQUIRE(smem <= 200 * 1024, "attention_decode: page_size %d x head_dim %d needs %d bytes of shared memory, limit is 204800",
                 a->page_size, a->head_dim, smem);
-    static int granted = 32 * 1024;      // above this the kernels (which also have a few KB of static shared memory) opt in
+    static int granted = 32 * 1024;      // above this the kernel (which also has a few KB of static shared memory) opts in
     if (smem > granted) {
-        RDL_CUDA(cudaFuncSetAttribute(attention_decode_kernel<HD, EXACT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
-                 "attention_decode");
-        RDL_CUDA(cudaFuncSetAttribute(attention_decode_kernel<HD, EXACT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+        RDL_CUDA(cudaFuncSetAttribute(attention_decode_kernel<HD, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
                  "attention_decode");
         granted = smem;
     }
+    dim3 grid(a->max_splits, a->n_kv_heads, a->n_tokens);
     AttentionArgs b = *a;
     b.wait_cycles = rdl_wait_cycles_for(RDL_FAULT_ATTENTION_DECODE);
     b.test_extra_tx = rdl_test_extra_tx_for(RDL_FAULT_ATTENTION_DECODE);
-    if (a->keys_per_split == 0) {
-        // the cluster form: DEC_CLUSTER blocks per (token, kv head)
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(DEC_CLUSTER, a->n_kv_heads, a->n_tokens);
-        cfg.blockDim = dim3(DEC_THREADS);
-        cfg.dynamicSmemBytes = (size_t)smem;
-        cfg.stream = st;
-        cudaLaunchAttribute attr[2];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = DEC_CLUSTER;
-        attr[0].val.clusterDim.y = attr[0].val.clusterDim.z = 1;
-        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[1].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = g_rdl_programmatic_launch ? 2 : 1;
-        RDL_CHECK_EX(cudaLaunchKernelEx(&cfg, attention_decode_kernel<HD, EXACT, true>, b), "attention_decode");
-        return 0;
-    }
-    dim3 grid(a->max_splits, a->n_kv_heads, a->n_tokens);
-    RDL_CHECK_EX(rdl_launch(attention_decode_kernel<HD, EXACT, false>, grid, dim3(DEC_THREADS), (size_t)smem, st, b), "attention_decode");
+    RDL_CHECK_EX(rdl_launch(attention_decode_kernel<HD, EXACT>, grid, dim3(DEC_THREADS), (size_t)smem, st, b), "attention_decode");
     return 0;
 }
 
@@ -714,19 +609,16 @@ extern "C" int rdl_attention_decode(const AttentionArgs* a, void* stream) {
     RDL_REQUIRE(a->tables && a->k_cache && a->v_cache, "attention_decode: needs a cache");
     RDL_REQUIRE(a->page_size % 16 == 0 && a->page_size <= 16 * DEC_WARPS,
                 "attention_decode: page_size %d must be a multiple of 16 and at most %d", a->page_size, 16 * DEC_WARPS);
-    RDL_REQUIRE(a->keys_per_split >= 0 && (a->keys_per_split == 0 || a->keys_per_split % a->page_size == 0),
-                "attention_decode: keys_per_split %d must be a whole number of pages of %d (or 0: the cluster form)", a->keys_per_split, a->page_size);
+    RDL_REQUIRE(a->keys_per_split > 0 && a->keys_per_split % a->page_size == 0,
+                "attention_decode: keys_per_split %d must be a whole number of pages of %d", a->keys_per_split, a->page_size);
+    RDL_REQUIRE(a->max_splits > 0 && a->max_splits <= 65535, "attention_decode: bad number of runs %d", a->max_splits);
     RDL_REQUIRE(a->n_kv_heads <= 65535 && a->n_tokens <= 65535, "attention_decode: grid too large");
-    if (a->keys_per_split > 0) {
-        RDL_REQUIRE(a->max_splits > 0 && a->max_splits <= 65535, "attention_decode: bad number of runs %d", a->max_splits);
-        RDL_REQUIRE(a->counter_bytes == rdl_attention_decode_counter_bytes(a->n_tokens, a->n_kv_heads),
-                    "attention_decode: counter_bytes must come from rdl_attention_decode_counter_bytes");
-        RDL_REQUIRE(a->scratch && a->scratch_bytes >= rdl_attention_decode_scratch_bytes(a->n_tokens, a->n_heads, a->n_kv_heads, a->head_dim, a->max_splits),
-                    "attention_decode: scratch of %lld bytes is too small", a->scratch_bytes);
-        RDL_REQUIRE((uintptr_t)a->scratch % 16 == 0, "attention_decode: the scratch must start on a 16-byte boundary");
-    }
+    RDL_REQUIRE(a->counter_bytes == rdl_attention_decode_counter_bytes(a->n_tokens, a->n_kv_heads),
+                "attention_decode: counter_bytes must come from rdl_attention_decode_counter_bytes");
+    RDL_REQUIRE(a->scratch && a->scratch_bytes >= rdl_attention_decode_scratch_bytes(a->n_tokens, a->n_heads, a->n_kv_heads, a->head_dim, a->max_splits),
+                "attention_decode: scratch of %lld bytes is too small", a->scratch_bytes);
     RDL_REQUIRE(a->q_stride % 8 == 0 && (uintptr_t)a->q % 16 == 0 && (uintptr_t)a->k_cache % 16 == 0 &&
-                    (uintptr_t)a->v_cache % 16 == 0 && a->out_stride % 2 == 0,
+                    (uintptr_t)a->v_cache % 16 == 0 && (uintptr_t)a->scratch % 16 == 0 && a->out_stride % 2 == 0,
                 "attention_decode: rows must start on 16-byte boundaries");
     if (a->new_rows) {
         RDL_REQUIRE(a->k_new && a->v_new && a->kv_stride % 8 == 0 && (uintptr_t)a->k_new % 16 == 0 && (uintptr_t)a->v_new % 16 == 0,

@@ -525,19 +525,6 @@ def choose_keys_per_split(n_tokens: int, n_kv_heads: int, max_keys: int, page_si
     return page_size
 
 
-DECODE_CLUSTER = 8                  # blocks of a (token, kv head) in the decode kernel's cluster form
-DECODE_CLUSTER_MAX_PAGES = 8        # the longest run of pages one of them should stream
-
-
-def decode_cluster_ok(n_tokens: int, n_kv_heads: int, max_keys: int, page_size: int, sms: int) -> bool:
-    """The decode kernel's cluster form pays where eight blocks per (token, kv head) fill the GPU (about one block a
-    multiprocessor or more) and no block gets more than eight pages; else the runs of fixed length with their merge
-    through memory, which can be cut finer."""
-    if os.environ.get("RDL_DECODE_CLUSTER") == "0":
-        return False
-    return n_tokens * n_kv_heads * DECODE_CLUSTER >= sms and max_keys <= DECODE_CLUSTER * DECODE_CLUSTER_MAX_PAGES * page_size
-
-
 def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n_heads: int, n_kv_heads: int,
               head_dim: int, score_scale: float, softcap: Optional[float], window: Optional[int],
               new_kv: Optional[Tuple[torch.Tensor, int, int]] = None, kind: str = "auto",
@@ -549,7 +536,6 @@ def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n
     query heads; the row stride may be larger (packed q/k/v rows).
     new_kv: (rows, k_col, v_col) - this step's packed rows and the columns at which the rotated
     keys and the values start; needed when `b.seq_cached` says that new keys are not in the cache.
-    keys_per_split (kind "decode"): the length of a block's run of keys; 0: the cluster form; None: chosen here.
     kind: "plain" (float arithmetic, any dtype), "prefill" (bfloat16, mma.sync tensor cores, keys from
     cache and packed rows), "prefill_tc" (bfloat16, TMA + tcgen05, for sequences that start at position 0
     with head_dim a multiple of 64), "decode" (bfloat16, split keys; reads the cache only), or "auto".
@@ -596,21 +582,17 @@ def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n
             library.check(lib.rdl_attention_prefill(ctypes.byref(a), _stream(q)))
     elif kind == "decode":
         _need(pages is not None, "attention: decode reads the cache")
-        sms = sm_count(q.device.index or 0)
-        if keys_per_split == 0 or (keys_per_split is None and decode_cluster_ok(b.n_tokens, n_kv_heads, b.max_keys, pages.page_size, sms)):
-            # the cluster form: eight blocks per (token, kv head) share the token's pages evenly and merge on the chip
-            a.keys_per_split = a.max_splits = 0
-        else:
-            ks = keys_per_split or choose_keys_per_split(b.n_tokens, n_kv_heads, b.max_keys, pages.page_size, sms)
-            a.keys_per_split = ks
-            # a run of max_keys positions can straddle one more split than its length suggests
-            a.max_splits = (max(b.max_keys, 1) + ks - 1) // ks + 1
-            need = lib.rdl_attention_decode_scratch_bytes(b.n_tokens, n_heads, n_kv_heads, head_dim, a.max_splits)
-            # the counters at the start of the scratch must be zero before a launch; the kernel leaves them so
-            buf = scratch(need) if scratch is not None else torch.zeros(-(-need // 4), dtype=torch.float32, device=q.device)
-            _need(buf.dtype is torch.float32 and buf.numel() * 4 >= need, "attention: decode scratch too small")
-            a.scratch, a.scratch_bytes = buf.data_ptr(), buf.numel() * 4
-            a.counter_bytes = lib.rdl_attention_decode_counter_bytes(b.n_tokens, n_kv_heads)
+        ks = keys_per_split or choose_keys_per_split(b.n_tokens, n_kv_heads, b.max_keys, pages.page_size,
+                                                     sm_count(q.device.index or 0))
+        a.keys_per_split = ks
+        # a run of max_keys positions can straddle one more split than its length suggests
+        a.max_splits = (max(b.max_keys, 1) + ks - 1) // ks + 1
+        need = lib.rdl_attention_decode_scratch_bytes(b.n_tokens, n_heads, n_kv_heads, head_dim, a.max_splits)
+        # the counters at the start of the scratch must be zero before a launch; the kernel leaves them so
+        buf = scratch(need) if scratch is not None else torch.zeros(-(-need // 4), dtype=torch.float32, device=q.device)
+        _need(buf.dtype is torch.float32 and buf.numel() * 4 >= need, "attention: decode scratch too small")
+        a.scratch, a.scratch_bytes = buf.data_ptr(), buf.numel() * 4
+        a.counter_bytes = lib.rdl_attention_decode_counter_bytes(b.n_tokens, n_kv_heads)
         a.status = _status(status)
         if rotate_and_write is not None:
             cos, sin, rotary_dim = rotate_and_write

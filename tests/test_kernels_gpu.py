@@ -383,14 +383,13 @@ DECODE_SHAPES = [
 
 
 @pytest.mark.parametrize("shape", DECODE_SHAPES)
-@pytest.mark.parametrize("keys_per_split", [None, "one_page", "eight_pages", "cluster"])
+@pytest.mark.parametrize("keys_per_split", [None, "one_page", "eight_pages"])
 def test_decode_attention_over_cache(shape, keys_per_split):
     shape = dict(shape)
     past = shape.pop("past")
     c = Case(past=past, new=[1] * len(past), dtype=torch.bfloat16, seed=40, **shape)
     b = c.batch("all")
-    # "cluster": eight blocks per (token, kv head) share the token's pages and merge through distributed shared memory
-    ks = {None: None, "one_page": c.page_size, "eight_pages": 8 * c.page_size, "cluster": 0}[keys_per_split]
+    ks = {None: None, "one_page": c.page_size, "eight_pages": 8 * c.page_size}[keys_per_split]
     for softcap in (None, 7.0):
         got = ops.attention(c.qkv, b, c.pages, kind="decode", keys_per_split=ks, **c.kw(softcap=softcap))
         want = ref.attention(c.qkv, b, c.pages, **c.kw(softcap=softcap))
@@ -419,7 +418,7 @@ def test_decode_attention_rotates_and_writes_the_new_rows(shape, rotary):
     ref_pages = ops.KVPages(c.k.clone(), c.v.clone(), c.pages.tables, c.page_size, c.ring_pages)
     want = ref.attention(c.qkv, b, ref_pages, new_kv=c.new_kv(), rotate_and_write=rw, **c.kw(softcap=9.0))
     rows_before = c.qkv.clone()
-    for ks in (None, c.page_size, 0):          # chosen by the wrapper, one page a block, the cluster form
+    for ks in (None, c.page_size):
         got_pages = ops.KVPages(c.k.clone(), c.v.clone(), c.pages.tables, c.page_size, c.ring_pages)
         got = ops.attention(c.qkv, b, got_pages, new_kv=c.new_kv(), kind="decode", keys_per_split=ks, rotate_and_write=rw,
                             **c.kw(softcap=9.0))
@@ -459,8 +458,6 @@ def test_attention_finds_one_far_key(sizes):
         for kind in ("decode", "plain"):
             got = ops.attention(c.qkv, b, c.pages, kind=kind, **c.kw(scale=1.0))
             assert_close(got, want, torch.bfloat16, rel=6.0, what=f"{kind} window={window} key={far}")
-        got = ops.attention(c.qkv, b, c.pages, kind="decode", keys_per_split=0, **c.kw(scale=1.0))
-        assert_close(got, want, torch.bfloat16, rel=6.0, what=f"decode, cluster form, window={window} key={far}")
 
 
 @pytest.mark.parametrize("kind", ["prefill", "prefill_tc", "plain"])
