@@ -16,8 +16,6 @@
 // Formulas as in attention_plain.cu.  Every wait is bounded; a block that gives up sets `status`.
 #include <cuda.h>
 
-#include <cstdlib>
-
 #include "api.h"
 #include "launch.cuh"
 #include "common.cuh"
@@ -110,27 +108,6 @@ __device__ __forceinline__ float exp2_fast(float x) {      // 2^x, -inf gives 0
     return y;
 }
 
-// Pairs of blocks (a cluster of two): the cluster-wide barrier and a float4 / float2 written into the other
-// block's shared memory.
-// The loader's and the issuer's warps come here with one lane having run the whole main loop and the others none of
-// it: the warp is brought together first, and the barrier instructions are the forms that do not require it.
-__device__ __forceinline__ void cl_sync() {
-    __syncwarp();
-    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
-}
-__device__ __forceinline__ uint32_t cl_map(const void* smem_ptr, uint32_t rank) {
-    uint32_t a = smem_u32(smem_ptr), r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ void cl_st_f32x4(uint32_t addr, float4 v) {
-    asm volatile("st.shared::cluster.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
-}
-__device__ __forceinline__ void cl_st_f32x2(uint32_t addr, float2 v) {
-    asm volatile("st.shared::cluster.v2.f32 [%0], {%1,%2};" ::"r"(addr), "f"(v.x), "f"(v.y) : "memory");
-}
-
 struct TcAttnArgs {
     void* out; long long out_stride;
     const int* tile_seq; const int* tile_q0; int n_tiles;
@@ -141,14 +118,8 @@ struct TcAttnArgs {
     int* status;
 };
 
-// DB: 64-column blocks of a head (head_dim / 64).
-// PAIR: a query tile and head belong to a cluster of two blocks (blockIdx.x = 2 head + half).  Block 0 takes the
-// first half of the tile's key tiles, block 1 the rest (with the diagonal); when both are through, block 1 puts
-// its sums into block 0's shared memory (the key and value buffers, free by then), and block 0 adds them to its
-// own and writes the rows.  The longest block of a step then has half as many key tiles, which is what the step
-// waits for while a prompt's tiles are fewer than the multiprocessors.  Every thread of both blocks reaches both
-// cluster barriers, whatever became of its waits.
-template <int DB, bool PAIR>
+// DB: 64-column blocks of a head (head_dim / 64)
+template <int DB>
 __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                       const __grid_constant__ CUtensorMap map_kv, TcAttnArgs a) {
     // 64-row tiles come from the host; a block takes two of them, so odd ones have nothing to do
@@ -157,7 +128,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
     const int tile = a.n_tiles - 1 - blockIdx.y;
     const int q0 = a.tile_q0[tile];
     if (q0 % QM) return;
-    const int seq = a.tile_seq[tile], h = PAIR ? blockIdx.x >> 1 : blockIdx.x, half = PAIR ? blockIdx.x & 1 : 0;
+    const int seq = a.tile_seq[tile], h = blockIdx.x;
     const int row0 = a.seq_start[seq];
     const int n_new = a.seq_start[seq + 1] - row0;
     const int rows = min(QM, n_new - q0);
@@ -205,19 +176,11 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
     // the tiles of keys this block visits: positions [kv_first, p_last], 64 at a time
     const int p_first = q0, p_last = q0 + rows - 1;
     const int lo_first = a.window > 0 ? max(0, p_first - a.window + 1) : 0;
-    int kv_first = (lo_first / KN) * KN;
-    int n_kv = (p_last - kv_first) / KN + 1;
-    if (PAIR) {
-        const int first_n = n_kv / 2;                      // may be none: block 0 then only waits for block 1's sums
-        if (half == 0) n_kv = first_n;
-        else { kv_first += first_n * KN; n_kv -= first_n; }
-    }
+    const int kv_first = (lo_first / KN) * KN;
+    const int n_kv = (p_last - kv_first) / KN + 1;
     bool ok = true;
-    float m_ref = -INFINITY, l = 0.f;                      // a softmax thread's reference maximum and normaliser
 
-    if (n_kv == 0) {
-        // nothing of its own to do
-    } else if (warp == 0) {
+    if (warp == 0) {
         if (lane == 0) {
             // ---- loader ----
             mbar_expect_tx(smem_u32(&q_full), q_bytes);
@@ -305,6 +268,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
         const float c_in = capped ? a.score_scale / a.softcap : a.score_scale * LOG2E;
         const float c_out = a.softcap * LOG2E;
         const int pr_warp_first = q0 + q * 32, pr_warp_last = pr_warp_first + 31;
+        float m_ref = -INFINITY, l = 0.f;
         for (int j = 0; j < n_kv && ok; ++j) {
             if (!mbar_wait_bounded(smem_u32(&s_full), j & 1)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -388,71 +352,16 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
         }
         if (ok && !mbar_wait_bounded(smem_u32(&pv_done), (n_kv - 1) & 1)) ok = false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    }
-    // ---- the rows' sums are complete (in tensor memory and in the softmax threads' registers) ----
-    bool write_out = true;
-    float w_me = 1.f, w_other = 0.f;
-    if (warp >= 2) ok = __all_sync(0xffffffffu, ok);       // what follows reads tensor memory a warp at a time
-    const float4* other_o = nullptr;                       // PAIR, block 0: block 1's sums, [head_dim / 4][QM] float4
-    if (PAIR) {
-        float4* xo = reinterpret_cast<float4*>(sK);        // the key and value buffers: QM x head_dim floats
-        float2* xml = reinterpret_cast<float2*>(sP);
-        cl_sync();                                         // both blocks are through with their key and value tiles
-        if (half == 1 && warp >= 2) {
-            const int r = (warp & 3) * 32 + lane;
-            const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-#pragma unroll
-            for (int c = 0; c < hd; c += 32) {
-                float o[32];
-                if (ok) tmem_ld32(tmem_o + lane_base + c, o);
-#pragma unroll
-                for (int i = 0; i < 32; i += 4)
-                    cl_st_f32x4(cl_map(xo + ((c + i) >> 2) * QM + r, 0), ok ? make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]) : make_float4(0.f, 0.f, 0.f, 0.f));
-            }
-            cl_st_f32x2(cl_map(xml + r, 0), ok ? make_float2(m_ref, l) : make_float2(-INFINITY, 0.f));
-        }
-        cl_sync();                                         // block 1's sums have arrived
-        write_out = half == 0;
-        if (half == 0 && warp >= 2) {
-            const float2 ml = xml[(warp & 3) * 32 + lane];
-            const float big = fmaxf(m_ref, ml.x);
-            w_me = m_ref == -INFINITY ? 0.f : exp2f(m_ref - big);
-            w_other = ml.x == -INFINITY ? 0.f : exp2f(ml.x - big);
-            l = l * w_me + ml.y * w_other;
-            other_o = xo;
-        }
-    }
-    if (warp >= 2) {
-        const int q = warp & 3;
-        const int r = q * 32 + lane;
-        const uint32_t lane_base = (uint32_t)(q * 32) << 16;
         // The rows go through shared memory (the query tile is no longer needed) so that the stores to
         // global memory are whole 16-byte chunks of consecutive addresses: thread -> row on the way in
         // (chunks swizzled by the row, no bank conflicts), thread -> chunk on the way out.
-        if (ok && write_out) {
+        if (ok) {
             const float inv = 1.0f / l;
             unsigned char* srow = sQ + (size_t)r * (hd * 2);
 #pragma unroll
             for (int c = 0; c < hd; c += 32) {
                 float o[32];
-                // tensor memory is read by whole warps: the choice must not depend on the row (a row whose keys all lie
-                // in the other block's half has weight 0 here, but its accumulator holds proper zeros)
-                if (n_kv > 0) {
-                    tmem_ld32(tmem_o + lane_base + c, o);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] = 0.f;       // nothing was summed in this block: the accumulator holds anything
-                }
-                if (other_o) {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        const float4 v = other_o[((c + i) >> 2) * QM + r];
-                        o[i] = o[i] * w_me + v.x * w_other;
-                        o[i + 1] = o[i + 1] * w_me + v.y * w_other;
-                        o[i + 2] = o[i + 2] * w_me + v.z * w_other;
-                        o[i + 3] = o[i + 3] * w_me + v.w * w_other;
-                    }
-                }
+                tmem_ld32(tmem_o + lane_base + c, o);
 #pragma unroll
                 for (int i = 0; i < 32; i += 8) {
                     uint4 raw;
@@ -466,7 +375,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 1) attention_tc_kernel(const __gr
             }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");           // the four softmax warps, whatever became of their waits
-        if (write_out) {
+        {
             constexpr int CHUNKS = hd / 8;                       // 16-byte chunks of a row
             __nv_bfloat16* obase = (__nv_bfloat16*)a.out + (long long)(row0 + q0) * a.out_stride + (long long)h * hd;
             const int tt = threadIdx.x - 64;
@@ -510,32 +419,13 @@ int make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols, 
 }
 
 template <int DB>
-int launch_tc(bool pair, int smem, cudaStream_t st, const CUtensorMap& map_q, const CUtensorMap& map_kv, const TcAttnArgs& t) {
+int launch_tc(dim3 grid, int smem, cudaStream_t st, const CUtensorMap& map_q, const CUtensorMap& map_kv, const TcAttnArgs& t) {
     static bool opted = false;
     if (!opted) {
-        RDL_CUDA(cudaFuncSetAttribute(attention_tc_kernel<DB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "attention_prefill_tc");
-        RDL_CUDA(cudaFuncSetAttribute(attention_tc_kernel<DB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "attention_prefill_tc");
+        RDL_CUDA(cudaFuncSetAttribute(attention_tc_kernel<DB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "attention_prefill_tc");
         opted = true;
     }
-    if (!pair) {
-        RDL_CHECK_EX(rdl_launch(attention_tc_kernel<DB, false>, dim3(t.n_heads, t.n_tiles), dim3(ATC_THREADS), (size_t)smem, st, map_q, map_kv, t),
-                     "attention_prefill_tc");
-        return 0;
-    }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * t.n_heads, t.n_tiles);
-    cfg.blockDim = dim3(ATC_THREADS);
-    cfg.dynamicSmemBytes = (size_t)smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = g_rdl_programmatic_launch ? 2 : 1;
-    RDL_CHECK_EX(cudaLaunchKernelEx(&cfg, attention_tc_kernel<DB, true>, map_q, map_kv, t), "attention_prefill_tc");
+    RDL_CHECK_EX(rdl_launch(attention_tc_kernel<DB>, grid, dim3(ATC_THREADS), (size_t)smem, st, map_q, map_kv, t), "attention_prefill_tc");
     return 0;
 }
 
@@ -563,15 +453,11 @@ extern "C" int rdl_attention_prefill_tc(const AttentionArgs* a, long long row_wi
     TcAttnArgs t{a->out, a->out_stride, a->tile_seq, a->tile_q0, a->n_tiles, a->seq_start, a->n_heads, a->n_kv_heads, a->head_dim,
                  a->score_scale, a->softcap, a->window, a->status};
     const int smem = QM * a->head_dim * 2 + 4 * KN * a->head_dim * 2 + QM * 128 + 1024;
-    // While a step's query tiles (128 rows, one block a head) are no more than the multiprocessors, the step waits for
-    // the block with the most key tiles: pairs of blocks then share every tile's keys.  With more tiles than that
-    // the blocks keep all multiprocessors busy anyway and the exchange would only cost.
-    static const bool pairs_off = getenv("RDL_PREFILL_PAIR") && atoi(getenv("RDL_PREFILL_PAIR")) == 0;     // for comparison
-    const bool pair = !pairs_off && (long long)a->n_heads * ((a->n_tiles + 1) / 2) <= rdl_sm_count() && 2LL * a->n_heads <= 0x7fffffffLL;
+    dim3 grid(a->n_heads, a->n_tiles);
     switch (a->head_dim / 64) {
-        case 1: return launch_tc<1>(pair, smem, (cudaStream_t)stream, map_q, map_kv, t);
-        case 2: return launch_tc<2>(pair, smem, (cudaStream_t)stream, map_q, map_kv, t);
-        case 3: return launch_tc<3>(pair, smem, (cudaStream_t)stream, map_q, map_kv, t);
-        default: return launch_tc<4>(pair, smem, (cudaStream_t)stream, map_q, map_kv, t);
+        case 1: return launch_tc<1>(grid, smem, (cudaStream_t)stream, map_q, map_kv, t);
+        case 2: return launch_tc<2>(grid, smem, (cudaStream_t)stream, map_q, map_kv, t);
+        case 3: return launch_tc<3>(grid, smem, (cudaStream_t)stream, map_q, map_kv, t);
+        default: return launch_tc<4>(grid, smem, (cudaStream_t)stream, map_q, map_kv, t);
     }
 }
