@@ -241,3 +241,27 @@ def test_toy_model_in_unequal_batches(toy):
             for i in [i for i in live if pos[i] == len(seqs[i])]:
                 eng.release(slots[i])
             live = [i for i in live if pos[i] < len(seqs[i])]
+
+
+def test_toy_model_in_bfloat16_single_tokens():
+    """The same model in bfloat16, where steps of few rows may carry their norms in the products (parts/norm.py): here
+    the attention and the gated feed-forward offer that, the toy parts do not, one post-norm is of a kind that cannot
+    take part and one branch has no post-norm at all - every combination must fall back to the same numbers."""
+    register_toys()
+    spec = toy_spec()
+    weights = random_weights(spec, 3, torch.bfloat16, DEV)
+    kept = {n: t.clone() for n, t in weights.items()}
+    eng = Engine(Model(spec, weights, torch.bfloat16, DEV), max_tokens=512, max_seqs=4, use_graphs=False)
+    rng = np.random.default_rng(2)
+    seqs = [[int(v) for v in rng.integers(0, V, size=n)] for n in (40, 23, 31)]
+    want = [plain_forward(kept, s) for s in seqs]
+    slots = [eng.new_sequence() for _ in seqs]
+    cut = [len(s) - 8 for s in seqs]
+    got = eng.step(slots, [s[:c] for s, c in zip(seqs, cut)], "last").double().cpu().numpy()
+    ref0 = np.stack([w[c - 1] for w, c in zip(want, cut)])
+    scale = max(np.abs(w).max() for w in want)
+    assert np.abs(got - ref0).max() <= 0.03 * scale
+    for k in range(8):
+        got = eng.step(slots, [[s[c + k]] for s, c in zip(seqs, cut)], "last").double().cpu().numpy()
+        ref = np.stack([w[c + k] for w, c in zip(want, cut)])
+        assert np.isfinite(got).all() and np.abs(got - ref).max() <= 0.03 * scale, (k, np.abs(got - ref).max(), scale)
