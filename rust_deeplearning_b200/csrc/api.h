@@ -10,7 +10,7 @@ extern "C" {
 #define RDL_ACT_GELU_TANH 0
 #define RDL_ACT_SILU 1
 
-#define RDL_ABI_VERSION 10
+#define RDL_ABI_VERSION 11
 
 const char* rdl_last_error(void);
 int rdl_abi_version(void);
@@ -87,6 +87,11 @@ int rdl_softcap_inplace(void* z_f32, long long total, float cap, void* stream);
 int rdl_residual_add(void* res_f32, const void* x, int x_dtype, long long total, void* stream);
 int rdl_convert_rows(void* out, int out_dtype, const void* in, int in_dtype, const int* row_index,
                      int n_rows, int width, void* stream);
+// A step's batch description from pinned host memory to the device, by a kernel (a copy engine's hand-over costs
+// several microseconds between two kernels): dst[i] = src_pinned[i] for n_ints (a multiple of 4) values, except that
+// dst[tokens_at + i] = sampled[src_pinned[token_src_at + i]] for i < n_fed when `sampled` (device, int32) is given.
+int rdl_upload_batch(int* dst, const int* src_pinned, int n_ints, const int* sampled, int token_src_at, int tokens_at,
+                     int n_fed, void* stream);
 
 int rdl_rope_cache(void* qkv, int dtype, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                    int rotary_dim, const float* cos_table, const float* sin_table,
@@ -163,7 +168,8 @@ typedef struct {
     float repetition_penalty;   // 1: off
     unsigned long long seed;
 } SamplingArgs;
-int rdl_sample(int* out_tokens, const float* logits, int n_rows, int vocab, const SamplingArgs* params,
+// host_tokens (optional): pinned host memory the kernel writes the tokens to as well
+int rdl_sample(int* out_tokens, int* host_tokens, const float* logits, int n_rows, int vocab, const SamplingArgs* params,
                const unsigned long long* row_stream, const int* row_step,
                const int* history, const int* history_start, float* work, void* stream);
 // the uniform number in [0, 1) that rdl_sample draws with for (seed, stream id, step); host function

@@ -393,3 +393,40 @@ extern "C" int rdl_convert_rows(void* out, int out_dtype, const void* in, int in
     RDL_CHECK_LAUNCH("convert_rows");
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// batch description: pinned host memory -> device, with the ids an earlier sampling left on the device put in place
+// ---------------------------------------------------------------------------------------------
+__global__ void upload_batch_kernel(int* __restrict__ dst, const int* __restrict__ src, int n, const int* __restrict__ sampled,
+                                    int token_src_at, int tokens_at, int n_fed) {
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
+    const int quads = n >> 2;
+    for (int q = blockIdx.x * blockDim.x + threadIdx.x; q < quads; q += gridDim.x * blockDim.x) {
+        int4 v = reinterpret_cast<const int4*>(src)[q];
+        if (sampled) {
+            int* e = reinterpret_cast<int*>(&v);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int i = 4 * q + k - tokens_at;
+                if (i >= 0 && i < n_fed) e[k] = sampled[src[token_src_at + i]];
+            }
+        }
+        reinterpret_cast<int4*>(dst)[q] = v;
+    }
+}
+
+extern "C" int rdl_upload_batch(int* dst, const int* src_pinned, int n_ints, const int* sampled, int token_src_at, int tokens_at,
+                                int n_fed, void* stream) {
+    RDL_REQUIRE(dst && src_pinned && n_ints >= 0 && n_ints % 4 == 0, "upload_batch: %d values (a multiple of 4 is expected)", n_ints);
+    RDL_REQUIRE(((uintptr_t)dst & 15) == 0 && ((uintptr_t)src_pinned & 15) == 0, "upload_batch: buffers must start on 16-byte boundaries");
+    RDL_REQUIRE(!sampled || (n_fed >= 0 && token_src_at >= 0 && tokens_at >= 0 && token_src_at + n_fed <= n_ints && tokens_at + n_fed <= n_ints),
+                "upload_batch: the fed tokens lie outside the description");
+    if (n_ints == 0) return 0;
+    const int threads = 256, quads = n_ints / 4;
+    int blocks = (quads + threads - 1) / threads;
+    if (blocks > 64) blocks = 64;
+    RDL_CHECK_EX(rdl_launch(upload_batch_kernel, dim3(blocks), dim3(threads), 0, (cudaStream_t)stream, dst, src_pinned, n_ints, sampled,
+                            token_src_at, tokens_at, n_fed), "upload_batch");
+    return 0;
+}

@@ -44,6 +44,13 @@ __host__ __device__ inline float uniform_from(unsigned long long seed, unsigned 
     return (float)(h >> 40) * (1.0f / 16777216.0f);
 }
 
+// The row's token goes to the device vector and, if asked for, straight into pinned host memory as well: the host
+// then reads it after the kernel's event, with no copy of its own queued in between.
+__device__ __forceinline__ void put_token(int* out_tokens, int* host_tokens, int row, int token) {
+    out_tokens[row] = token;
+    if (host_tokens) host_tokens[row] = token;
+}
+
 __device__ float block_max(float v, float* scratch) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     v = warp_max(v);
@@ -76,7 +83,7 @@ __device__ unsigned block_count(unsigned v, unsigned* scratch) {
     return scratch[32];
 }
 
-__global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(int* __restrict__ out_tokens, const float* __restrict__ logits,
+__global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(int* __restrict__ out_tokens, int* __restrict__ host_tokens, const float* __restrict__ logits,
                                                                 int vocab, SamplingArgs prm,
                                                                 const unsigned long long* __restrict__ row_stream,
                                                                 const int* __restrict__ row_step,
@@ -119,7 +126,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(int* __restrict_
                 const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
                 if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
             }
-            if (tid == 0) out_tokens[row] = bi == 0x7fffffff ? 0 : bi;
+            if (tid == 0) put_token(out_tokens, host_tokens, row, bi == 0x7fffffff ? 0 : bi);
         }
         return;
     }
@@ -221,7 +228,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(int* __restrict_
         if (tid == 0) chosen = (int)lf;
         __syncthreads();
     }
-    if (tid == 0) out_tokens[row] = chosen < 0 ? 0 : chosen;
+    if (tid == 0) put_token(out_tokens, host_tokens, row, chosen < 0 ? 0 : chosen);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -297,7 +304,82 @@ __device__ __forceinline__ unsigned cl_sum_u(unsigned block_value, ClusterExchan
     return t;
 }
 
-__global__ void __launch_bounds__(CL_THREADS, 1) sample_cluster_kernel(int* __restrict__ out_tokens, const float* __restrict__ logits,
+// Arg max with the row shared by a cluster: every block takes a contiguous part of the row, the first block picks among
+// the blocks' best (the smallest index among equal maxima, as in the one-block kernel).  One block a row reads a
+// megabyte through one multiprocessor (14 us at 256,000 tokens); eight read it in 4 us.
+__global__ void __launch_bounds__(CL_THREADS, 1) argmax_cluster_kernel(int* __restrict__ out_tokens, int* __restrict__ host_tokens, const float* __restrict__ logits,
+                                                                       int vocab, int n_blocks) {
+    __shared__ float best_val[32];
+    __shared__ int best_idx[32];
+    __shared__ float blk_val;
+    __shared__ int blk_idx;
+    rdl_grid_wait();
+    rdl_grid_launch_dependents();
+    const int row = blockIdx.y, tid = threadIdx.x;
+    const int rank = (int)cl_rank();
+    const float* x = logits + (long long)row * vocab;
+    const int per = (vocab + n_blocks - 1) / n_blocks;
+    const int lo = rank * per, hi = min(vocab, lo + per);
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    int i0 = lo;
+    if (vocab % 4 == 0 && per % 4 == 0) {
+        // sixteen values a thread and round, asked for together (one value at a time is a trip to L2 each: 12 us a row)
+        const float4* x4 = reinterpret_cast<const float4*>(x + lo);
+        const int n4 = (hi - lo) / 4;
+        for (int q = tid; q < n4; q += 4 * CL_THREADS) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                v[u] = q + u * CL_THREADS < n4 ? __ldcg(x4 + q + u * CL_THREADS) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int at = lo + 4 * (q + u * CL_THREADS);
+                if (v[u].x > bv) { bv = v[u].x; bi = at; }
+                if (v[u].y > bv) { bv = v[u].y; bi = at + 1; }
+                if (v[u].z > bv) { bv = v[u].z; bi = at + 2; }
+                if (v[u].w > bv) { bv = v[u].w; bi = at + 3; }
+            }
+        }
+        i0 = lo + 4 * n4;
+    }
+    for (int i = i0 + tid; i < hi; i += CL_THREADS) {
+        const float v = __ldcg(x + i);
+        if (v > bv) { bv = v; bi = i; }
+    }
+    auto better = [](float ov, int oi, float bv, int bi) { return ov > bv || (ov == bv && oi < bi); };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    if ((tid & 31) == 0) { best_val[tid >> 5] = bv; best_idx[tid >> 5] = bi; }
+    __syncthreads();
+    if (tid < 32) {
+        bv = best_val[tid];
+        bi = best_idx[tid];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        }
+        if (tid == 0) { blk_val = bv; blk_idx = bi; }
+    }
+    cl_sync();                 // every block's best is in its shared memory
+    if (rank == 0 && tid == 0) {
+        for (int r = 1; r < n_blocks; ++r) {
+            const float ov = cl_ld_f32(cl_map(&blk_val, r));
+            const int oi = (int)cl_ld_u32(cl_map(&blk_idx, r));
+            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        }
+        put_token(out_tokens, host_tokens, row, bi == 0x7fffffff ? 0 : bi);
+    }
+    cl_sync();                 // no block leaves while the first may still read its shared memory
+}
+
+__global__ void __launch_bounds__(CL_THREADS, 1) sample_cluster_kernel(int* __restrict__ out_tokens, int* __restrict__ host_tokens, const float* __restrict__ logits,
                                                                        int vocab, SamplingArgs prm,
                                                                        const unsigned long long* __restrict__ row_stream,
                                                                        const int* __restrict__ row_step,
@@ -455,7 +537,7 @@ __global__ void __launch_bounds__(CL_THREADS, 1) sample_cluster_kernel(int* __re
     __syncthreads();
     const float found = cl_max_f((float)chosen, &xch, parity, n_blocks);
     const float row_last = cl_max_f(block_last, &xch, parity, n_blocks);
-    if (rank == 0 && tid == 0) out_tokens[row] = found >= 0.f ? (int)found : (row_last >= 0.f ? (int)row_last : 0);
+    if (rank == 0 && tid == 0) put_token(out_tokens, host_tokens, row, found >= 0.f ? (int)found : (row_last >= 0.f ? (int)row_last : 0));
     cl_sync();                 // no block leaves while another may still read its shared memory
 }
 
@@ -465,7 +547,7 @@ extern "C" float rdl_sampling_uniform(unsigned long long seed, unsigned long lon
     return uniform_from(seed, stream, step);
 }
 
-extern "C" int rdl_sample(int* out_tokens, const float* logits, int n_rows, int vocab, const SamplingArgs* prm,
+extern "C" int rdl_sample(int* out_tokens, int* host_tokens, const float* logits, int n_rows, int vocab, const SamplingArgs* prm,
                           const unsigned long long* row_stream, const int* row_step,
                           const int* history, const int* history_start, float* work, void* stream) {
     RDL_REQUIRE(out_tokens && logits && prm, "sample: missing operand");
@@ -480,6 +562,24 @@ extern "C" int rdl_sample(int* out_tokens, const float* logits, int n_rows, int 
         RDL_REQUIRE(prm->repetition_penalty == 1.0f || !history || history_start, "sample: history without offsets");
     }
     if (n_rows == 0) return 0;
+    if (prm->temperature < 1e-7f && vocab >= 4 * CL_PER_BLOCK && n_rows <= 65535) {
+        // arg max of a long row: eight blocks a row
+        const int n_blocks = CL_MAX_BLOCKS;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(n_blocks, n_rows);
+        cfg.blockDim = dim3(CL_THREADS);
+        cfg.stream = (cudaStream_t)stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = n_blocks;
+        attr[0].val.clusterDim.y = attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = g_rdl_programmatic_launch ? 2 : 1;
+        RDL_CHECK_EX(cudaLaunchKernelEx(&cfg, argmax_cluster_kernel, out_tokens, host_tokens, logits, vocab, n_blocks), "sample");
+        return 0;
+    }
     if (prm->temperature >= 1e-7f && vocab <= CL_MAX_BLOCKS * CL_PER_BLOCK && n_rows <= 65535) {
         // the row on the chip: 1, 2, 4 or 8 blocks a row
         int n_blocks = 1;
@@ -503,11 +603,11 @@ extern "C" int rdl_sample(int* out_tokens, const float* logits, int n_rows, int 
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = g_rdl_programmatic_launch ? 2 : 1;
-        RDL_CHECK_EX(cudaLaunchKernelEx(&cfg, sample_cluster_kernel, out_tokens, logits, vocab, *prm, row_stream, row_step, history,
+        RDL_CHECK_EX(cudaLaunchKernelEx(&cfg, sample_cluster_kernel, out_tokens, host_tokens, logits, vocab, *prm, row_stream, row_step, history,
                                         history_start, work, n_blocks), "sample");
         return 0;
     }
-    RDL_CHECK_EX(rdl_launch(sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, out_tokens, logits, vocab,
+    RDL_CHECK_EX(rdl_launch(sample_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, out_tokens, host_tokens, logits, vocab,
                             *prm, row_stream, row_step, history, history_start, work), "sample");
     return 0;
 }

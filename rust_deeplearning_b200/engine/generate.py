@@ -124,15 +124,14 @@ def plan_batches(prompt_lens: Sequence[int], max_new_tokens: int, *, max_seqs: i
 
 
 class _Readback:
-    """Sampled ids on their way to the host: the copy into pinned memory is queued right behind the
-    sampling, and `tokens()` waits for that copy alone - not for whatever was queued after it."""
+    """Sampled ids on their way to the host: the sampling kernel writes them into pinned memory itself, and
+    `tokens()` waits for that kernel alone - not for whatever was queued after it."""
 
     def __init__(self, sampled, pinned):
         self.sampled, self.n = sampled, sampled.numel()
         self.event = None
-        if sampled.device.type == "cuda":
+        if pinned is not None:
             self.host = pinned[:self.n]
-            self.host.copy_(sampled, non_blocking=True)
             self.event = torch.cuda.Event()
             self.event.record()
 
@@ -180,12 +179,13 @@ def generate(engine, prompts: Sequence[Sequence[int]], *, max_new_tokens: int = 
             flip = [0]
 
             def sample(rows, logits):
+                flip[0] ^= 1
+                host = pinned[flip[0]] if pinned is not None else None
                 toks = sampler.sample(logits, [seqs[j].request for j in rows], [issued[j] for j in rows],
-                                      [seqs[j].history() for j in rows] if need_history else None)
+                                      [seqs[j].history() for j in rows] if need_history else None, host_out=host)
                 for j in rows:
                     issued[j] += 1
-                flip[0] ^= 1
-                return _Readback(toks, pinned[flip[0]] if pinned is not None else None)
+                return _Readback(toks, host)
 
             rows = list(range(len(seqs)))       # the sequences whose tokens `sampled` holds, row by row
             t_start = time.perf_counter()

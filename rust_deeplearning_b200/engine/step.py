@@ -151,9 +151,7 @@ class Engine:
                                                       slots=slots, want=want, tables=tables,
                                                       token_src=fed[1] if fed is not None else None)
             dev = torch.empty(layout.size, dtype=torch.int32, device=self.device)
-            self._upload(dev, host, layout.size)
-            if fed is not None:
-                self._take_fed_tokens(dev, layout, fed[0], n)
+            self._upload(dev, host, layout, fed[0] if fed is not None else None, n)
             batch = batch_from_buffer(dev, layout, real_tokens=real_tokens, real_seqs=n, n_want=n_want, n_tiles=n_tiles,
                                       is_decode=is_decode, max_total_len=max(totals), scratch=self._scratch)
             batch.status = self.status
@@ -194,17 +192,18 @@ class Engine:
             self._pinned[i] = buf
         return buf
 
-    def _upload(self, dev: torch.Tensor, host: torch.Tensor, size: int):
-        dev.copy_(host[:size], non_blocking=True)
+    def _upload(self, dev: torch.Tensor, host: torch.Tensor, layout: BatchLayout, sampled: Optional[torch.Tensor] = None, n_fed: int = 0):
+        """The batch description goes to the device by a kernel that reads the pinned buffer (a copy engine between
+        the kernels of two steps costs several microseconds of hand-over each way); with `sampled`, the first
+        n_fed tokens are taken from that device vector on the way: tokens[i] = sampled[token_src[i]]."""
+        fed = None
+        if sampled is not None:
+            fed = (sampled, layout.fields["token_src"][0], layout.fields["tokens"][0], n_fed)
+        ops.upload_batch(dev, host, layout.size, fed)
         if self.device.type == "cuda":
             ev = torch.cuda.Event()
             ev.record()
             self._pinned_event[self._flip] = ev
-
-    @staticmethod
-    def _take_fed_tokens(dev: torch.Tensor, layout: BatchLayout, sampled: torch.Tensor, n: int):
-        """tokens[i] = sampled[token_src[i]], on the device."""
-        torch.index_select(sampled, 0, layout.view(dev, "token_src")[:n], out=layout.view(dev, "tokens")[:n])
 
     def _graph_step(self, slots, tokens, past, want, tables, widths, max_total, fed=None):
         n = len(slots)
@@ -224,9 +223,7 @@ class Engine:
         host = self._host_buffer(g.layout.size)
         fill_batch(host.numpy()[:g.layout.size], g.layout, tokens=tokens, past=past, slots=slots, want=all_rows,
                    tables=tables, token_src=fed[1] if fed is not None else None)
-        self._upload(g.dev, host, g.layout.size)
-        if fed is not None:
-            self._take_fed_tokens(g.dev, g.layout, fed[0], n)
+        self._upload(g.dev, host, g.layout, fed[0] if fed is not None else None, n)
         g.seen += 1
         if g.graph is None and g.seen >= 2:
             # the first step of a shape ran eagerly (and warmed the libraries up); capture now

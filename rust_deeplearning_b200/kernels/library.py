@@ -23,7 +23,7 @@ from concurrent.futures import ThreadPoolExecutor
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(_PKG, "csrc")
 LIB_NAME = "librdl_b200_kernels.so"
-ABI_VERSION = 10
+ABI_VERSION = 11
 
 # fast math is never enabled: the 32-bit path relies on exact tanhf/expf/sqrtf and plain FMA
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -230,7 +230,8 @@ _SIGNATURES = {
     "rdl_stream_rows": [_P, _I, _F, _P, _P, _P, _P, _I, _F, _P, _I, _I, _P],
     "rdl_gemm_tc": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
     "rdl_random_normal": [_P, _I, _LL, ctypes.c_ulonglong, ctypes.c_double, _P],
-    "rdl_sample": [_P, _P, _I, _I, ctypes.POINTER(SamplingArgs), _P, _P, _P, _P, _P, _P],
+    "rdl_sample": [_P, _P, _P, _I, _I, ctypes.POINTER(SamplingArgs), _P, _P, _P, _P, _P, _P],
+    "rdl_upload_batch": [_P, _P, _I, _P, _I, _I, _I, _P],
 }
 
 _lib = None

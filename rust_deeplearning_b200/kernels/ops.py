@@ -628,8 +628,10 @@ def random_normal(shape, key: int, std: float, dtype: torch.dtype, device) -> to
 def sample(logits: torch.Tensor, *, temperature: float, top_k: Optional[int] = None, top_p: Optional[float] = None,
            repetition_penalty: Optional[float] = None, seed: int = 0, row_stream: Optional[torch.Tensor] = None,
            row_step: Optional[torch.Tensor] = None, history: Optional[torch.Tensor] = None,
-           history_start: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None):
-    """One token per row of float32 logits [rows, vocab] -> int32 [rows]."""
+           history_start: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+           host_out: Optional[torch.Tensor] = None):
+    """One token per row of float32 logits [rows, vocab] -> int32 [rows].  host_out: pinned int32 host memory of
+    at least `rows` values that the kernel writes the tokens to as well (readable once the kernel has ended)."""
     _need(logits.dtype is torch.float32 and logits.dim() == 2 and logits.is_contiguous(),
           "sample takes contiguous float32 logits [rows, vocab]")
     rows, vocab = logits.shape
@@ -647,6 +649,23 @@ def sample(logits: torch.Tensor, *, temperature: float, top_k: Optional[int] = N
         if history is not None:
             _int32(history, "history")
             _int32(history_start, "history_start", rows + 1)
-    library.check(library.load().rdl_sample(_ptr(out), _ptr(logits), rows, vocab, ctypes.byref(prm), _ptr(row_stream),
+    if host_out is not None:
+        _need(host_out.dtype is torch.int32 and host_out.is_pinned() and host_out.is_contiguous() and host_out.numel() >= rows,
+              "sample: host_out must be pinned int32 host memory with a value per row")
+    library.check(library.load().rdl_sample(_ptr(out), host_out.data_ptr() if host_out is not None else None, _ptr(logits), rows, vocab,
+                                            ctypes.byref(prm), _ptr(row_stream),
                                             _ptr(row_step), _ptr(history), _ptr(history_start), _ptr(work), _stream(logits)))
     return out
+
+
+def upload_batch(dst: torch.Tensor, src_pinned: torch.Tensor, n_ints: int, fed: Optional[Tuple[torch.Tensor, int, int, int]] = None):
+    """A step's int32 batch description from pinned host memory to the device by a kernel (no copy engine between the
+    kernels of two steps).  fed = (sampled ids on the device, where the description lists their rows, where its
+    tokens lie, how many): those tokens are taken from `sampled` on the way."""
+    _need(dst.dtype is torch.int32 and dst.is_cuda and src_pinned.dtype is torch.int32 and src_pinned.is_pinned()
+          and dst.numel() >= n_ints and src_pinned.numel() >= n_ints, "upload_batch: int32 device buffer and pinned int32 host buffer")
+    sampled, src_at, tok_at, n_fed = fed if fed is not None else (None, 0, 0, 0)
+    if sampled is not None:
+        _int32(sampled, "sampled")
+    library.check(library.load().rdl_upload_batch(_ptr(dst), src_pinned.data_ptr(), n_ints, _ptr(sampled), src_at, tok_at, n_fed,
+                                                  _stream(dst)))

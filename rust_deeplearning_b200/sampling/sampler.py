@@ -69,13 +69,13 @@ class Sampler:
         self.device = device
 
     def sample(self, logits: torch.Tensor, request_ids: Sequence[int], steps: Sequence[int],
-               histories: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+               histories: Optional[Sequence[Sequence[int]]] = None, host_out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """logits [rows, vocab]; request_ids and steps key each row's random number; histories (all
         tokens of each row's sequence so far) are needed only with a repetition penalty.
-        Returns int32 tokens [rows] on the device."""
+        Returns int32 tokens [rows] on the device; host_out (pinned int32) receives them as well, written by the kernel."""
         p = self.params
         if p.greedy:
-            return ops.sample(logits, temperature=0.0)
+            return ops.sample(logits, temperature=0.0, host_out=host_out)
         rows = logits.shape[0]
         stream = torch.tensor(list(request_ids), dtype=torch.int64).to(self.device, non_blocking=True)
         step = torch.tensor(list(steps), dtype=torch.int32).to(self.device, non_blocking=True)
@@ -90,4 +90,4 @@ class Sampler:
             starts = torch.from_numpy(offs).to(self.device, non_blocking=True)
         return ops.sample(logits, temperature=p.temperature, top_k=p.top_k, top_p=p.top_p,
                           repetition_penalty=p.repetition_penalty, seed=p.seed, row_stream=stream, row_step=step,
-                          history=history, history_start=starts)
+                          history=history, history_start=starts, host_out=host_out)

@@ -185,7 +185,7 @@ def attention(q, b, pages, *, n_heads, n_kv_heads, head_dim, score_scale, softca
 
 
 def sample(logits, *, temperature, top_k=None, top_p=None, repetition_penalty=None, seed=0, row_stream=None,
-           row_step=None, history=None, history_start=None, out=None):
+           row_step=None, history=None, history_start=None, out=None, host_out=None):
     """Follows the kernel's stated semantics (penalty once per distinct token; ties at the top-p
     threshold kept), in float32 like the reference's sampling functions."""
     from rust_deeplearning_b200.sampling.sampler import uniform_for
@@ -219,14 +219,24 @@ def sample(logits, *, temperature, top_k=None, top_p=None, repetition_penalty=No
         c = torch.cumsum(e, 0)
         hit = (u * c[-1] < c).nonzero()
         res[r] = int(hit[0]) if len(hit) else int((w > -math.inf).nonzero()[-1])
+    if host_out is not None:
+        host_out[:rows] = res.cpu()
     if out is not None:
         out.copy_(res)
         return out
     return res
 
 
+def upload_batch(dst, src_pinned, n_ints, fed=None):
+    dst[:n_ints] = src_pinned[:n_ints].to(dst.device)
+    if fed is not None:
+        sampled, src_at, tok_at, n_fed = fed
+        rows = src_pinned[src_at:src_at + n_fed].long().to(dst.device)
+        dst[tok_at:tok_at + n_fed] = sampled[rows]
+
+
 _NAMES = ["embed_rows", "norm_residual_norm", "gated_activation", "softcap_", "residual_add_", "convert_rows",
-          "linear", "linear_gated", "rope_cache", "attention", "sample"]
+          "linear", "linear_gated", "rope_cache", "attention", "sample", "upload_batch"]
 
 
 def install(monkeypatch):

@@ -546,3 +546,28 @@ def test_sampling(vocab):
             got = ops.sample(logits, **args).tolist()
             want = ref.sample(logits, **args).tolist()
             assert got == want, (kw, step, got, want)
+
+
+def test_sampling_writes_pinned_host_memory_and_upload_takes_fed_tokens():
+    """The sampler's tokens arrive in pinned host memory without a copy of its own; the kernel that brings a step's
+    batch description to the device puts the tokens of an earlier sampling in place on the way."""
+    logits = rnd((6, 140000), torch.float32, 61, 3.0)
+    for kw in (dict(temperature=0.0), dict(temperature=0.8, top_k=20, seed=5)):
+        host = torch.full((8,), -1, dtype=torch.int32).pin_memory()
+        got = ops.sample(logits, host_out=host, **kw)
+        torch.cuda.synchronize()
+        assert host[:6].tolist() == got.tolist() and host[6:].tolist() == [-1, -1]
+    n = 4096 + 64
+    src = torch.arange(n, dtype=torch.int32).pin_memory()
+    sampled = torch.tensor([100, 200, 300, 400, 500], dtype=torch.int32, device=DEV)
+    tokens_at, token_src_at, n_fed = 8, 2000, 3
+    src[token_src_at:token_src_at + n_fed] = torch.tensor([4, 0, 2], dtype=torch.int32)
+    dst = torch.full((n,), -7, dtype=torch.int32, device=DEV)
+    ops.upload_batch(dst, src, n)
+    assert torch.equal(dst.cpu(), src)
+    dst.fill_(-7)
+    ops.upload_batch(dst, src, n - 64, (sampled, token_src_at, tokens_at, n_fed))
+    want = src.clone()
+    want[tokens_at:tokens_at + n_fed] = torch.tensor([500, 100, 300], dtype=torch.int32)
+    want[n - 64:] = -7
+    assert torch.equal(dst.cpu(), want)
