@@ -536,6 +536,12 @@ def test_sampling(vocab):
     got = ops.sample(logits, temperature=0.0)
     assert got.tolist() == ref.sample(logits, temperature=0.0).tolist()
     assert got[1].item() == 7
+    # equal maxima far apart (in different blocks where a cluster shares the row): the smaller index wins; a maximum at the row's end
+    logits[2, vocab - 3] = logits[2, 40] = logits[2].max() + 1.0
+    logits[3, vocab - 1] = logits[3].max() + 1.0
+    got = ops.sample(logits, temperature=0.0)
+    assert got[2].item() == 40 and got[3].item() == vocab - 1
+    assert got.tolist() == ref.sample(logits, temperature=0.0).tolist()
     stream = torch.arange(rows, dtype=torch.int64, device=DEV) + 10
     for step in range(3):
         steps = torch.full((rows,), step, dtype=torch.int32, device=DEV)
