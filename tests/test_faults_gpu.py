@@ -41,6 +41,7 @@ def test_every_kernel_of_a_step_gets_the_status_word(monkeypatch):
     watch("rdl_embed_rows", lambda a: _value(a[8]))
     watch("rdl_gemm_skinny", lambda a: _value(a[10]))
     watch("rdl_gemm_tc", lambda a: _value(a[10]))
+    watch("rdl_gemm_skinny_norm", lambda a: _value(a[11]))      # the products that carry the norms in single-token steps
     watch("rdl_attention_decode", lambda a: a[0]._obj.status)
     watch("rdl_attention_prefill_tc", lambda a: a[0]._obj.status)
     name = "D"                                     # head size 64: the tcgen05 prefill attention takes its prompts
@@ -53,7 +54,8 @@ def test_every_kernel_of_a_step_gets_the_status_word(monkeypatch):
     eng.step([slot], [[ids[149]]], "last")          # one row: the decode attention
     torch.cuda.synchronize()
     word = eng.status.data_ptr()
-    for kernel in ("rdl_embed_rows", "rdl_gemm_skinny", "rdl_gemm_tc", "rdl_attention_decode", "rdl_attention_prefill_tc"):
+    for kernel in ("rdl_embed_rows", "rdl_gemm_skinny", "rdl_gemm_skinny_norm", "rdl_gemm_tc", "rdl_attention_decode",
+                   "rdl_attention_prefill_tc"):
         assert kernel in seen, f"{kernel} was not launched"
         assert all(s == word for s in seen[kernel]), f"{kernel} was launched without the engine's status word"
     eng.check_status()
