@@ -10,7 +10,7 @@ extern "C" {
 #define RDL_ACT_GELU_TANH 0
 #define RDL_ACT_SILU 1
 
-#define RDL_ABI_VERSION 12
+#define RDL_ABI_VERSION 11
 
 const char* rdl_last_error(void);
 int rdl_abi_version(void);
@@ -63,11 +63,6 @@ typedef struct {
     // them, one token per sequence; the kernel rotates the query and key heads itself (float tables
     // [position][rotary_dim / 2]; rotary_dim 0: no rotation) and writes the new key and value rows to the cache
     const float* rope_cos; const float* rope_sin; int rotary_dim; int new_rows;
-    // decode kernel, optional: 1 - as many blocks as fit the GPU at once go through the list of runs, the copies of a
-    // block's next run under way while it finishes the one before (up to 256 tokens, query heads per kv head and
-    // head size small enough for two blocks a multiprocessor: the launcher refuses what does not fit); a number above 1:
-    // that many blocks (for tests)
-    int persistent;
     // filled in by the launcher: clock cycles after which a wait is given up, and the test's extra bytes
     long long wait_cycles; int test_extra_tx;
 } AttentionArgs;
@@ -79,7 +74,6 @@ int rdl_attention_decode(const AttentionArgs* a, void* stream);
 // multiples of 64; q, k_new and v_new must be the packed rows of one [tokens, row_width] buffer
 int rdl_attention_prefill_tc(const AttentionArgs* a, long long row_width, void* stream);
 long long rdl_attention_decode_counter_bytes(int n_tokens, int n_kv_heads);
-int rdl_attention_decode_persistent_fits(int n_tokens, int n_heads, int n_kv_heads, int head_dim, int page_size, int max_splits);
 long long rdl_attention_decode_scratch_bytes(int n_tokens, int n_heads, int n_kv_heads, int head_dim, int max_splits);
 
 int rdl_embed_rows(void* out_f32, const void* table, int table_dtype, const int* ids, float scale,

@@ -23,7 +23,7 @@ from concurrent.futures import ThreadPoolExecutor
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(_PKG, "csrc")
 LIB_NAME = "librdl_b200_kernels.so"
-ABI_VERSION = 12
+ABI_VERSION = 11
 
 # fast math is never enabled: the 32-bit path relies on exact tanhf/expf/sqrtf and plain FMA
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
@@ -172,7 +172,6 @@ class AttentionArgs(ctypes.Structure):
         ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_longlong),
         ("counter_bytes", ctypes.c_longlong), ("status", ctypes.c_void_p),
         ("rope_cos", ctypes.c_void_p), ("rope_sin", ctypes.c_void_p), ("rotary_dim", ctypes.c_int), ("new_rows", ctypes.c_int),
-        ("persistent", ctypes.c_int),
         ("wait_cycles", ctypes.c_longlong), ("test_extra_tx", ctypes.c_int),     # filled in by the launcher
     ]
 
@@ -262,8 +261,6 @@ def load():
             fn.restype = ctypes.c_int
         lib.rdl_attention_decode_scratch_bytes.argtypes = [_I, _I, _I, _I, _I]
         lib.rdl_attention_decode_counter_bytes.argtypes = [_I, _I]
-        lib.rdl_attention_decode_persistent_fits.argtypes = [_I, _I, _I, _I, _I, _I]
-        lib.rdl_attention_decode_persistent_fits.restype = _I
         lib.rdl_attention_decode_counter_bytes.restype = _LL
         lib.rdl_attention_decode_scratch_bytes.restype = _LL
         lib.rdl_sampling_uniform.argtypes = [ctypes.c_ulonglong] * 3

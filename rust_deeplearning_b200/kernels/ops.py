@@ -525,23 +525,17 @@ def choose_keys_per_split(n_tokens: int, n_kv_heads: int, max_keys: int, page_si
     return page_size
 
 
-DECODE_PERSISTENT = os.environ.get("RDL_DECODE_PERSISTENT", "1") != "0"     # 0: one block a run always, for comparison
-
-
 def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n_heads: int, n_kv_heads: int,
               head_dim: int, score_scale: float, softcap: Optional[float], window: Optional[int],
               new_kv: Optional[Tuple[torch.Tensor, int, int]] = None, kind: str = "auto",
               scratch=None, keys_per_split: Optional[int] = None, status: Optional[torch.Tensor] = None,
-              rotate_and_write: Optional[Tuple[Optional[torch.Tensor], Optional[torch.Tensor], int]] = None,
-              persistent: Optional[bool] = None):
+              rotate_and_write: Optional[Tuple[Optional[torch.Tensor], Optional[torch.Tensor], int]] = None):
     """Attention of the step's tokens over cache and new rows.
 
     q: [tokens, >= n_heads * head_dim] rows whose first n_heads * head_dim values are the (rotated)
     query heads; the row stride may be larger (packed q/k/v rows).
     new_kv: (rows, k_col, v_col) - this step's packed rows and the columns at which the rotated
     keys and the values start; needed when `b.seq_cached` says that new keys are not in the cache.
-    persistent (kind "decode"): True / False forces or forbids the form in which the blocks go through the list of
-    runs (a number above 1: with that many blocks); None: chosen here.
     kind: "plain" (float arithmetic, any dtype), "prefill" (bfloat16, mma.sync tensor cores, keys from
     cache and packed rows), "prefill_tc" (bfloat16, TMA + tcgen05, for sequences that start at position 0
     with head_dim a multiple of 64), "decode" (bfloat16, split keys; reads the cache only), or "auto".
@@ -599,14 +593,6 @@ def attention(q: torch.Tensor, b: AttentionBatch, pages: Optional[KVPages], *, n
         _need(buf.dtype is torch.float32 and buf.numel() * 4 >= need, "attention: decode scratch too small")
         a.scratch, a.scratch_bytes = buf.data_ptr(), buf.numel() * 4
         a.counter_bytes = lib.rdl_attention_decode_counter_bytes(b.n_tokens, n_kv_heads)
-        # More runs than blocks fit the GPU at once (many sequences, long contexts): the blocks go through the list of
-        # runs, the copies of a block's next run under way while it finishes the one before.
-        fits = bool(lib.rdl_attention_decode_persistent_fits(b.n_tokens, n_heads, n_kv_heads, head_dim, pages.page_size, a.max_splits))
-        if persistent is None:
-            runs = b.n_tokens * n_kv_heads * max(1, -(-b.max_keys // ks))
-            persistent = DECODE_PERSISTENT and fits and runs > 2 * sm_count(q.device.index or 0)
-        _need(fits or not persistent, "attention: the persistent decode form does not take this shape")
-        a.persistent = int(persistent)
         a.status = _status(status)
         if rotate_and_write is not None:
             cos, sin, rotary_dim = rotate_and_write

@@ -143,7 +143,7 @@ def rope_cache(qkv, n_heads, n_kv_heads, head_dim, *, tok_seq, tok_pos, cos=None
 
 
 def attention(q, b, pages, *, n_heads, n_kv_heads, head_dim, score_scale, softcap, window, new_kv=None,
-              kind="auto", scratch=None, keys_per_split=None, status=None, rotate_and_write=None, persistent=None):
+              kind="auto", scratch=None, keys_per_split=None, status=None, rotate_and_write=None):
     if rotate_and_write is not None:
         # the step's rows as the projection left them: rotate a copy, write the cache, then read everything from it
         cos, sin, rotary_dim = rotate_and_write

@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import kernel_refs as ref
-from rust_deeplearning_b200.kernels import library, ops
+from rust_deeplearning_b200.kernels import ops
 from rust_deeplearning_b200.sampling.sampler import uniform_for
 
 pytestmark = pytest.mark.gpu
@@ -383,19 +383,15 @@ DECODE_SHAPES = [
 
 
 @pytest.mark.parametrize("shape", DECODE_SHAPES)
-@pytest.mark.parametrize("keys_per_split", [None, "one_page", "eight_pages", "one_page_persistent"])
+@pytest.mark.parametrize("keys_per_split", [None, "one_page", "eight_pages"])
 def test_decode_attention_over_cache(shape, keys_per_split):
     shape = dict(shape)
     past = shape.pop("past")
     c = Case(past=past, new=[1] * len(past), dtype=torch.bfloat16, seed=40, **shape)
     b = c.batch("all")
-    # "persistent": the blocks go through the list of runs (forced here, and with few blocks so that each has several)
-    ks = {None: None, "one_page": c.page_size, "eight_pages": 8 * c.page_size, "one_page_persistent": c.page_size}[keys_per_split]
-    pers = 3 if keys_per_split == "one_page_persistent" else None          # three blocks: several runs each
-    if pers and not library.load().rdl_attention_decode_persistent_fits(c.T, c.n_heads, c.n_kv_heads, c.head_dim, c.page_size, 64):
-        pytest.skip("more query heads per kv head than the persistent form's shared memory takes")
+    ks = {None: None, "one_page": c.page_size, "eight_pages": 8 * c.page_size}[keys_per_split]
     for softcap in (None, 7.0):
-        got = ops.attention(c.qkv, b, c.pages, kind="decode", keys_per_split=ks, persistent=pers, **c.kw(softcap=softcap))
+        got = ops.attention(c.qkv, b, c.pages, kind="decode", keys_per_split=ks, **c.kw(softcap=softcap))
         want = ref.attention(c.qkv, b, c.pages, **c.kw(softcap=softcap))
         assert_close(got, want, torch.bfloat16, rel=6.0, what=f"decode softcap={softcap}")
         plain = ops.attention(c.qkv, b, c.pages, kind="plain", **c.kw(softcap=softcap))
@@ -422,12 +418,10 @@ def test_decode_attention_rotates_and_writes_the_new_rows(shape, rotary):
     ref_pages = ops.KVPages(c.k.clone(), c.v.clone(), c.pages.tables, c.page_size, c.ring_pages)
     want = ref.attention(c.qkv, b, ref_pages, new_kv=c.new_kv(), rotate_and_write=rw, **c.kw(softcap=9.0))
     rows_before = c.qkv.clone()
-    fits = library.load().rdl_attention_decode_persistent_fits(c.T, c.n_heads, c.n_kv_heads, c.head_dim, c.page_size, 64)
-    # chosen by the wrapper; one page a block; one page a run with two blocks going through the list of runs
-    for ks, pers in ((None, None), (c.page_size, None)) + (((c.page_size, 2),) if fits else ()):
+    for ks in (None, c.page_size):
         got_pages = ops.KVPages(c.k.clone(), c.v.clone(), c.pages.tables, c.page_size, c.ring_pages)
         got = ops.attention(c.qkv, b, got_pages, new_kv=c.new_kv(), kind="decode", keys_per_split=ks, rotate_and_write=rw,
-                            persistent=pers, **c.kw(softcap=9.0))
+                            **c.kw(softcap=9.0))
         assert_close(got, want, torch.bfloat16, rel=6.0, what=f"output, keys_per_split={ks}")
         assert torch.equal(c.qkv, rows_before), "the packed rows must stay as the projection left them"
         # value rows are copied (equal bits); key rows are rotated in float and rounded once, as the reference does
@@ -464,8 +458,6 @@ def test_attention_finds_one_far_key(sizes):
         for kind in ("decode", "plain"):
             got = ops.attention(c.qkv, b, c.pages, kind=kind, **c.kw(scale=1.0))
             assert_close(got, want, torch.bfloat16, rel=6.0, what=f"{kind} window={window} key={far}")
-        got = ops.attention(c.qkv, b, c.pages, kind="decode", persistent=5, **c.kw(scale=1.0))        # five blocks over all runs
-        assert_close(got, want, torch.bfloat16, rel=6.0, what=f"decode, persistent, window={window} key={far}")
 
 
 @pytest.mark.parametrize("kind", ["prefill", "prefill_tc", "plain"])
