@@ -26,7 +26,7 @@ constexpr int SAMPLE_THREADS = 1024;
 
 // order-preserving map from float to unsigned
 __device__ __forceinline__ unsigned ordered_key(float f) {
-    const unsigned u = __float_as_uint(f);
+    const unsigned u = __float_as_uint(f + 0.0f);          // -0 becomes +0: the two are one value and must have one key
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 

@@ -554,6 +554,24 @@ def test_sampling(vocab):
             assert got == want, (kw, step, got, want)
 
 
+@pytest.mark.parametrize("vocab", [256, 40000])
+def test_sampling_takes_minus_zero_for_zero(vocab):
+    """Logits that are +0 and -0 in turn are all equal: the thresholds of top-k and top-p (found on bit patterns)
+    keep all of them, as a comparison of values does."""
+    rows = 4
+    logits = torch.zeros((rows, vocab), dtype=torch.float32, device=DEV)
+    logits[:, ::2] = -0.0
+    logits[1, 5] = 1.0
+    stream = torch.arange(rows, dtype=torch.int64, device=DEV)
+    steps = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    hist = torch.zeros(0, dtype=torch.int32, device=DEV)
+    starts = torch.zeros(rows + 1, dtype=torch.int32, device=DEV)
+    for kw in (dict(top_k=7), dict(top_p=0.5), dict(top_k=3, top_p=0.9)):
+        for seed in (1, 2, 3):
+            args = dict(temperature=0.7, seed=seed, row_stream=stream, row_step=steps, history=hist, history_start=starts, **kw)
+            assert ops.sample(logits, **args).tolist() == ref.sample(logits, **args).tolist(), (kw, seed)
+
+
 def test_sampling_writes_pinned_host_memory_and_upload_takes_fed_tokens():
     """The sampler's tokens arrive in pinned host memory without a copy of its own; the kernel that brings a step's
     batch description to the device puts the tokens of an earlier sampling in place on the way."""
