@@ -184,6 +184,48 @@ def attention(q, b, pages, *, n_heads, n_kv_heads, head_dim, score_scale, softca
     return out
 
 
+def attention_vectorised(q, b, pages, *, n_heads, n_kv_heads, head_dim, score_scale, softcap, window, new_kv=None):
+    """The same function as `attention`, a sequence at a time with whole matrices (float64 on the tensors'
+    device): for cases of thousands of keys, where the loop above over every key of every head takes minutes.
+    `tests/test_attention_random_gpu.py` holds the two against each other on small cases."""
+    def logical(stored):        # every row of every page in its logical order
+        n_pages, n_kv, rows, hd = stored.shape
+        idx = torch.stack([_swizzle_index(r, hd, stored.element_size()) for r in range(rows)]).to(stored.device)
+        return torch.gather(stored, 3, idx[None, None].expand(n_pages, n_kv, rows, hd))
+    k_all, v_all = logical(pages.k), logical(pages.v)
+    out = torch.zeros((q.shape[0], n_heads * head_dim), dtype=q.dtype, device=q.device)
+    group = n_heads // n_kv_heads
+    ps, ring = pages.page_size, pages.ring_pages
+    scale = float(torch.tensor(score_scale, dtype=torch.float32))
+    for i in range(b.n_seqs):
+        r0, r1 = int(b.seq_start[i]), int(b.seq_start[i + 1])
+        if r1 == r0:
+            continue
+        past, cached = int(b.seq_past[i]), int(b.seq_cached[i])
+        total = past + (r1 - r0)
+        j = torch.arange(total, device=q.device)
+        page = pages.tables[i][((j // ps) % ring).long()].long()
+        # (in a ring the rows of positions that have been overwritten are wrong here; the window masks them below)
+        K = k_all[page, :, (j % ps).long(), :].to(F64)           # [positions, kv heads, head_dim]
+        V = v_all[page, :, (j % ps).long(), :].to(F64)
+        if cached < total:
+            rows, k_col, v_col = new_kv
+            width = n_kv_heads * head_dim
+            K[cached:] = rows[r0 + (cached - past):r1, k_col:k_col + width].reshape(-1, n_kv_heads, head_dim).to(F64)
+            V[cached:] = rows[r0 + (cached - past):r1, v_col:v_col + width].reshape(-1, n_kv_heads, head_dim).to(F64)
+        Q = q[r0:r1, :n_heads * head_dim].reshape(-1, n_kv_heads, group, head_dim).to(F64)
+        p = b.tok_pos[r0:r1].long()
+        s = torch.einsum("tkgd,jkd->tkgj", Q, K) * scale
+        if softcap:
+            s = softcap * torch.tanh(s / softcap)
+        seen = j[None, :] <= p[:, None]
+        if window:
+            seen &= j[None, :] > p[:, None] - window
+        a = torch.softmax(s.masked_fill(~seen[:, None, None, :], -math.inf), dim=-1)
+        out[r0:r1] = torch.einsum("tkgj,jkd->tkgd", a, V).reshape(r1 - r0, -1).to(q.dtype)
+    return out
+
+
 def sample(logits, *, temperature, top_k=None, top_p=None, repetition_penalty=None, seed=0, row_stream=None,
            row_step=None, history=None, history_start=None, out=None, host_out=None):
     """Follows the kernel's stated semantics (penalty once per distinct token; ties at the top-p
