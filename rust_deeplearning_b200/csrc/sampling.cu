@@ -9,9 +9,9 @@
 //   top-k: keep values >= the k-th largest (ties kept)    sampling.rs:38-52
 //   top-p: keep the smallest set of most probable tokens whose mass reaches p   sampling.rs:56-87
 //   draw: softmax, first index whose cumulative probability exceeds r           sampling.rs:91-106
-// (sampling.rs = rustml/nlp/main/src/core/sampling.rs).  Differences, all by design:
-//   - the penalty is applied once per distinct token of the history (the reference applies it
-//     once per occurrence);
+// (sampling.rs = rustml/nlp/main/src/core/sampling.rs).  The penalty is applied once per occurrence of a token in
+// the history, as the reference's loop over the history does (a token seen n times is penalised n times; every
+// application rounds to float like the reference's).  Differences, all by design:
 //   - tokens whose probability ties with the last kept one in top-p are all kept;
 //   - r comes from a counter-based generator keyed by (seed, the row's stream id, the row's
 //     step), so a row's draw does not depend on what else is in the batch (the reference draws
@@ -28,6 +28,18 @@ constexpr int SAMPLE_THREADS = 1024;
 __device__ __forceinline__ unsigned ordered_key(float f) {
     const unsigned u = __float_as_uint(f + 0.0f);          // -0 becomes +0: the two are one value and must have one key
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// One application of the repetition penalty to the logit at `addr`, atomically: the occurrences of a token in the
+// history are handled by different threads, and n applications give the same bits in any order.
+__device__ __forceinline__ void penalise(float* addr, float penalty) {
+    unsigned* bits = reinterpret_cast<unsigned*>(addr);
+    unsigned old = *bits, assumed;
+    do {
+        assumed = old;
+        const float v = __uint_as_float(assumed);
+        old = atomicCAS(bits, assumed, __float_as_uint(v > 0.f ? v / penalty : v * penalty));
+    } while (old != assumed);
 }
 
 __host__ __device__ inline unsigned long long splitmix64(unsigned long long x) {
@@ -132,18 +144,18 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(int* __restrict_
     }
 
     float* w = work + (long long)row * vocab;
-    // ---- penalty (once per distinct token, from the untouched logits) and temperature ----
-    for (int i = tid; i < vocab; i += SAMPLE_THREADS) w[i] = x[i] / prm.temperature;
+    // ---- penalty (once per occurrence in the history), then temperature ----
+    const bool penalty = prm.repetition_penalty != 1.0f && history;
+    for (int i = tid; i < vocab; i += SAMPLE_THREADS) w[i] = penalty ? x[i] : x[i] / prm.temperature;
     __syncthreads();
-    if (prm.repetition_penalty != 1.0f && history) {
+    if (penalty) {
         const int hb = history_start[row], he = history_start[row + 1];
         for (int i = hb + tid; i < he; i += SAMPLE_THREADS) {
             const int tok = history[i];
-            if (tok >= 0 && tok < vocab) {
-                const float v = x[tok];
-                w[tok] = (v > 0.f ? v / prm.repetition_penalty : v * prm.repetition_penalty) / prm.temperature;  // equal writers
-            }
+            if (tok >= 0 && tok < vocab) penalise(w + tok, prm.repetition_penalty);
         }
+        __syncthreads();
+        for (int i = tid; i < vocab; i += SAMPLE_THREADS) w[i] = w[i] / prm.temperature;
         __syncthreads();
     }
     // ---- top-k: threshold = k-th largest value, found bit by bit on ordered keys ----
@@ -401,7 +413,7 @@ __global__ void __launch_bounds__(CL_THREADS, 1) sample_cluster_kernel(int* __re
     const int first = rank * CL_PER_BLOCK + tid * CL_ITEMS;   // this thread's first element
     int parity = 0;
 
-    // ---- penalty (once per distinct token, from the untouched logits) and temperature ----
+    // ---- penalty (once per occurrence in the history) and temperature ----
     const float* src = x;
     const bool penalty = prm.repetition_penalty != 1.0f && history;
     if (penalty) {
@@ -414,10 +426,7 @@ __global__ void __launch_bounds__(CL_THREADS, 1) sample_cluster_kernel(int* __re
             const int hb = history_start[row], he = history_start[row + 1];
             for (int i = hb + tid; i < he; i += CL_THREADS) {
                 const int tok = history[i];
-                if (tok >= 0 && tok < vocab) {
-                    const float v = x[tok];
-                    w[tok] = v > 0.f ? v / prm.repetition_penalty : v * prm.repetition_penalty;   // equal writers
-                }
+                if (tok >= 0 && tok < vocab) penalise(w + tok, prm.repetition_penalty);
             }
             __threadfence();
         }

@@ -228,8 +228,8 @@ def attention_vectorised(q, b, pages, *, n_heads, n_kv_heads, head_dim, score_sc
 
 def sample(logits, *, temperature, top_k=None, top_p=None, repetition_penalty=None, seed=0, row_stream=None,
            row_step=None, history=None, history_start=None, out=None, host_out=None):
-    """Follows the kernel's stated semantics (penalty once per distinct token; ties at the top-p
-    threshold kept), in float32 like the reference's sampling functions."""
+    """Follows the kernel's stated semantics (ties at the top-p threshold kept), in float32 like the
+    reference's sampling functions; the penalty once per occurrence in the history, each in float32."""
     from rust_deeplearning_b200.sampling.sampler import uniform_for
     rows, vocab = logits.shape
     res = torch.zeros(rows, dtype=torch.int32, device=logits.device)
@@ -238,13 +238,13 @@ def sample(logits, *, temperature, top_k=None, top_p=None, repetition_penalty=No
         if temperature < 1e-7:
             res[r] = int(torch.argmax(x))       # torch returns the first maximum
             continue
-        w = x / temperature
         if repetition_penalty not in (None, 1.0) and history is not None:
             hb, he = int(history_start[r]), int(history_start[r + 1])
-            for tok in set(int(v) for v in history[hb:he]):
+            for tok in (int(v) for v in history[hb:he]):
                 if 0 <= tok < vocab:
                     v = x[tok]
-                    w[tok] = (v / repetition_penalty if v > 0 else v * repetition_penalty) / temperature
+                    x[tok] = v / repetition_penalty if v > 0 else v * repetition_penalty
+        w = x / temperature
         if top_k and top_k < vocab:
             thr = torch.sort(w).values[vocab - top_k]
             w[w < thr] = -math.inf

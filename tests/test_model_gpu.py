@@ -152,11 +152,13 @@ def test_greedy_generation_through_the_entry_point(name):
     assert compared > 0
 
 
-@pytest.mark.parametrize("options", [dict(), dict(top_k=20), dict(top_p=0.9), dict(top_k=50, top_p=0.95)])
+@pytest.mark.parametrize("options", [dict(), dict(top_k=20), dict(top_p=0.9), dict(top_k=50, top_p=0.95),
+                                     dict(repetition_penalty=1.2), dict(top_k=5, repetition_penalty=1.5)])
 def test_temperature_generation_equals_the_plain_sampler(options):
     """T = 0.8, seeded: the tokens of the BASELINE workload of tiny B (prompts of 1, 9, 23 and 40 tokens, 12 new)
     equal what the plain implementation samples from its own logits with the same uniform numbers
-    (seed, request index, step) - as a batch, and one request at a time."""
+    (seed, request index, step) - as a batch, and one request at a time.  With a repetition penalty a token
+    that came n times (in the prompt or since) is penalised n times, as the reference's loop over the history does."""
     from rust_deeplearning_b200 import Generator
     from rust_deeplearning_b200.sampling.sampler import uniform_for
     name, seed, new = "B", 7, 12
@@ -172,7 +174,8 @@ def test_temperature_generation_equals_the_plain_sampler(options):
         want.append(tokens)
     gen = (Generator(mh.loaded_model(name, "float32"), max_batch=4, max_context=128)
            .with_temperature(0.8).with_seed(seed).with_stop_tokens([])
-           .with_top_k(options.get("top_k")).with_top_p(options.get("top_p")))
+           .with_top_k(options.get("top_k")).with_top_p(options.get("top_p"))
+           .with_repetition_penalty(options.get("repetition_penalty")))
     assert gen.generate_batch(prompts, new) == want
     # one at a time: request i alone is request 0 of its own call, so its stream is keyed by 0
     alone = gen.generate(prompts[0], new)
