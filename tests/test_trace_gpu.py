@@ -141,3 +141,36 @@ def test_replay_portions_and_mixed_steps(tmp_path, name, dtype):
     ]
     out = replay(name, dtype, steps, max_tokens=384, out_dir=str(tmp_path))
     check(name, dtype, steps, out, seqs)
+
+
+@pytest.mark.parametrize("case,name,dtype", [(0, "A", "float32"), (1, "B", "bfloat16"), (2, "D", "bfloat16"), (3, "E", "float32")])
+def test_replay_of_a_trace_drawn_at_random_with_the_cache_at_its_bound(tmp_path, case, name, dtype):
+    """One to four batches of one to five requests of 1 to 149 tokens, prompts cut anywhere, requests ended
+    anywhere (also before their last token), logits wanted at random places - and --max-tokens set to exactly
+    what the protocol promises: the most that live requests hold at any time, each rounded up to 64."""
+    rng = np.random.default_rng(case)
+    V = tiny_configs.config(name)[0]["vocab_size"]
+    seqs, steps, most = {}, [], 0
+    held = lambda lengths: sum(-(-n // 64) * 64 for n in lengths)
+    for batch in range(int(rng.integers(1, 5))):
+        members = [f"b{batch}r{i}" for i in range(int(rng.integers(1, 6)))]
+        for m in members:
+            seqs[m] = mh.prompt(int(rng.integers(0, 1 << 30)), int(rng.integers(1, 150)), V)
+        pos = {m: int(rng.integers(1, len(seqs[m]) + 1)) for m in members}
+        stop_at = {m: int(rng.integers(pos[m], len(seqs[m]) + 1)) for m in members}
+        ending = [m for m in members if pos[m] >= stop_at[m]]
+        steps.append({"step": len(steps), "end": list(ending), "entries": [
+            {"id": m, "tokens": seqs[m][:pos[m]], "want": sorted(set(int(v) for v in rng.integers(0, pos[m], size=int(rng.integers(0, 4)))))}
+            for m in members]})
+        most = max(most, held(pos[m] for m in members))
+        live = [m for m in members if m not in ending]
+        while live:
+            for m in live:
+                pos[m] += 1
+            most = max(most, held(pos[m] for m in live))
+            ending = [m for m in live if pos[m] >= stop_at[m]]
+            steps.append({"step": len(steps), "end": list(ending), "entries": [
+                {"id": m, "tokens": [seqs[m][pos[m] - 1]], "want": [0] if rng.integers(0, 3) else []} for m in live]})
+            live = [m for m in live if m not in ending]
+    out = replay(name, dtype, steps, max_tokens=most, out_dir=str(tmp_path))
+    check(name, dtype, steps, out, seqs)
