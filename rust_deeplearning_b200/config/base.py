@@ -9,6 +9,7 @@ error that lists what is registered.
 from __future__ import annotations
 
 import json
+import math
 import os
 from dataclasses import dataclass
 from typing import Any, Callable, Dict
@@ -39,7 +40,8 @@ class ConfigReader:
             return None
         return default
 
-    def integer(self, key, default=_MISSING, minimum=None):
+    def integer(self, key, default=_MISSING, minimum=None, maximum=2 ** 31 - 1):
+        """A whole number; by default at most 2^31 - 1, which is what the kernels' 32-bit indices hold."""
         v = self._get(key, default)
         if v is None:
             return None
@@ -51,6 +53,9 @@ class ConfigReader:
                 return None
         if minimum is not None and v < minimum:
             self.problems.append(f"key '{key}' must be >= {minimum}, got {v}")
+        if maximum is not None and v > maximum:
+            self.problems.append(f"key '{key}' must be <= {maximum}, got {v}")
+            return None
         return v
 
     def number(self, key, default=_MISSING, positive=False):
@@ -59,6 +64,9 @@ class ConfigReader:
             return None
         if isinstance(v, bool) or not isinstance(v, (int, float)):
             self.problems.append(f"key '{key}' must be a number, got {v!r}")
+            return None
+        if not math.isfinite(v):
+            self.problems.append(f"key '{key}' must be a finite number, got {v!r}")
             return None
         if positive and not v > 0:
             self.problems.append(f"key '{key}' must be > 0, got {v}")
@@ -129,15 +137,19 @@ def registered_architectures():
 
 def architecture_for(raw: Dict[str, Any]) -> Architecture:
     """Choose by `architectures[0]`, else by `model_type`; an unknown name is an error."""
+    if not isinstance(raw, dict):
+        raise ConfigError("config.json must hold a JSON object")
     names = raw.get("architectures") or []
     if isinstance(names, str):
         names = [names]
+    if not isinstance(names, (list, tuple)):
+        raise ConfigError(f"key 'architectures' must be a list of names, got {names!r}")
     for n in names:
-        if n in _ARCHITECTURES:
+        if isinstance(n, str) and n in _ARCHITECTURES:
             return _ARCHITECTURES[n]
     mt = raw.get("model_type")
     for arch in _ARCHITECTURES.values():
-        if mt is not None and arch.model_type == mt:
+        if isinstance(mt, str) and arch.model_type == mt:
             return arch
     raise ConfigError(
         f"no registered architecture for architectures={names!r}, model_type={mt!r}; "

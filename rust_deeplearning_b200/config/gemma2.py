@@ -50,7 +50,7 @@ class Gemma2Config:
     @staticmethod
     def from_dict(raw: Dict[str, Any]) -> "Gemma2Config":
         r = ConfigReader(raw, "Gemma2 config")
-        L = r.integer("num_hidden_layers", minimum=1)
+        L = r.integer("num_hidden_layers", minimum=1, maximum=65536)
         H = r.integer("hidden_size", minimum=1)
         nh = r.integer("num_attention_heads", minimum=1)
         # optional in the reference too, falling back to the number of heads (types.rs:340, :606)

@@ -10,6 +10,7 @@ read from disk only when it is copied to the device.
 from __future__ import annotations
 
 import json
+import math
 import os
 import struct
 from typing import Dict, Iterable, Optional, Tuple
@@ -65,13 +66,15 @@ class SafetensorsFile:
         spans = []
         for name, info in header.items():
             try:
-                dtype, shape = info["dtype"], tuple(int(s) for s in info["shape"])
-                begin, end = (int(v) for v in info["data_offsets"])
+                dtype, shape, (begin, end) = info["dtype"], tuple(info["shape"]), info["data_offsets"]
             except (KeyError, TypeError, ValueError):
                 raise SafetensorsError(f"{path}: malformed header entry for '{name}'") from None
-            if dtype not in _DTYPES:
+            whole = lambda v: isinstance(v, int) and not isinstance(v, bool) and v >= 0
+            if not (isinstance(info["shape"], list) and all(whole(v) for v in shape) and whole(begin) and whole(end)):
+                raise SafetensorsError(f"{path}: malformed header entry for '{name}': sizes and offsets must be whole numbers")
+            if not isinstance(dtype, str) or dtype not in _DTYPES:
                 raise SafetensorsError(f"{path}: tensor '{name}' has unsupported dtype {dtype}")
-            numel = int(np.prod(shape, dtype=np.int64)) if shape else 1
+            numel = math.prod(shape)       # Python integers: no overflow
             if not (0 <= begin <= end <= data_size) or end - begin != numel * _DTYPES[dtype][2]:
                 raise SafetensorsError(
                     f"{path}: tensor '{name}' ({dtype}{list(shape)}) does not match its data range [{begin}, {end}) "

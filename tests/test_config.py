@@ -107,6 +107,17 @@ def test_all_problems_are_reported_together():
     bad["layer_types"] = ["sliding_attention"] * 25
     with pytest.raises(ConfigError):
         load_config(bad)
+    # sizes beyond what 32-bit indices hold, numbers that are not finite, names of the wrong type: refused, not tried
+    for key, value in (("num_hidden_layers", 2 ** 40), ("vocab_size", 2 ** 31), ("rms_norm_eps", float("inf")),
+                       ("rope_theta", float("nan")), ("architectures", 5), ("architectures", [5, None]), ("model_type", ["gemma2"])):
+        bad = copy.deepcopy(GEMMA2_2B)
+        bad[key] = value
+        if key == "architectures":
+            bad.pop("model_type", None)
+        if key == "model_type":
+            bad.pop("architectures", None)
+        with pytest.raises(ConfigError):
+            load_config(bad)
 
 
 def test_config_json_from_a_folder(tmp_path):

@@ -59,6 +59,19 @@ def test_broken_files_are_refused(tmp_path):
             SafetensorsFile(bad)
     with pytest.raises(SafetensorsError):
         WeightFiles(str(tmp_path / "nothing_here"))
+    # header entries with sizes that are no whole numbers, negative, or too large for 64 bits; names that are no strings
+    import json
+    header = json.loads(blob[8:8 + hlen])
+    for key, value in (("shape", [2 ** 70]), ("shape", [-4, -4]), ("shape", [1.5, 4]), ("shape", "4x4"), ("shape", [True, 16]),
+                       ("data_offsets", [0, 2 ** 70]), ("data_offsets", [0.0, 64.0]), ("data_offsets", [5]), ("dtype", ["F32"]),
+                       ("dtype", None)):
+        h = json.loads(json.dumps(header))
+        h["a"][key] = value
+        hb = json.dumps(h).encode()
+        bad = str(tmp_path / "bad_entry.safetensors")
+        open(bad, "wb").write(struct.pack("<Q", len(hb)) + hb + bytes(blob[8 + hlen:]))
+        with pytest.raises(SafetensorsError):
+            SafetensorsFile(bad)
 
 
 @pytest.mark.parametrize("name", ["A", "B"])
