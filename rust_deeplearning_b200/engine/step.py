@@ -123,11 +123,14 @@ class Engine:
         elif len(want) != n:
             raise StepError("`want` must name places for every sequence")
         for i, (w, l) in enumerate(zip(want, lens)):
-            if any(not 0 <= int(x) < l for x in w):
-                raise StepError(f"sequence {i}: a wanted place is outside its {l} new tokens")
+            if any(isinstance(x, (bool, float)) or not 0 <= int(x) < l for x in w):
+                raise StepError(f"sequence {i}: a wanted place is outside its {l} new tokens (or no whole number)")
         # the ids as arrays, once: checked here, copied into the batch description below (a list of 2,048 ids costs
         # 60-80 us to convert, and the device waits meanwhile)
-        tokens = [np.asarray(t, dtype=np.int64).reshape(-1) for t in tokens]
+        tokens = [np.asarray(t).reshape(-1) for t in tokens]
+        if any(t.dtype.kind not in "iu" for t in tokens):
+            raise StepError("token ids must be whole numbers")
+        tokens = [t.astype(np.int64, copy=False) for t in tokens]
         flat = np.concatenate(tokens) if n > 1 else tokens[0]
         if flat.min() < 0 or flat.max() >= self.model.vocab_size:
             raise StepError(f"token id outside the vocabulary of {self.model.vocab_size}")

@@ -112,7 +112,89 @@ def test_wanted_places_and_errors(tmp_path, monkeypatch):
         engine.step([s0], [[256]])
     with pytest.raises(StepError):
         engine.step([s0], [[]])
+    with pytest.raises(StepError):
+        engine.step([s0], [[1.5]])                # no whole number: refused, not cut down to 1
+    with pytest.raises(StepError):
+        engine.step([s0], [[True]])
+    with pytest.raises(StepError):
+        engine.step([s0], [[3, 4]], [[0.5]])
     assert engine.length(s0) == 7                 # failed steps changed nothing
+
+
+def test_a_walk_of_valid_and_invalid_steps_drawn_at_random(tmp_path, monkeypatch):
+    """Four slots on a cache of 160 rows: sequences begin and are given back, steps bring 1 to 17 tokens for any
+    subset of them and want any places, and about a third of the steps are wrong in one way (an empty list, an id
+    outside the vocabulary or no whole number, a slot twice or not in use, a wanted place outside, more tokens than
+    the context or the cache holds, tokens for too few sequences).  A wrong step raises the engine's own error and
+    changes no length; a right one gives the plain implementation's logits, whatever came before."""
+    import random
+    from rust_deeplearning_b200.cache.cache import CacheError
+    from rust_deeplearning_b200.engine.step import StepError
+    engine, cfg, w = build(tmp_path, "A", monkeypatch, page_size=4, max_tokens=160, max_seqs=4)
+    V = cfg["vocab_size"]
+    rnd = random.Random(5)
+    live, checked, refused = {}, 0, 0          # slot -> the tokens it holds
+    for _ in range(90):
+        kind = rnd.random()
+        if kind < 0.15 and len(live) < 4:
+            live[engine.new_sequence()] = []
+            continue
+        if kind < 0.25 and live:
+            slot = rnd.choice(list(live))
+            engine.release(slot)
+            del live[slot]
+            continue
+        if kind < 0.30:
+            with pytest.raises((StepError, CacheError)):
+                if rnd.random() < 0.5:
+                    engine.release(rnd.choice([-1, 99] + [s for s in range(4) if s not in live]))
+                else:
+                    for _ in range(5 - len(live)):
+                        live[engine.new_sequence()] = []
+            refused += 1
+            continue
+        if not live:
+            continue
+        slots = rnd.sample(list(live), rnd.randint(1, len(live)))
+        toks = [[rnd.randrange(V) for _ in range(rnd.choice([1, 1, 2, 5, 17]))] for _ in slots]
+        want = rnd.choice(["last", "all", None])
+        if want is None:
+            want = [sorted(rnd.sample(range(len(t)), rnd.randint(0, len(t)))) for t in toks]
+        before = {s: engine.length(s) for s in live}
+        if rnd.random() < 0.35:
+            k = rnd.randrange(9)
+            if k == 0: toks[0] = []
+            elif k == 1: toks[0] = [V + rnd.randrange(3)]
+            elif k == 2: toks[0] = [-1]
+            elif k == 3: slots, toks = slots + [slots[0]], toks + [toks[0]]
+            elif k == 4: slots[0] = rnd.choice([-1, 99] + [s for s in range(4) if s not in live])
+            elif k == 5: want = [[len(t)] for t in toks]
+            elif k == 6: toks[0] = [rnd.randrange(V) for _ in range(600)]
+            elif k == 7: toks = toks[:-1] if len(toks) > 1 else toks + [[1]]
+            elif k == 8: toks[0] = [1.5]
+            if k in (5, 7) and not isinstance(want, str) and len(want) != len(toks):
+                want = "last"
+            with pytest.raises((StepError, CacheError)):
+                engine.step(slots, toks, want)
+            assert {s: engine.length(s) for s in live} == before, f"a refused step (kind {k}) changed a length"
+            refused += 1
+            continue
+        try:
+            got = engine.step(slots, toks, want)
+        except CacheError:                      # the cache is full: nothing may have changed
+            assert {s: engine.length(s) for s in live} == before
+            refused += 1
+            continue
+        places = [[len(t) - 1] for t in toks] if want == "last" else ([list(range(len(t))) for t in toks] if want == "all" else want)
+        rows = []
+        for slot, t, ws in zip(slots, toks, places):
+            if ws:
+                rows += list(plain.forward(cfg, w, live[slot] + t)[[len(live[slot]) + i for i in ws]])
+            live[slot] = live[slot] + t
+        if rows:
+            close(got, np.stack(rows))
+            checked += 1
+    assert checked > 20 and refused > 10, (checked, refused)
 
 
 def test_a_run_that_reads_another_runs_ring_sees_the_rows_of_earlier_steps(tmp_path, monkeypatch):
