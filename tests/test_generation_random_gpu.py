@@ -1,6 +1,7 @@
 """Generation workloads drawn at random (seeded): 1 to 11 requests with prompts of 1 to 49 tokens, 1 to 13 new
 tokens, batches of at most 1 to 5 requests one after another, greedy or seeded temperature sampling with top-k,
-top-p and a repetition penalty, and a stop token that the first request is known to produce - the tokens of
+top-p and a repetition penalty, a stop token that the first request is known to produce, and a context that
+some requests fill before they have their tokens - the tokens of
 `Generator.generate_batch` in float32 against the plain implementation's loop, which re-runs the whole sequence
 for every token and samples with the same uniform numbers."""
 import numpy as np
@@ -32,6 +33,7 @@ def test_generation_workloads_drawn_at_random(first):
             options["top_p"] = float(rng.choice([0.5, 0.9]))
         if temperature and rng.integers(0, 2):
             options["repetition_penalty"] = 1.2
+        max_context = int(rng.integers(max(lengths), max(lengths) + new + 3))     # some requests run out of context
         greedy = plain.generate_greedy(cfg, w, prompts[0], new, ())
         stops = frozenset([greedy[len(greedy) // 2]] if rng.integers(0, 2) else [])
         want = []
@@ -43,11 +45,13 @@ def test_generation_workloads_drawn_at_random(first):
                 if t in stops:
                     break
                 tokens.append(t)
+                if len(tokens) > max_context:       # it was sampled from the last position; it cannot be fed back
+                    break
             want.append(tokens)
-        gen = (Generator(mh.loaded_model(name, "float32"), max_batch=max_batch, max_context=128)
+        gen = (Generator(mh.loaded_model(name, "float32"), max_batch=max_batch, max_context=max_context)
                .with_temperature(temperature).with_seed(seed).with_stop_tokens(stops)
                .with_top_k(options.get("top_k")).with_top_p(options.get("top_p"))
                .with_repetition_penalty(options.get("repetition_penalty")))
         got = gen.generate_batch(prompts, new)
-        assert got == want, (f"case {case}: {name}, prompts of {lengths}, {new} new, batches of {max_batch}, T {temperature}, "
+        assert got == want, (f"case {case}: {name}, prompts of {lengths}, {new} new, context {max_context}, batches of {max_batch}, T {temperature}, "
                              f"{options}, stops {set(stops)}")
