@@ -111,21 +111,31 @@ def main(argv: Optional[List[str]] = None, stdin=None, stdout=None) -> int:
     spec = model.spec
     print(f"  arch={spec.architecture}, dim={spec.hidden_size}, layers={len(spec.layers)}, vocab={spec.vocab_size}",
           file=sys.stderr)
-    longest = max(len(p) for p in prompts) + args.max_tokens
-    gen = Generator(model, max_batch=min(len(prompts), 64), max_context=args.max_context or min(longest, model.max_positions),
-                    time_steps=args.timings)
-    gen.with_temperature(args.temperature).with_top_k(args.top_k).with_top_p(args.top_p)
-    gen.with_repetition_penalty(args.repetition_penalty).with_seed(args.seed)
-    if args.stop_ids is not None:
-        gen.with_stop_tokens(_parse_ids(args.stop_ids))
-    print(f"Generating up to {args.max_tokens} tokens for {len(prompts)} prompt(s)...", file=sys.stderr)
+    from .cache.cache import CacheError
+    from .engine.step import StepError
 
     def on_token(request, token):
         stdout.write(f"{request}\t{token}\n" if len(prompts) > 1 else f"{token}\n")
         stdout.flush()
 
     stats = GenerationStats()
-    results = gen.generate_batch_results(prompts, args.max_tokens, stream=on_token if args.stream else None, stats=stats)
+    try:
+        # what the user's numbers can get wrong (a context shorter than a prompt, an id outside the vocabulary, a
+        # sampling option outside its range) comes back as the library's own errors: one line, no traceback
+        if args.max_context is not None and args.max_context < 1:
+            raise ValueError("--max-context must be at least 1")
+        longest = max(len(p) for p in prompts) + max(args.max_tokens, 0)
+        gen = Generator(model, max_batch=min(len(prompts), 64), max_context=args.max_context or min(longest, model.max_positions),
+                        time_steps=args.timings)
+        gen.with_temperature(args.temperature).with_top_k(args.top_k).with_top_p(args.top_p)
+        gen.with_repetition_penalty(args.repetition_penalty).with_seed(args.seed)
+        if args.stop_ids is not None:
+            gen.with_stop_tokens(_parse_ids(args.stop_ids))
+        print(f"Generating up to {args.max_tokens} tokens for {len(prompts)} prompt(s)...", file=sys.stderr)
+        results = gen.generate_batch_results(prompts, args.max_tokens, stream=on_token if args.stream else None, stats=stats)
+    except (StepError, CacheError, ValueError) as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 1
     if not args.stream:
         for r in results:
             stdout.write(" ".join(str(t) for t in r.tokens) + "\n")

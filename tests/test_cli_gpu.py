@@ -71,3 +71,19 @@ def test_seeded_sampling_is_reproducible_in_bfloat16():
     assert a == b and len(a.split()) == 10
     c, _ = run(args[:-4] + ["--seed", "12", "--max-context", "128", "--stop-ids", ""])
     assert c != a
+
+
+@pytest.mark.parametrize("args,needle", [
+    (["--prompt-ids", "3 100000"], "vocabulary"),                       # an id outside the vocabulary
+    (["--prompt-ids", "1 2 3 4 5 6", "--max-context", "4"], "context"),   # a prompt longer than the context asked for
+    (["--prompt-ids", "1 2", "--temperature", "-1"], "temperature"),
+    (["--prompt-ids", "1 2", "--top-k", "0"], "top_k"),
+    (["--prompt-ids", "1 2", "--repetition-penalty", "0"], "repetition_penalty"),
+])
+def test_a_wrong_number_is_one_line_on_standard_error(args, needle):
+    r = subprocess.run([sys.executable, INFER, mh.model_folder("A"), "--max-tokens", "3", "--dtype", "float32", *args],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 1 and r.stdout == ""
+    last = r.stderr.strip().splitlines()[-1]
+    assert last.startswith("error:") and needle in last, r.stderr
+    assert "Traceback" not in r.stderr
