@@ -35,12 +35,19 @@ def run(argv=None, stdin=None, stdout=None) -> int:
     stdin = stdin or sys.stdin
     stdout = stdout or sys.stdout
 
-    from ..cache.cache import DEFAULT_PAGE_SIZE
+    from ..cache.cache import DEFAULT_PAGE_SIZE, CacheError
+    from ..config.base import ConfigError
+    from ..weights.loader import WeightError
+    from ..weights.safetensors_io import SafetensorsError
     from .api import load_model
-    from .step import Engine
+    from .step import Engine, StepError
 
     os.makedirs(args.out, exist_ok=True)
-    model = load_model(args.model, args.dtype)
+    try:
+        model = load_model(args.model, args.dtype)
+    except (ConfigError, WeightError, SafetensorsError) as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 1
     page = DEFAULT_PAGE_SIZE     # the unit requests' token counts are rounded up to
     max_tokens = max(page, -(-args.max_tokens // page) * page)
     engine = Engine(model, max_tokens=max_tokens, max_seqs=max_tokens // page,
@@ -50,27 +57,39 @@ def run(argv=None, stdin=None, stdout=None) -> int:
         line = line.strip()
         if not line:
             continue
-        msg = json.loads(line)
-        step = msg["step"]
-        entries = msg.get("entries", [])
-        if entries:
-            ids = [e["id"] for e in entries]
-            for rid in ids:
-                if rid not in slots:
-                    slots[rid] = engine.new_sequence()
-            want = [list(e.get("want", [])) for e in entries]
-            logits = engine.step([slots[r] for r in ids], [e["tokens"] for e in entries], want)
-            if sum(len(w) for w in want):
-                data = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
-                engine.check_status()
-                tmp = os.path.join(args.out, f"{step}.f32.tmp")
-                data.tofile(tmp)
-                os.replace(tmp, os.path.join(args.out, f"{step}.f32"))
-        for rid in msg.get("end", []):
-            if rid in slots:
-                engine.release(slots.pop(rid))
+        step = None
+        try:
+            msg = json.loads(line)
+            step = msg["step"]
+            entries = msg.get("entries", [])
+            if entries:
+                ids = [e["id"] for e in entries]
+                for rid in ids:
+                    if rid not in slots:
+                        slots[rid] = engine.new_sequence()
+                want = [list(e.get("want", [])) for e in entries]
+                logits = engine.step([slots[r] for r in ids], [e["tokens"] for e in entries], want)
+                if sum(len(w) for w in want):
+                    data = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
+                    engine.check_status()
+                    tmp = os.path.join(args.out, f"{step}.f32.tmp")
+                    data.tofile(tmp)
+                    os.replace(tmp, os.path.join(args.out, f"{step}.f32"))
+            for rid in msg.get("end", []):
+                if rid in slots:
+                    engine.release(slots.pop(rid))
+        except (ValueError, KeyError, TypeError, AttributeError, StepError, CacheError) as e:
+            # a line that is no step, or a step the engine refuses (an id outside the vocabulary, more tokens than
+            # --max-tokens promised): say which and stop; nothing is written for it
+            what = f"{type(e).__name__}: {e}" if not isinstance(e, (StepError, CacheError)) else str(e)
+            print(f"error: step {step if step is not None else '?'}: {what}", file=sys.stderr)
+            return 1
         stdout.write(f"done {step}\n")
         stdout.flush()
+    if engine.device.type == "cuda":
+        import torch
+        torch.cuda.synchronize()
+    engine.check_status()        # also for steps that wanted nothing
     return 0
 
 

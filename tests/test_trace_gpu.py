@@ -174,3 +174,19 @@ def test_replay_of_a_trace_drawn_at_random_with_the_cache_at_its_bound(tmp_path,
             live = [m for m in live if m not in ending]
     out = replay(name, dtype, steps, max_tokens=most, out_dir=str(tmp_path))
     check(name, dtype, steps, out, seqs)
+
+
+def test_a_step_the_engine_refuses_ends_the_replay_with_a_message(tmp_path):
+    """More tokens than --max-tokens promised, an id outside the vocabulary, a line that is no JSON: `done` for the
+    steps before, one line on standard error, exit code 1, no file for the refused step."""
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": [1, 2, 3], "want": [2]}], "end": []}]
+    for bad in ({"step": 1, "entries": [{"id": "b", "tokens": list(range(100)), "want": [0]}], "end": []},
+                {"step": 1, "entries": [{"id": "a", "tokens": [100000], "want": [0]}], "end": []},
+                "this is no step"):
+        out_dir = tmp_path / f"out{len(os.listdir(tmp_path))}"
+        lines = "".join(json.dumps(s) + "\n" for s in steps) + (bad if isinstance(bad, str) else json.dumps(bad)) + "\n"
+        r = subprocess.run([sys.executable, TRACE_RUN, "--model", mh.model_folder("A"), "--dtype", "float32", "--out", str(out_dir),
+                            "--max-tokens", "64"], input=lines, capture_output=True, text=True, timeout=300)
+        assert r.returncode == 1 and r.stdout.split() == ["done", "0"], (r.stdout, r.stderr)
+        assert r.stderr.strip().splitlines()[-1].startswith("error: step") and "Traceback" not in r.stderr, r.stderr
+        assert sorted(os.listdir(out_dir)) == ["0.f32"]
