@@ -171,3 +171,50 @@ def test_window_of_4096_wraps_its_ring(shape):
         report(f"{shape} window 4096, portions {portions}", torch.cat(got), want)
         mh.assert_logits(torch.cat(got), want, "bfloat16", f"{shape} window 4096 {portions}", bf16_fraction=REAL_BF16)
         eng.release(slot)
+
+
+@pytest.mark.parametrize("case", range(9))
+def test_batches_drawn_at_random_against_the_32_bit_engine(case):
+    """1 to 24 sequences (the split norms' 8-row and 16-row operands, the weight-streaming product without them, the
+    library product from 17 rows) of 2 to 1,500 tokens at the three widths, prompts whole or in portions of up to
+    600 tokens that mix with one another, then the last 1 to 7 tokens one by one with the shorter sequences ending
+    earlier: the bfloat16 engine's logits against the 32-bit engine's."""
+    from rust_deeplearning_b200 import Engine
+    rng = np.random.default_rng(case)
+    shape = ["2b", "27b", "9b"][case % 3]
+    V = WIDTHS[shape]["vocab_size"]
+    n = int(rng.choice([1, 3, 4, 5, 8, 9, 16, 17, 24]))
+    lengths = [int(v) for v in rng.integers(2, 1500 if n <= 8 else 400, size=n)]
+    k = int(rng.integers(1, 8))
+    cut = [max(1, n_tokens - k) for n_tokens in lengths]
+    portions = bool(rng.integers(0, 2))
+    seqs = [mh.prompt(9000 + 50 * case + i, n_tokens, V) for i, n_tokens in enumerate(lengths)]
+    outs = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine(loaded(shape, dtype), max_tokens=24 * 1536, max_seqs=24)
+        slots = [eng.new_sequence() for _ in seqs]
+        rows = []
+        if portions:
+            pos, draw = [0] * n, np.random.default_rng(case + 1)
+            while any(p < c for p, c in zip(pos, cut)):
+                live = [i for i in range(n) if pos[i] < cut[i]]
+                toks = [seqs[i][pos[i]:min(cut[i], pos[i] + int(draw.integers(1, 600)))] for i in live]
+                rows.append(eng.step([slots[i] for i in live], toks, "last").clone())
+                for i, t in zip(live, toks):
+                    pos[i] += len(t)
+        else:
+            rows.append(eng.step(slots, [s[:c] for s, c in zip(seqs, cut)], "last").clone())
+        pos = list(cut)
+        while True:
+            live = [i for i in range(n) if pos[i] < lengths[i]]
+            if not live:
+                break
+            rows.append(eng.step([slots[i] for i in live], [[seqs[i][pos[i]]] for i in live], "last").clone())
+            for i in live:
+                pos[i] += 1
+        eng.check_status()
+        outs[dtype] = torch.cat(rows)
+        del eng
+    want = outs["float32"].double().cpu().numpy()
+    report(f"{shape}, {n} sequences, bfloat16 against float32", outs["bfloat16"], want)
+    mh.assert_logits(outs["bfloat16"], want, "bfloat16", f"{shape}, {n} sequences of {lengths[:6]}, portions {portions}", bf16_fraction=REAL_BF16)
