@@ -4,11 +4,13 @@ heads each (nine is more than the fast decode kernel takes), widths that are no 
 layers, any vocabulary, windows from 5 keys to none, soft-caps on and off, tied and untied heads, pages of 16, 32
 and 64 rows.  Each case runs one to five sequences of unequal length through the engine in both dtypes - whole,
 as a prefix with single tokens after it (shorter sequences end earlier), and as chunks of 1 to 59 tokens a step
-that mix with one another - and compares every logit with the plain implementation."""
+that mix with one another - and compares every logit with the plain implementation; in float32 the three ways
+of cutting also have to give the same bits."""
 import tempfile
 
 import numpy as np
 import pytest
+import torch
 
 import model_helpers as mh
 import plain_gemma2 as plain
@@ -54,7 +56,10 @@ def test_a_configuration_drawn_at_random(case):
             eng = Engine(load_model(folder, dtype, "cuda:0"), max_tokens=4096, max_seqs=8, page_size=page)
             # whole prompts, one batch, every position
             slots = [eng.new_sequence() for _ in seqs]
-            mh.assert_logits(eng.step(slots, seqs, "all"), np.concatenate(want), dtype, f"{dtype}, whole; {what}")
+            whole = eng.step(slots, seqs, "all").clone()
+            mh.assert_logits(whole, np.concatenate(want), dtype, f"{dtype}, whole; {what}")
+            first_row = np.concatenate([[0], np.cumsum(lengths)])
+            exact = dtype == "float32"          # the 32-bit path gives the same bits however the tokens are cut
             for s in slots:
                 eng.release(s)
             # a prefix, then single tokens
@@ -68,6 +73,9 @@ def test_a_configuration_drawn_at_random(case):
                     break
                 got = eng.step([slots[i] for i in live], [[seqs[i][cut[i] + j]] for i in live], "last")
                 mh.assert_logits(got, np.stack([want[i][cut[i] + j] for i in live]), dtype, f"{dtype}, single tokens, step {j}; {what}")
+                for r, i in enumerate(live):
+                    assert not exact or torch.equal(got[r], whole[first_row[i] + cut[i] + j]), \
+                        f"float32 bits of position {cut[i] + j} of sequence {i} differ between a single-token step and the whole prompt; {what}"
             for s in slots:
                 eng.release(s)
             # chunks of many tokens on a cached prefix, of another length for each sequence and step
@@ -81,7 +89,12 @@ def test_a_configuration_drawn_at_random(case):
                 got = eng.step([slots[i] for i in live], toks, "all")
                 mh.assert_logits(got, np.concatenate([want[i][pos[i]:pos[i] + len(t)] for i, t in zip(live, toks)]), dtype,
                                  f"{dtype}, chunks from {pos}; {what}")
+                r = 0
                 for i, t in zip(live, toks):
+                    at = first_row[i] + pos[i]
+                    assert not exact or torch.equal(got[r:r + len(t)], whole[at:at + len(t)]), \
+                        f"float32 bits of a chunk of {len(t)} at position {pos[i]} of sequence {i} differ from the whole prompt; {what}"
+                    r += len(t)
                     pos[i] += len(t)
             for s in slots:
                 eng.release(s)
