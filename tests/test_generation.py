@@ -31,6 +31,28 @@ def test_plan_batches():
         plan_batches([100], 8, max_seqs=1, max_tokens=64, page_size=64, max_context=128)
 
 
+def test_plan_batches_on_requests_drawn_at_random():
+    """Every request once and in order; no batch over its limits; a batch ends only where the next request would
+    not have fitted."""
+    import random
+    rnd = random.Random(3)
+    for _ in range(300):
+        page = rnd.choice([16, 64])
+        max_context = rnd.choice([64, 200, 1024])
+        max_seqs = rnd.randint(1, 6)
+        max_tokens = page * rnd.randint(max_context // page + 1, max_context // page + 40)
+        new = rnd.randint(1, 300)
+        lens = [rnd.randint(1, max_context) for _ in range(rnd.randint(1, 30))]
+        cost = lambda n: -(-min(n + new - 1, max_context) // page) * page
+        batches = plan_batches(lens, new, max_seqs=max_seqs, max_tokens=max_tokens, page_size=page, max_context=max_context)
+        assert [i for b in batches for i in b] == list(range(len(lens)))
+        for k, b in enumerate(batches):
+            assert 1 <= len(b) <= max_seqs and sum(cost(lens[i]) for i in b) <= max_tokens
+            if k + 1 < len(batches):
+                nxt = batches[k + 1][0]
+                assert len(b) == max_seqs or sum(cost(lens[i]) for i in b) + cost(lens[nxt]) > max_tokens
+
+
 def test_sequence_state_decisions():
     s = SequenceState(0, [1, 2, 3], max_new_tokens=3, max_context=100, stop_token_ids=frozenset([9]))
     assert s.accept(4) and s.accept(5) and s.new_tokens == [4, 5] and not s.finished
